@@ -1,0 +1,113 @@
+/* Additions to the cs1_* C ABI exported by the same libqwen3_5_cuda.so: runtime helpers a
+ * host needs for timing and pinned staging, engine-pinned GEMM entry points, and the host
+ * executor (the decoder layer loop the reference keeps in Rust,
+ * src/models/qwen3_5/native/src/model.rs). Plain pointers and sizes only.
+ */
+#ifndef S1_EXECUTOR_H
+#define S1_EXECUTOR_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- runtime helpers (no counterpart in the reference ABI; its host links none of these
+ * because it never times on the device or stages through pinned memory) ---- */
+int s1_device_count(int* count);
+int s1_event_create(void** event);
+int s1_event_destroy(void* event);
+int s1_event_record(void* event, void* stream);
+int s1_event_sync(void* event);
+int s1_event_elapsed_ms(void* start, void* stop, float* ms);
+int s1_host_alloc(void** ptr, size_t bytes);
+int s1_host_free(void* ptr);
+int s1_upload_async(void* dst, const void* src, size_t bytes, void* stream);
+int s1_download_async(void* dst, const void* src, size_t bytes, void* stream);
+int s1_memset_async(void* dst, int value, size_t bytes, void* stream);
+int s1_device_sync(void);
+int s1_mem_info(size_t* free_bytes, size_t* total_bytes);
+
+/* ---- GEMM engines behind cs1_gemm, pinned (benchmark arms and parity tests) ---- */
+int s1_gemm_cublaslt(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream);
+int s1_gemm_tcgen05(const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream);
+/* Waits for the device, returns in *code the error word of the tcgen05 GEMM (0 = no bounded
+ * wait gave up) and clears it. */
+int s1_gemm_tc5_status(int* code);
+
+/* ---- host executor: the decoder prefill the reference keeps in Rust ---- */
+
+/* Model shape, the fields of the reference's Config (model.rs:28-48) that the text path uses. */
+typedef struct S1Config {
+    int hidden, intermediate, n_layers;
+    int heads, kv_heads, head_dim, rotary_half;   /* full attention; head_dim 128 or 256 */
+    int lin_k_heads, lin_v_heads;                 /* Gated DeltaNet, head dims fixed at 128 */
+    int vocab, max_positions;
+    float eps;
+    double rope_theta;
+    const unsigned char* full_attention;          /* n_layers flags: 1 = full attention, 0 = Gated DeltaNet */
+} S1Config;
+
+/* Model::load (model.rs:622-705) without the file reading: allocates the weight arena for
+ * `cfg` on `device` (one allocation, stacked GEMM groups contiguous, 256-byte aligned parts),
+ * a stream and a GEMM handle. Tensors arrive through s1_model_set_tensor under their
+ * checkpoint names without the model prefix ("layers.3.mlp.down_proj.weight", ...), or all
+ * at once from the seeded device-side generator. Returns 0 or an error code. */
+int s1_model_create(const S1Config* cfg, int device, void** model);
+void s1_model_destroy(void* model);
+int s1_model_set_tensor(void* model, const char* name, const void* host_bf16, size_t bytes);
+int s1_model_tensor(void* model, const char* name, void** device_ptr, size_t* bytes);
+/* Random weights of the shape, generated on the device: matrices and zero-centred norm
+ * weights N(0, std), the gated norm weight 1 + N(0, std), A_log U(0, ln 16), dt_bias N(0, 0.1). */
+int s1_model_init_random(void* model, uint64_t seed, float std);
+size_t s1_model_weight_bytes(void* model);
+void* s1_model_stream(void* model);
+/* CUDA-graph replay per ordered length vector (64 entries, first in first out; eager on a
+ * miss; a failed capture switches replay off): model.rs:797-897. Off by default, or on when
+ * CUA_S1_GRAPH=1 is in the environment at creation, as in the reference (model.rs:695). */
+int s1_model_enable_graphs(void* model, int on);
+int s1_model_graph_stats(void* model, int* replays, int* captures, int* enabled);
+
+/* Model::forward_batch (model.rs:769-823): prefill a pack of independent prompts
+ * (ids concatenated, lengths[nseq]) and return the final-norm hidden state of each prompt's
+ * last token as float32 [nseq, hidden] in host memory. Validates like the reference: empty
+ * batch, empty or oversized prompt and out-of-vocabulary ids are errors (S1_ERR_ARGUMENT).
+ * layer_out (nullable, host, bf16 [n_layers, T, hidden]) receives the residual stream after
+ * every layer; it forces eager execution and is meant for parity tests. */
+int s1_model_forward_batch(void* model, const int32_t* ids, const int* lengths, int nseq, float* last_hidden,
+                           void* layer_out);
+/* The same pass with ids already on the device (int32 [T]) and the last-token rows left on
+ * the device as bf16 [nseq, hidden] at *last_rows (owned by the model, valid until the next
+ * call); queue-only, no host synchronisation. */
+int s1_model_forward_device(void* model, const int32_t* ids_device, const int* lengths, int nseq, void** last_rows);
+/* A single Gated DeltaNet or attention layer's mixer on caller-provided hidden states is
+ * not exposed; parity of single layers goes through layer_out above. */
+int s1_model_sync(void* model);
+/* Device time of each operator family over the last eager forward is not tracked here; use events. */
+
+/* DecisionHead::score (open_jev executor.rs:56-68) and letter_logits (cua_s1 executor.rs:61-78):
+ * float64 accumulation on the host rounded to float32, bias added in float32 (bias nullable).
+ * weights [n_classes, hidden] float32, last [hidden] float32, logits [n_classes].
+ * Returns 0, or S1_ERR_NONFINITE when a logit is not finite. */
+int s1_head_logits(const float* weights, const float* bias, const float* last, int hidden, int n_classes,
+                   float* logits);
+/* contract::answer's softmax over (x - max) / temperature in float64 and its decision: the
+ * first maximum wins (contract.rs:227-247). probs nullable. Returns the argmax or -1. */
+int s1_decide(const float* logits, int n, double temperature, double* probs);
+/* batching::ranges (open_jev batching.rs:9-25): order-preserving groups of at most 16
+ * prompts and 4096 tokens. Writes group starts and returns the number of groups. */
+int s1_batch_ranges(const int* lengths, int n, int* starts);
+/* Token-balanced assignment of whole requests to n_ranks GPUs: longest processing time
+ * first on the cost a*T + b*T^2. rank_of [n]. No counterpart in the reference (single GPU). */
+int s1_assign_requests(const int* lengths, int n, int n_ranks, double a, double b, int* rank_of);
+
+#define S1_ERR_ARGUMENT 3000
+#define S1_ERR_NONFINITE 3001
+#define S1_ERR_UNKNOWN_TENSOR 3002
+#define S1_ERR_TENSOR_SIZE 3003
+
+#ifdef __cplusplus
+}
+#endif
+#endif

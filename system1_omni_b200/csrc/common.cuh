@@ -1,0 +1,83 @@
+// Device helpers shared by the sm_100a kernels: bf16 conversion, 128-bit packs, warp and
+// block reductions, and the launch-argument checks every entry point performs.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace s1 {
+
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ float f32(bf16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ bf16 to_bf16(float x) { return __float2bfloat16(x); }
+// A float rounded through bf16 (round to nearest even), where the model stores a bf16 result.
+__device__ __forceinline__ float rbf(float x) { return __bfloat162float(__float2bfloat16(x)); }
+
+__device__ __forceinline__ float silu(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float sigmoid(float x) { return 1.f / (1.f + expf(-x)); }
+
+// Eight bf16 values moved as one 16-byte access.
+struct alignas(16) Pack8 {
+    uint4 raw;
+};
+
+__device__ __forceinline__ void unpack8(const uint4& p, float (&out)[8]) {
+    const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        out[2 * i] = __uint_as_float(w[i] << 16);
+        out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__device__ __forceinline__ uint4 pack8(const float (&in)[8]) {
+    uint4 p;
+    p.x = pack2(in[0], in[1]);
+    p.y = pack2(in[2], in[3]);
+    p.z = pack2(in[4], in[5]);
+    p.w = pack2(in[6], in[7]);
+    return p;
+}
+
+__device__ __forceinline__ uint4 ld16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void st16(void* p, const uint4& v) { *reinterpret_cast<uint4*>(p) = v; }
+// Streaming variants for data touched once: keep it out of L1 and mark it evict-first.
+__device__ __forceinline__ uint4 ld16_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+template <int WIDTH = 32>
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+    for (int o = WIDTH / 2; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    return x;
+}
+
+// Sum over a block of up to 1024 threads; scratch holds 32 floats; every thread gets the sum.
+__device__ __forceinline__ float block_sum(float x, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+    x = warp_sum(x);
+    if (lane == 0) scratch[warp] = x;
+    __syncthreads();
+    float t = lane < warps ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    __syncthreads();
+    return t;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
+
+}  // namespace s1

@@ -1,0 +1,658 @@
+// Host executor of the Qwen3.5-style hybrid decoder prefill: weight arena, scratch plan,
+// layer loop, packed batches, CUDA-graph cache, last-token readout, decision heads, packing
+// policy and the multi-GPU request assignment. It drives the device only through the
+// cs1_* C ABI of this library, the way the reference's Rust executor does
+// (src/models/qwen3_5/native/src/model.rs); citations below are to that file unless noted.
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+#include <deque>
+#include <numeric>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "cs1_ops.h"
+#include "exec_kernels.h"
+#include "s1_executor.h"
+
+namespace {
+
+constexpr size_t ALIGN = 256;  // model.rs:23
+constexpr size_t BF16 = 2, F32 = 4;
+constexpr size_t GEMM_WORKSPACE = 32u << 20;  // model.rs:26
+constexpr int GRAPH_CACHE = 64;               // model.rs:879-882
+constexpr int ENDS_RING = 16;
+
+#define S1_TRY(expr)            \
+    do {                        \
+        const int rc_ = (expr); \
+        if (rc_ != 0) return rc_; \
+    } while (0)
+
+struct Tensor {
+    size_t offset = 0, bytes = 0;
+    bool filled = false;
+};
+
+// Byte offsets into one scratch allocation for up to `cap` tokens (model.rs:415-555).
+struct Scratch {
+    size_t cap = 0;
+    void* buf = nullptr;
+    size_t ids, res, x, delta, gdn_in, beta, g, lq, lk, lv, lo, ln, workspace, attn_in, aq, agate, ak, ao, gate_up,
+        act, cos, sin, ends, last, total;
+    char* at(size_t off) const { return static_cast<char*>(buf) + off; }
+};
+
+struct Layer {
+    bool full = false;
+    Tensor input_norm, post_norm, gate_up, down;
+    Tensor in_proj, conv, a_log, dt_bias, norm, out;  // Gated DeltaNet
+    Tensor qkv, o, q_norm, k_norm;                    // full attention
+};
+
+struct Model {
+    S1Config cfg{};
+    std::vector<unsigned char> full;
+    int device = 0;
+    void* arena = nullptr;
+    size_t arena_bytes = 0;
+    std::unordered_map<std::string, Tensor> named;  // every checkpoint tensor
+    std::vector<std::pair<std::string, Tensor>> order;
+    Tensor embed, final_norm;
+    std::vector<Layer> layers;
+    void* stream = nullptr;
+    void* gemm = nullptr;
+    Scratch s;
+    bool graph_enabled = false;
+    int replays = 0, captures = 0;
+    std::deque<std::pair<std::vector<int>, void*>> graphs;
+    int* ends_host = nullptr;  // pinned ring of ENDS_RING slots of cap ints
+    size_t ends_slot = 0;
+    void* last_host = nullptr;  // pinned staging of the last rows
+    size_t last_host_bytes = 0;
+
+    int key_dim() const { return cfg.lin_k_heads * 128; }
+    int value_dim() const { return cfg.lin_v_heads * 128; }
+    int conv_w() const { return 2 * key_dim() + value_dim(); }
+    int gdn_in_w() const { return conv_w() + value_dim() + 2 * cfg.lin_v_heads; }
+    int attn_q_w() const { return cfg.heads * cfg.head_dim * 2; }
+    int attn_in_w() const { return attn_q_w() + 2 * cfg.kv_heads * cfg.head_dim; }
+    char* w(const Tensor& t) const { return static_cast<char*>(arena) + t.offset; }
+};
+
+void clear_graphs(Model* m) {
+    for (auto& g : m->graphs) cs1_graph_destroy(g.second);
+    m->graphs.clear();
+}
+
+// What the kernels implement (model.rs:134-180), with head_dim 128 accepted besides 256.
+int validate(const S1Config& c) {
+    if (c.hidden <= 0 || c.hidden % 8 || c.intermediate <= 0 || c.intermediate % 8 || c.n_layers <= 0 || c.vocab <= 0)
+        return S1_ERR_ARGUMENT;
+    if (c.head_dim != 128 && c.head_dim != 256) return S1_ERR_ARGUMENT;
+    if (c.kv_heads <= 0 || c.heads <= 0 || c.heads % c.kv_heads) return S1_ERR_ARGUMENT;
+    if (c.lin_k_heads <= 0 || c.lin_v_heads <= 0 || c.lin_v_heads % c.lin_k_heads) return S1_ERR_ARGUMENT;
+    if (c.rotary_half <= 0 || c.rotary_half % 8 || 2 * c.rotary_half > c.head_dim ||
+        ((c.rotary_half / 8) & (c.rotary_half / 8 - 1)))
+        return S1_ERR_ARGUMENT;
+    if (c.max_positions <= 0 || c.max_positions > (1 << 24)) return S1_ERR_ARGUMENT;
+    if (!(c.rope_theta > 0.0) || !isfinite(c.rope_theta) || !c.full_attention) return S1_ERR_ARGUMENT;
+    return 0;
+}
+
+// Arena plan: by layer, the members of a stacked GEMM group back to back (model.rs:205-231).
+void plan_arena(Model* m) {
+    const S1Config& c = m->cfg;
+    size_t at = 0;
+    auto place = [&](const std::string& name, size_t elems, bool aligned) {
+        if (aligned) at = (at + ALIGN - 1) / ALIGN * ALIGN;
+        Tensor t;
+        t.offset = at;
+        t.bytes = elems * BF16;
+        at += t.bytes;
+        m->named[name] = t;
+        m->order.emplace_back(name, t);
+        return t;
+    };
+    auto join = [](const Tensor& first, const Tensor& last) {
+        Tensor t;
+        t.offset = first.offset;
+        t.bytes = last.offset + last.bytes - first.offset;
+        return t;
+    };
+    const size_t h = c.hidden, I = c.intermediate, kd = m->key_dim(), vd = m->value_dim(), hv = c.lin_v_heads;
+    const size_t hq = c.heads, hk = c.kv_heads, hd = c.head_dim;
+    m->embed = place("embed_tokens.weight", (size_t)c.vocab * h, true);
+    m->final_norm = place("norm.weight", h, true);
+    m->layers.resize(c.n_layers);
+    for (int i = 0; i < c.n_layers; i++) {
+        const std::string p = "layers." + std::to_string(i) + ".";
+        Layer& ly = m->layers[i];
+        ly.full = m->full[i] != 0;
+        if (!ly.full) {
+            const Tensor a = place(p + "linear_attn.in_proj_qkv.weight", (2 * kd + vd) * h, true);
+            place(p + "linear_attn.in_proj_z.weight", vd * h, false);
+            place(p + "linear_attn.in_proj_b.weight", hv * h, false);
+            const Tensor d = place(p + "linear_attn.in_proj_a.weight", hv * h, false);
+            ly.in_proj = join(a, d);
+        } else {
+            const Tensor a = place(p + "self_attn.q_proj.weight", hq * hd * 2 * h, true);
+            place(p + "self_attn.k_proj.weight", hk * hd * h, false);
+            const Tensor d = place(p + "self_attn.v_proj.weight", hk * hd * h, false);
+            ly.qkv = join(a, d);
+        }
+        {
+            const Tensor a = place(p + "mlp.gate_proj.weight", I * h, true);
+            const Tensor d = place(p + "mlp.up_proj.weight", I * h, false);
+            ly.gate_up = join(a, d);
+        }
+        ly.down = place(p + "mlp.down_proj.weight", h * I, true);
+        ly.input_norm = place(p + "input_layernorm.weight", h, true);
+        ly.post_norm = place(p + "post_attention_layernorm.weight", h, true);
+        if (!ly.full) {
+            ly.conv = place(p + "linear_attn.conv1d.weight", (2 * kd + vd) * 4, true);
+            ly.a_log = place(p + "linear_attn.A_log", hv, true);
+            ly.dt_bias = place(p + "linear_attn.dt_bias", hv, true);
+            ly.norm = place(p + "linear_attn.norm.weight", 128, true);
+            ly.out = place(p + "linear_attn.out_proj.weight", h * vd, true);
+        } else {
+            ly.o = place(p + "self_attn.o_proj.weight", h * hq * hd, true);
+            ly.q_norm = place(p + "self_attn.q_norm.weight", hd, true);
+            ly.k_norm = place(p + "self_attn.k_norm.weight", hd, true);
+        }
+    }
+    m->arena_bytes = (at + ALIGN - 1) / ALIGN * ALIGN;
+}
+
+inline uint16_t f2bf(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+inline float bf2f(uint16_t b) {
+    const uint32_t u = (uint32_t)b << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+// cos/sin tables [positions, half] in bf16 for text positions 0..n-1 (all three rotary axes
+// equal): float32 inverse frequencies and products, float64 trigonometry (inputs.rs:69-95).
+void rotary_tables(int n, int half, double theta, std::vector<uint16_t>& cos_t, std::vector<uint16_t>& sin_t) {
+    std::vector<float> inv(half);
+    for (int i = 0; i < half; i++) inv[i] = 1.0f / powf((float)theta, (float)(2 * i) / (float)(2 * half));
+    cos_t.resize((size_t)n * half);
+    sin_t.resize((size_t)n * half);
+    for (int t = 0; t < n; t++)
+        for (int i = 0; i < half; i++) {
+            const double angle = (double)(inv[i] * (float)t);
+            cos_t[(size_t)t * half + i] = f2bf((float)cos(angle));
+            sin_t[(size_t)t * half + i] = f2bf((float)sin(angle));
+        }
+}
+
+int make_scratch(Model* m, size_t cap) {
+    const S1Config& c = m->cfg;
+    Scratch& s = m->s;
+    if (s.buf) {
+        S1_TRY(cs1_stream_sync(m->stream));
+        S1_TRY(cs1_free(s.buf));
+        s.buf = nullptr;
+        s.cap = 0;
+    }
+    if (m->ends_host) {
+        cudaFreeHost(m->ends_host);
+        m->ends_host = nullptr;
+    }
+    const size_t h = c.hidden, kd = m->key_dim(), vd = m->value_dim(), hv = c.lin_v_heads;
+    const size_t hq = c.heads, hk = c.kv_heads, hd = c.head_dim;
+    size_t next = 0;
+    auto take = [&](size_t bytes) {
+        const size_t off = next;
+        next = (off + bytes + ALIGN - 1) / ALIGN * ALIGN;
+        return off;
+    };
+    const size_t ws_floats = cs1_gdn_workspace_floats((int)cap, (int)hv);
+    s.ids = take(cap * 4);
+    s.res = take(cap * h * BF16);
+    s.x = take(cap * h * BF16);
+    s.delta = take(cap * h * BF16);
+    s.gdn_in = take(cap * m->gdn_in_w() * BF16);
+    s.beta = take(cap * hv * BF16);
+    s.g = take(cap * hv * F32);
+    s.lq = take(cap * kd * BF16);
+    s.lk = take(cap * kd * BF16);
+    s.lv = take(cap * vd * BF16);
+    s.lo = take(cap * vd * BF16);
+    s.ln = take(cap * vd * BF16);
+    s.workspace = take(ws_floats * F32);
+    s.attn_in = take(cap * m->attn_in_w() * BF16);
+    s.aq = take(cap * hq * hd * BF16);
+    s.agate = take(cap * hq * hd * BF16);
+    s.ak = take(cap * hk * hd * BF16);
+    s.ao = take(cap * hq * hd * BF16);
+    s.gate_up = take(cap * 2 * c.intermediate * BF16);
+    s.act = take(cap * c.intermediate * BF16);
+    s.cos = take(cap * c.rotary_half * BF16);
+    s.sin = take(cap * c.rotary_half * BF16);
+    s.ends = take(cap * 4);
+    s.last = take(cap * h * BF16);  // at most one row per prompt, at most cap prompts
+    s.total = next;
+    S1_TRY(cs1_malloc(&s.buf, s.total));
+    s.cap = cap;
+    std::vector<uint16_t> cos_t, sin_t;
+    const size_t npos = std::min(cap, (size_t)c.max_positions);
+    rotary_tables((int)npos, c.rotary_half, c.rope_theta, cos_t, sin_t);
+    S1_TRY(cs1_upload(s.at(s.cos), cos_t.data(), cos_t.size() * 2, m->stream));
+    S1_TRY(cs1_upload(s.at(s.sin), sin_t.data(), sin_t.size() * 2, m->stream));
+    S1_TRY((int)cudaHostAlloc(reinterpret_cast<void**>(&m->ends_host), ENDS_RING * cap * sizeof(int),
+                              cudaHostAllocDefault));
+    return 0;
+}
+
+// Grow to the next multiple of 1024 tokens; a new scratch invalidates captured graphs (model.rs:747-761).
+int prepare_scratch(Model* m, size_t t) {
+    S1_TRY(cs1_set_device(m->device));
+    if (m->s.buf == nullptr || t > m->s.cap) {
+        clear_graphs(m);
+        S1_TRY(make_scratch(m, (t + 1023) / 1024 * 1024));
+    }
+    return 0;
+}
+
+int gemm(Model* m, size_t x, const Tensor& w, size_t y, int rows, int n, int k) {
+    return cs1_gemm(m->gemm, m->s.at(x), m->w(w), m->s.at(y), rows, n, k, n, m->stream);
+}
+
+// The layer loop (model.rs:1119-1338). Pointwise operators and every GEMM run once over the
+// packed rows; conv, delta rule, attention prep and attention run per sequence. (The
+// reference also splits the out/down GEMMs per sequence, only to pin cuBLASLt's
+// shape-dependent reduction order; here a row's result does not depend on the row count.)
+// dump (nullable, host) receives the residual stream after each layer.
+int run(Model* m, const int* lengths, int nseq, char* dump) {
+    const S1Config& c = m->cfg;
+    const Scratch& s = m->s;
+    void* st = m->stream;
+    int t = 0;
+    for (int i = 0; i < nseq; i++) t += lengths[i];
+    const int h = c.hidden, kd = m->key_dim(), vd = m->value_dim(), hv = c.lin_v_heads;
+    const int hq = c.heads, hk = c.kv_heads, hd = c.head_dim, I = c.intermediate;
+    const int gdn_in = m->gdn_in_w(), attn_in = m->attn_in_w(), attn_q = m->attn_q_w(), conv = m->conv_w();
+    const float eps = c.eps;
+    S1_TRY(cs1_rms_norm(s.at(s.res), m->w(m->layers[0].input_norm), s.at(s.x), t, h, eps, st));
+    for (size_t li = 0; li < m->layers.size(); li++) {
+        const Layer& ly = m->layers[li];
+        if (!ly.full) {
+            S1_TRY(gemm(m, s.x, ly.in_proj, s.gdn_in, t, gdn_in, h));
+            const size_t z = s.gdn_in + (size_t)conv * BF16;
+            const size_t b = z + (size_t)vd * BF16;
+            const size_t a = b + (size_t)hv * BF16;
+            size_t off = 0;
+            for (int q = 0; q < nseq; q++) {
+                S1_TRY(cs1_gdn_conv(s.at(s.gdn_in + off * gdn_in * BF16), gdn_in, m->w(ly.conv),
+                                    s.at(s.lq + off * kd * BF16), s.at(s.lk + off * kd * BF16),
+                                    s.at(s.lv + off * vd * BF16), lengths[q], kd, vd, st));
+                off += lengths[q];
+            }
+            S1_TRY(cs1_gdn_gates(s.at(b), s.at(a), gdn_in, m->w(ly.a_log), m->w(ly.dt_bias), s.at(s.beta),
+                                 reinterpret_cast<float*>(s.at(s.g)), t, hv, st));
+            off = 0;
+            for (int q = 0; q < nseq; q++) {
+                S1_TRY(cs1_gdn_prefill(s.at(s.lq + off * kd * BF16), s.at(s.lk + off * kd * BF16),
+                                       s.at(s.lv + off * vd * BF16),
+                                       reinterpret_cast<const float*>(s.at(s.g + off * hv * F32)),
+                                       s.at(s.beta + off * hv * BF16), s.at(s.lo + off * vd * BF16),
+                                       reinterpret_cast<float*>(s.at(s.workspace)), lengths[q], hv, c.lin_k_heads,
+                                       1.0f / sqrtf(128.0f), st));
+                off += lengths[q];
+            }
+            S1_TRY(cs1_gated_rms_norm(s.at(s.lo), s.at(z), gdn_in, m->w(ly.norm), s.at(s.ln), t, hv, 128, eps, st));
+            S1_TRY(gemm(m, s.ln, ly.out, s.delta, t, h, vd));
+        } else {
+            S1_TRY(gemm(m, s.x, ly.qkv, s.attn_in, t, attn_in, h));
+            const size_t k = s.attn_in + (size_t)attn_q * BF16;
+            const size_t v = k + (size_t)hk * hd * BF16;
+            size_t off = 0;
+            for (int q = 0; q < nseq; q++) {
+                // the unshifted table base restarts positions at 0 for every sequence (model.rs:1244-1251)
+                S1_TRY(cs1_attn_prep(s.at(s.attn_in + off * attn_in * BF16), s.at(k + off * attn_in * BF16), attn_in,
+                                     m->w(ly.q_norm), m->w(ly.k_norm), s.at(s.cos), s.at(s.sin),
+                                     s.at(s.aq + off * hq * hd * BF16), s.at(s.agate + off * hq * hd * BF16),
+                                     s.at(s.ak + off * hk * hd * BF16), lengths[q], hq, hk, hd, c.rotary_half, eps,
+                                     st));
+                S1_TRY(cs1_attention_gated(s.at(s.aq + off * hq * hd * BF16), s.at(s.ak + off * hk * hd * BF16),
+                                           s.at(v + off * attn_in * BF16), attn_in,
+                                           s.at(s.agate + off * hq * hd * BF16), s.at(s.ao + off * hq * hd * BF16),
+                                           lengths[q], hq, hk, hd, 1.0f / sqrtf((float)hd), st));
+                off += lengths[q];
+            }
+            S1_TRY(gemm(m, s.ao, ly.o, s.delta, t, h, hq * hd));
+        }
+        S1_TRY(cs1_add_rms_norm(s.at(s.res), s.at(s.delta), m->w(ly.post_norm), s.at(s.x), t, h, eps, st));
+        S1_TRY(gemm(m, s.x, ly.gate_up, s.gate_up, t, 2 * I, h));
+        S1_TRY(cs1_silu_mul(s.at(s.gate_up), 2 * I, s.at(s.act), t, I, st));
+        S1_TRY(gemm(m, s.act, ly.down, s.delta, t, h, I));
+        const Tensor& next = li + 1 < m->layers.size() ? m->layers[li + 1].input_norm : m->final_norm;
+        S1_TRY(cs1_add_rms_norm(s.at(s.res), s.at(s.delta), m->w(next), s.at(s.x), t, h, eps, st));
+        if (dump) S1_TRY(cs1_download(dump + li * (size_t)t * h * BF16, s.at(s.res), (size_t)t * h * BF16, st));
+    }
+    return 0;
+}
+
+// Replay a captured graph for this ordered length vector, or run eagerly and capture
+// (model.rs:797-813, 862-897). The eager result of a miss is kept: run() advances the
+// residual in place, so replaying on top of it would advance it twice.
+int run_or_replay(Model* m, const int* lengths, int nseq) {
+    if (!m->graph_enabled) return run(m, lengths, nseq, nullptr);
+    const std::vector<int> key(lengths, lengths + nseq);
+    for (auto& g : m->graphs) {
+        if (g.first == key) {
+            m->replays++;
+            return cs1_graph_launch(g.second, m->stream);
+        }
+    }
+    S1_TRY(run(m, lengths, nseq, nullptr));
+    S1_TRY(cs1_stream_sync(m->stream));
+    void* exec = nullptr;
+    int rc = cs1_graph_begin(m->stream);
+    if (rc == 0) {
+        const int body = run(m, lengths, nseq, nullptr);
+        rc = cs1_graph_end(m->stream, &exec);
+        if (rc == 0 && body != 0) {
+            cs1_graph_destroy(exec);
+            rc = body;
+        }
+    }
+    if (rc == 0) {
+        if ((int)m->graphs.size() == GRAPH_CACHE) {
+            cs1_graph_destroy(m->graphs.front().second);
+            m->graphs.pop_front();
+        }
+        m->graphs.emplace_back(key, exec);
+        m->captures++;
+    } else {
+        // keep the eager result, stop trying to capture
+        m->graph_enabled = false;
+        clear_graphs(m);
+    }
+    return 0;
+}
+
+int check_batch(const Model* m, const int* lengths, int nseq, long* total) {
+    if (nseq <= 0 || !lengths) return S1_ERR_ARGUMENT;
+    long t = 0;
+    for (int i = 0; i < nseq; i++) {
+        if (lengths[i] <= 0 || lengths[i] > m->cfg.max_positions) return S1_ERR_ARGUMENT;
+        t += lengths[i];
+    }
+    if (t > 0x7fffffffL) return S1_ERR_ARGUMENT;
+    *total = t;
+    return 0;
+}
+
+int stage_ends(Model* m, const int* lengths, int nseq) {
+    int* slot = m->ends_host + (m->ends_slot++ % ENDS_RING) * m->s.cap;
+    int end = 0;
+    for (int i = 0; i < nseq; i++) {
+        end += lengths[i];
+        slot[i] = end;
+    }
+    return (int)cudaMemcpyAsync(m->s.at(m->s.ends), slot, (size_t)nseq * sizeof(int), cudaMemcpyHostToDevice,
+                                static_cast<cudaStream_t>(m->stream));
+}
+
+}  // namespace
+
+extern "C" {
+
+int s1_model_create(const S1Config* cfg, int device, void** out) {
+    if (!cfg || !out) return S1_ERR_ARGUMENT;
+    S1_TRY(validate(*cfg));
+    S1_TRY(cs1_set_device(device));
+    Model* m = new Model();
+    m->cfg = *cfg;
+    m->full.assign(cfg->full_attention, cfg->full_attention + cfg->n_layers);
+    m->cfg.full_attention = m->full.data();
+    m->device = device;
+    plan_arena(m);
+    int rc = cs1_stream_create(&m->stream);
+    if (rc == 0) rc = cs1_malloc(&m->arena, m->arena_bytes);
+    if (rc == 0) {
+        m->gemm = cs1_gemm_create(GEMM_WORKSPACE);
+        if (!m->gemm) rc = CS1_ERR_GEMM_BASE + 1;
+    }
+    if (rc != 0) {
+        s1_model_destroy(m);
+        return rc;
+    }
+    const char* flag = getenv("CUA_S1_GRAPH");
+    m->graph_enabled = flag && strcmp(flag, "1") == 0;
+    *out = m;
+    return 0;
+}
+
+void s1_model_destroy(void* model) {
+    Model* m = static_cast<Model*>(model);
+    if (!m) return;
+    cs1_set_device(m->device);
+    if (m->stream) cs1_stream_sync(m->stream);
+    clear_graphs(m);
+    if (m->gemm) cs1_gemm_destroy(m->gemm);
+    if (m->s.buf) cs1_free(m->s.buf);
+    if (m->arena) cs1_free(m->arena);
+    if (m->ends_host) cudaFreeHost(m->ends_host);
+    if (m->last_host) cudaFreeHost(m->last_host);
+    if (m->stream) cs1_stream_destroy(m->stream);
+    delete m;
+}
+
+int s1_model_set_tensor(void* model, const char* name, const void* host_bf16, size_t bytes) {
+    Model* m = static_cast<Model*>(model);
+    if (!m || !name || !host_bf16) return S1_ERR_ARGUMENT;
+    auto it = m->named.find(name);
+    if (it == m->named.end()) return S1_ERR_UNKNOWN_TENSOR;
+    if (it->second.bytes != bytes) return S1_ERR_TENSOR_SIZE;
+    S1_TRY(cs1_set_device(m->device));
+    S1_TRY(cs1_upload(m->w(it->second), host_bf16, bytes, m->stream));
+    it->second.filled = true;
+    return 0;
+}
+
+int s1_model_tensor(void* model, const char* name, void** device_ptr, size_t* bytes) {
+    Model* m = static_cast<Model*>(model);
+    if (!m || !name) return S1_ERR_ARGUMENT;
+    auto it = m->named.find(name);
+    if (it == m->named.end()) return S1_ERR_UNKNOWN_TENSOR;
+    if (device_ptr) *device_ptr = m->w(it->second);
+    if (bytes) *bytes = it->second.bytes;
+    return 0;
+}
+
+int s1_model_init_random(void* model, uint64_t seed, float std) {
+    Model* m = static_cast<Model*>(model);
+    if (!m) return S1_ERR_ARGUMENT;
+    S1_TRY(cs1_set_device(m->device));
+    cudaStream_t st = static_cast<cudaStream_t>(m->stream);
+    uint64_t index = 0;
+    auto ends_with = [](const std::string& s, const char* tail) {
+        const size_t n = strlen(tail);
+        return s.size() >= n && s.compare(s.size() - n, n, tail) == 0;
+    };
+    for (auto& entry : m->order) {
+        const std::string& name = entry.first;
+        const Tensor& t = entry.second;
+        const uint64_t sd = seed * 0x100000001b3ull + (++index) * 0x9e3779b97f4a7c15ull;
+        const size_t n = t.bytes / BF16;
+        int rc;
+        if (ends_with(name, "linear_attn.A_log"))
+            rc = s1::fill_bf16(m->w(t), n, sd, 0.f, logf(16.f), 1, st);
+        else if (ends_with(name, "linear_attn.dt_bias"))
+            rc = s1::fill_bf16(m->w(t), n, sd, 0.f, 0.1f, 0, st);
+        else if (ends_with(name, "linear_attn.norm.weight"))
+            rc = s1::fill_bf16(m->w(t), n, sd, 1.f, std, 0, st);
+        else
+            rc = s1::fill_bf16(m->w(t), n, sd, 0.f, std, 0, st);
+        S1_TRY(rc);
+    }
+    for (auto& kv : m->named) kv.second.filled = true;
+    return cs1_stream_sync(m->stream);
+}
+
+size_t s1_model_weight_bytes(void* model) { return model ? static_cast<Model*>(model)->arena_bytes : 0; }
+void* s1_model_stream(void* model) { return model ? static_cast<Model*>(model)->stream : nullptr; }
+
+int s1_model_enable_graphs(void* model, int on) {
+    Model* m = static_cast<Model*>(model);
+    if (!m) return S1_ERR_ARGUMENT;
+    m->graph_enabled = on != 0;
+    if (!on) clear_graphs(m);
+    return 0;
+}
+
+int s1_model_graph_stats(void* model, int* replays, int* captures, int* enabled) {
+    Model* m = static_cast<Model*>(model);
+    if (!m) return S1_ERR_ARGUMENT;
+    if (replays) *replays = m->replays;
+    if (captures) *captures = m->captures;
+    if (enabled) *enabled = m->graph_enabled ? 1 : 0;
+    return 0;
+}
+
+int s1_model_forward_batch(void* model, const int32_t* ids, const int* lengths, int nseq, float* last_hidden,
+                           void* layer_out) {
+    Model* m = static_cast<Model*>(model);
+    if (!m || !ids || !last_hidden) return S1_ERR_ARGUMENT;
+    long total = 0;
+    S1_TRY(check_batch(m, lengths, nseq, &total));
+    for (long i = 0; i < total; i++)
+        if (ids[i] < 0 || ids[i] >= m->cfg.vocab) return S1_ERR_ARGUMENT;
+    S1_TRY(prepare_scratch(m, (size_t)total));
+    const Scratch& s = m->s;
+    const int h = m->cfg.hidden;
+    S1_TRY(cs1_upload(s.at(s.ids), ids, (size_t)total * 4, m->stream));
+    S1_TRY(stage_ends(m, lengths, nseq));
+    S1_TRY(cs1_embed(reinterpret_cast<const int32_t*>(s.at(s.ids)), m->w(m->embed), s.at(s.res), (int)total, h,
+                     m->stream));
+    if (layer_out)
+        S1_TRY(run(m, lengths, nseq, static_cast<char*>(layer_out)));
+    else
+        S1_TRY(run_or_replay(m, lengths, nseq));
+    S1_TRY(s1::gather_rows(s.at(s.x), reinterpret_cast<const int*>(s.at(s.ends)), s.at(s.last), nseq, h,
+                           static_cast<cudaStream_t>(m->stream)));
+    const size_t bytes = (size_t)nseq * h * BF16;
+    if (m->last_host_bytes < bytes) {
+        if (m->last_host) cudaFreeHost(m->last_host);
+        m->last_host = nullptr;
+        m->last_host_bytes = 0;
+        S1_TRY((int)cudaHostAlloc(&m->last_host, bytes, cudaHostAllocDefault));
+        m->last_host_bytes = bytes;
+    }
+    S1_TRY(cs1_download(m->last_host, s.at(s.last), bytes, m->stream));
+    const uint16_t* rows = static_cast<const uint16_t*>(m->last_host);
+    for (size_t i = 0; i < (size_t)nseq * h; i++) last_hidden[i] = bf2f(rows[i]);
+    return 0;
+}
+
+int s1_model_forward_device(void* model, const int32_t* ids_device, const int* lengths, int nseq, void** last_rows) {
+    Model* m = static_cast<Model*>(model);
+    if (!m || !ids_device) return S1_ERR_ARGUMENT;
+    long total = 0;
+    S1_TRY(check_batch(m, lengths, nseq, &total));
+    S1_TRY(prepare_scratch(m, (size_t)total));
+    const Scratch& s = m->s;
+    const int h = m->cfg.hidden;
+    S1_TRY(stage_ends(m, lengths, nseq));
+    S1_TRY(cs1_embed(ids_device, m->w(m->embed), s.at(s.res), (int)total, h, m->stream));
+    S1_TRY(run_or_replay(m, lengths, nseq));
+    S1_TRY(s1::gather_rows(s.at(s.x), reinterpret_cast<const int*>(s.at(s.ends)), s.at(s.last), nseq, h,
+                           static_cast<cudaStream_t>(m->stream)));
+    if (last_rows) *last_rows = s.at(s.last);
+    return 0;
+}
+
+int s1_model_sync(void* model) {
+    Model* m = static_cast<Model*>(model);
+    if (!m) return S1_ERR_ARGUMENT;
+    S1_TRY(cs1_set_device(m->device));
+    return cs1_stream_sync(m->stream);
+}
+
+int s1_head_logits(const float* weights, const float* bias, const float* last, int hidden, int n_classes,
+                   float* logits) {
+    if (!weights || !last || !logits || hidden <= 0 || n_classes < 0) return S1_ERR_ARGUMENT;
+    int bad = 0;
+    for (int o = 0; o < n_classes; o++) {
+        double acc = 0.0;
+        const float* w = weights + (size_t)o * hidden;
+        for (int i = 0; i < hidden; i++) acc += (double)w[i] * (double)last[i];
+        float v = (float)acc;
+        if (bias) v += bias[o];
+        logits[o] = v;
+        if (!isfinite(v)) bad = 1;
+    }
+    return bad ? S1_ERR_NONFINITE : 0;
+}
+
+int s1_decide(const float* logits, int n, double temperature, double* probs) {
+    if (!logits || n <= 0 || !(temperature > 0.0) || !isfinite(temperature)) return -1;
+    float mx = -INFINITY;
+    for (int i = 0; i < n; i++) {
+        if (!isfinite(logits[i])) return -1;
+        mx = std::max(mx, logits[i]);
+    }
+    std::vector<double> p(n);
+    double total = 0.0;
+    for (int i = 0; i < n; i++) {
+        p[i] = exp(((double)logits[i] - (double)mx) / temperature);
+        total += p[i];
+    }
+    int mode = 0;
+    for (int i = 0; i < n; i++) {
+        p[i] /= total;
+        if (i > 0 && p[i] > p[mode]) mode = i;
+    }
+    if (probs) memcpy(probs, p.data(), sizeof(double) * n);
+    return mode;
+}
+
+int s1_batch_ranges(const int* lengths, int n, int* starts) {
+    const int MAX_SEQUENCES = 16;
+    const long MAX_TOKENS = 4096;
+    int groups = 0, start = 0;
+    long tokens = 0;
+    for (int index = 0; index < n; index++) {
+        if (index > start && (index - start == MAX_SEQUENCES || tokens + lengths[index] > MAX_TOKENS)) {
+            starts[groups++] = start;
+            start = index;
+            tokens = 0;
+        }
+        tokens += lengths[index];
+    }
+    if (start < n) starts[groups++] = start;
+    return groups;
+}
+
+int s1_assign_requests(const int* lengths, int n, int n_ranks, double a, double b, int* rank_of) {
+    if (n < 0 || n_ranks <= 0 || (n > 0 && (!lengths || !rank_of))) return S1_ERR_ARGUMENT;
+    std::vector<int> idx(n);
+    std::iota(idx.begin(), idx.end(), 0);
+    auto cost = [&](int i) { return a * lengths[i] + b * (double)lengths[i] * (double)lengths[i]; };
+    std::stable_sort(idx.begin(), idx.end(), [&](int x, int y) { return cost(x) > cost(y); });
+    std::vector<double> load(n_ranks, 0.0);
+    for (int i : idx) {
+        int best = 0;
+        for (int r = 1; r < n_ranks; r++)
+            if (load[r] < load[best]) best = r;
+        rank_of[i] = best;
+        load[best] += cost(i);
+    }
+    return 0;
+}
+
+}  // extern "C"

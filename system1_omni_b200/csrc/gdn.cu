@@ -1,0 +1,616 @@
+// Chunked (C = 64) WY-form gated delta rule, prefill only, head dim 128.
+//
+// Two kernels per call:
+//   gdn_prep  one block per (chunk, value head), fully parallel: cumulative log-decays, L2
+//             norms of q and k, the pair products k.k and q.k on TF32 tensor cores, the
+//             triangular inverse T = (I + A)^-1 in float32, u = T beta v and
+//             w = T beta exp(cum) k on bf16 tensor cores. Leaves u, w, qd = q exp(cum),
+//             kd = k exp(cum_last - cum), P = (q.k) decay-masked and exp(cum_last) in the
+//             workspace.
+//   gdn_scan  one block per (value head, slice of value columns), sequential over chunks:
+//             the state S [128 x slice] stays in float32 registers for the whole sequence
+//             with a bf16 copy in shared memory as the tensor-core operand; per chunk
+//             v_new = u - w S, o = qd S + P v_new (written straight to the output) and
+//             S = decay S + kd^T v_new. Neither S nor v_new ever goes to global memory.
+//
+// Arithmetic and rounding points are those of the reference implementation
+// (src/backends/cuda/qwen3_5/gdn_prefill.cu:110-544): float32 cumsum, norms, pair products
+// (TF32 operands), inverse and state; bf16 qd, kd, P, T*beta, k*exp(cum), u, w, v_new and
+// the chunk-entry state. The state is float32 across calls (s_in / s_out), so a window that
+// starts on a multiple of 64 tokens continues a previous one bit for bit.
+#include "common.cuh"
+#include "cs1_ops.h"
+#include "mma.cuh"
+
+namespace s1 {
+namespace {
+
+constexpr int C = 64;   // chunk length
+constexpr int D = 128;  // key and value head dim
+constexpr int LDF = D + 4;   // float row stride of the TF32 operand tiles
+constexpr int LDA = C + 4;   // float row stride of A
+constexpr int LDH = D + 8;   // bf16 row stride of [64][128] tiles
+constexpr int LDT = C + 8;   // bf16 row stride of [64][64] tiles
+
+struct Work {
+    bf16* u;       // [H, NCC, 128]
+    bf16* w;       // [H, NCC, 128]
+    bf16* qd;      // [H, NCC, 128]
+    bf16* kd;      // [H, NCC, 128]
+    bf16* p;       // [H, NC, 64, 64]
+    float* decay;  // [H, NC]
+};
+
+struct Layout {
+    size_t u, w, qd, kd, p, decay, total;
+    Layout(int T, int H) {
+        const size_t NC = ((size_t)T + C - 1) / C, NCC = NC * C;
+        size_t at = 0;
+        auto take = [&](size_t bytes) {
+            const size_t off = at;
+            at = (at + bytes + 255) / 256 * 256;
+            return off;
+        };
+        u = take((size_t)H * NCC * D * 2);
+        w = take((size_t)H * NCC * D * 2);
+        qd = take((size_t)H * NCC * D * 2);
+        kd = take((size_t)H * NCC * D * 2);
+        p = take((size_t)H * NC * C * C * 2);
+        decay = take((size_t)H * NC * 4);
+        total = at;
+    }
+};
+
+Work split(float* workspace, int T, int H) {
+    const Layout l(T, H);
+    unsigned char* b = reinterpret_cast<unsigned char*>(workspace);
+    Work ws;
+    ws.u = reinterpret_cast<bf16*>(b + l.u);
+    ws.w = reinterpret_cast<bf16*>(b + l.w);
+    ws.qd = reinterpret_cast<bf16*>(b + l.qd);
+    ws.kd = reinterpret_cast<bf16*>(b + l.kd);
+    ws.p = reinterpret_cast<bf16*>(b + l.p);
+    ws.decay = reinterpret_cast<float*>(b + l.decay);
+    return ws;
+}
+
+// ---------------------------------------------------------------------------------------
+// gdn_prep
+// ---------------------------------------------------------------------------------------
+constexpr int PREP_THREADS = 256;
+// shared memory map (bytes)
+constexpr int P_KF = 0;                          // float [64][LDF]  k normalized, TF32 bits
+constexpr int P_QF = P_KF + C * LDF * 4;         // float [64][LDF]  q normalized * scale, TF32 bits
+constexpr int P_A = P_QF + C * LDF * 4;          // float [64][LDA]  A
+constexpr int P_TB = P_A + C * LDA * 4;          // bf16  [64][LDT]  T * beta
+constexpr int P_SM = P_TB + C * LDT * 2;         // float [6][64]    g/cum, beta, ecum, erem, kinv, spare
+constexpr int PREP_SMEM = P_SM + 6 * C * 4;
+// after the pair products the operand tiles are dead: v and k*exp(cum) reuse them
+constexpr int P_VS = P_KF;                       // bf16 [64][LDH]
+constexpr int P_KE = P_QF;                       // bf16 [64][LDH]
+static_assert(C * LDH * 2 <= C * LDF * 4, "bf16 tile fits over a float tile");
+
+__global__ void __launch_bounds__(PREP_THREADS, 2)
+    gdn_prep(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
+             const float* __restrict__ g, const bf16* __restrict__ beta, Work ws, int T, int H, int HK, float scale) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    float* kf = reinterpret_cast<float*>(smem + P_KF);
+    float* qf = reinterpret_cast<float*>(smem + P_QF);
+    float* A = reinterpret_cast<float*>(smem + P_A);
+    bf16* Tb = reinterpret_cast<bf16*>(smem + P_TB);
+    float* cum = reinterpret_cast<float*>(smem + P_SM);
+    float* bt = cum + C;
+    float* ecum = bt + C;
+    float* erem = ecum + C;
+    float* kinv = erem + C;
+    bf16* vs = reinterpret_cast<bf16*>(smem + P_VS);
+    bf16* ke = reinterpret_cast<bf16*>(smem + P_KE);
+
+    const int c = blockIdx.x, h = blockIdx.y, hk = h / (H / HK);
+    const int NC = gridDim.x, NCC = NC * C;
+    const int r0 = c * C, n = min(C, T - r0);
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+
+    // ---- log-decays: sequential float32 prefix sum, rows past the end have g = beta = 0 ----
+    if (tid < C) {
+        cum[tid] = tid < n ? g[(size_t)(r0 + tid) * H + h] : 0.f;
+        bt[tid] = tid < n ? f32(beta[(size_t)(r0 + tid) * H + h]) : 0.f;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float run = 0.f;
+        for (int i = 0; i < C; i++) {
+            run += cum[i];
+            cum[i] = run;
+        }
+    }
+    __syncthreads();
+    if (tid < C) {
+        const float last = cum[C - 1];
+        ecum[tid] = expf(cum[tid]);
+        erem[tid] = expf(last - cum[tid]);
+        if (tid == 0) ws.decay[(size_t)h * NC + c] = expf(last);
+    }
+    __syncthreads();
+
+    // ---- L2 norms; TF32 operand tiles; qd and kd to the workspace ----
+    {
+        const int sub = tid & 15, rsel = tid >> 4;  // 16 lanes per row, 16 rows per pass
+        const int d0 = sub * 8;
+        bf16* qd_out = ws.qd + ((size_t)h * NCC + r0) * D;
+        bf16* kd_out = ws.kd + ((size_t)h * NCC + r0) * D;
+#pragma unroll
+        for (int pass = 0; pass < 8; pass++) {
+            const bool is_k = pass < 4;
+            const int i = (pass & 3) * 16 + rsel;
+            float x[8];
+            if (i < n) {
+                const bf16* src = (is_k ? k : q) + ((size_t)(r0 + i) * HK + hk) * D + d0;
+                unpack8(ld16(src), x);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; e++) x[e] = 0.f;
+            }
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; e++) ss += x[e] * x[e];
+            ss = warp_sum<16>(ss);
+            float inv = rsqrtf(ss + 1e-6f);
+            float y[8];
+            if (is_k) {
+                if (sub == 0) kinv[i] = inv;
+                const float er = erem[i];
+                float* dst = kf + i * LDF + d0;
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    const float kn = x[e] * inv;
+                    dst[e] = __uint_as_float(to_tf32(kn));
+                    y[e] = kn * er;
+                }
+                st16(kd_out + (size_t)i * D + d0, pack8(y));
+            } else {
+                inv *= scale;
+                const float ec = ecum[i];
+                float* dst = qf + i * LDF + d0;
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    const float qn = x[e] * inv;
+                    dst[e] = __uint_as_float(to_tf32(qn));
+                    y[e] = qn * ec;
+                }
+                st16(qd_out + (size_t)i * D + d0, pack8(y));
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- pair products on TF32 tensor cores: warps 0-3 k.k -> A, warps 4-7 q.k -> P ----
+    {
+        const int mt = warp & 3;
+        const bool is_kk = warp < 4;
+        const float* am = is_kk ? kf : qf;
+        const int gq = lane / 4, tq = lane % 4;
+        const int ntiles = 2 * mt + 2;  // 8-column tiles up to and including the diagonal block
+        float acc[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+        for (int k0 = 0; k0 < D; k0 += 8) {
+            uint32_t a[4];
+            a[0] = __float_as_uint(am[(mt * 16 + gq) * LDF + k0 + tq]);
+            a[1] = __float_as_uint(am[(mt * 16 + gq + 8) * LDF + k0 + tq]);
+            a[2] = __float_as_uint(am[(mt * 16 + gq) * LDF + k0 + tq + 4]);
+            a[3] = __float_as_uint(am[(mt * 16 + gq + 8) * LDF + k0 + tq + 4]);
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++) {
+                if (nt < ntiles) {
+                    const uint32_t b0 = __float_as_uint(kf[(nt * 8 + gq) * LDF + k0 + tq]);
+                    const uint32_t b1 = __float_as_uint(kf[(nt * 8 + gq) * LDF + k0 + tq + 4]);
+                    mma_tf32(acc[nt], a, b0, b1);
+                }
+            }
+        }
+        bf16* p_out = ws.p + ((size_t)h * NC + c) * C * C;
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) {
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const int i = mt * 16 + gq + r * 8;
+                const int j = nt * 8 + 2 * tq;
+                float v0 = 0.f, v1 = 0.f;
+                if (nt < ntiles) {
+                    const float ci = cum[i];
+                    const float e0 = expf(ci - cum[j]), e1 = expf(ci - cum[j + 1]);
+                    if (is_kk) {
+                        v0 = j < i ? bt[i] * acc[nt][2 * r] * e0 : 0.f;
+                        v1 = j + 1 < i ? bt[i] * acc[nt][2 * r + 1] * e1 : 0.f;
+                    } else {
+                        v0 = j <= i ? acc[nt][2 * r] * e0 : 0.f;
+                        v1 = j + 1 <= i ? acc[nt][2 * r + 1] * e1 : 0.f;
+                    }
+                }
+                if (is_kk) {
+                    A[i * LDA + j] = v0;
+                    A[i * LDA + j + 1] = v1;
+                } else {
+                    *reinterpret_cast<uint32_t*>(p_out + i * C + j) = pack2(v0, v1);
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- warps 0-1: T = (I + A)^-1 by forward substitution, one column per thread held in
+    //      registers; warps 2-7 meanwhile stage v and k*exp(cum) over the dead operand tiles ----
+    if (warp < 2) {
+        const int j = tid;
+        float col[C];
+#pragma unroll
+        for (int i = 0; i < C; i++) {
+            float acc = i == j ? 1.f : 0.f;
+            const float* arow = A + i * LDA;
+#pragma unroll
+            for (int m4 = 0; m4 < (i + 3) / 4; m4++) {
+                const float4 a4 = *reinterpret_cast<const float4*>(arow + m4 * 4);
+                if (m4 * 4 + 0 < i) acc -= a4.x * col[m4 * 4 + 0];
+                if (m4 * 4 + 1 < i) acc -= a4.y * col[m4 * 4 + 1];
+                if (m4 * 4 + 2 < i) acc -= a4.z * col[m4 * 4 + 2];
+                if (m4 * 4 + 3 < i) acc -= a4.w * col[m4 * 4 + 3];
+            }
+            col[i] = acc;
+        }
+        const float bj = bt[j];
+#pragma unroll
+        for (int i = 0; i < C; i++) Tb[i * LDT + j] = to_bf16(col[i] * bj);
+    } else {
+        const int t2 = tid - 64;  // 0..191
+        for (int cidx = t2; cidx < C * (D / 8); cidx += PREP_THREADS - 64) {
+            const int i = cidx / (D / 8), d0 = (cidx % (D / 8)) * 8;
+            uint4 vv = make_uint4(0, 0, 0, 0);
+            float y[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) y[e] = 0.f;
+            if (i < n) {
+                vv = ld16(v + ((size_t)(r0 + i) * H + h) * D + d0);
+                float x[8];
+                unpack8(ld16(k + ((size_t)(r0 + i) * HK + hk) * D + d0), x);
+                const float inv = kinv[i], ec = ecum[i];
+#pragma unroll
+                for (int e = 0; e < 8; e++) y[e] = (x[e] * inv) * ec;
+            }
+            st16(vs + i * LDH + d0, vv);
+            st16(ke + i * LDH + d0, pack8(y));
+        }
+    }
+    __syncthreads();
+
+    // ---- u = (T beta) v (warps 0-3), w = (T beta) (k exp(cum)) (warps 4-7), bf16 tensor cores ----
+    {
+        const int mt = warp & 3;
+        const bool is_u = warp < 4;
+        const bf16* bm = is_u ? vs : ke;
+        float acc[16][4];
+#pragma unroll
+        for (int nt = 0; nt < 16; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < C / 16; kk++) {
+            uint32_t a[4];
+            load_a_rm(a, Tb, LDT, mt * 16, kk * 16, lane);
+#pragma unroll
+            for (int np = 0; np < 8; np++) {
+                uint32_t b[4];
+                load_b_kn(b, bm, LDH, kk * 16, np * 16, lane);
+                mma_bf16(acc[2 * np], a, b[0], b[1]);
+                mma_bf16(acc[2 * np + 1], a, b[2], b[3]);
+            }
+        }
+        bf16* dst = (is_u ? ws.u : ws.w) + ((size_t)h * NCC + r0) * D;
+        const int gq = lane / 4, tq = lane % 4;
+#pragma unroll
+        for (int nt = 0; nt < 16; nt++) {
+            const int col = nt * 8 + 2 * tq;
+            *reinterpret_cast<uint32_t*>(dst + (size_t)(mt * 16 + gq) * D + col) = pack2(acc[nt][0], acc[nt][1]);
+            *reinterpret_cast<uint32_t*>(dst + (size_t)(mt * 16 + gq + 8) * D + col) = pack2(acc[nt][2], acc[nt][3]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// gdn_scan
+// ---------------------------------------------------------------------------------------
+constexpr int SCAN_THREADS = 128;
+
+template <int VS>
+struct ScanSmem {
+    static constexpr int LDV = VS + 8;  // bf16 row stride of [*][VS] tiles
+    static constexpr int W = 0;                                // [2][64][LDH]
+    static constexpr int U = W + 2 * C * LDH * 2;              // [2][64][LDV]
+    static constexpr int QD = U + 2 * C * LDV * 2;             // [64][LDH]
+    static constexpr int KD = QD + C * LDH * 2;                // [64][LDH]
+    static constexpr int P = KD + C * LDH * 2;                 // [64][LDT]
+    static constexpr int SB = P + C * LDT * 2;                 // [128][LDV]
+    static constexpr int VN = SB + D * LDV * 2;                // [64][LDV]
+    static constexpr int BYTES = VN + C * LDV * 2;
+};
+
+template <int VS>
+__global__ void __launch_bounds__(SCAN_THREADS, 2)
+    gdn_scan(Work ws, bf16* __restrict__ o, int T, int H, int NC, const float* __restrict__ s_in,
+             float* __restrict__ s_out) {
+    using L = ScanSmem<VS>;
+    constexpr int LDV = L::LDV;
+    constexpr int NT = VS / 8;  // 8-column tiles across the slice
+    extern __shared__ __align__(16) unsigned char smem[];
+    bf16* Wb = reinterpret_cast<bf16*>(smem + L::W);
+    bf16* Ub = reinterpret_cast<bf16*>(smem + L::U);
+    bf16* QDb = reinterpret_cast<bf16*>(smem + L::QD);
+    bf16* KDb = reinterpret_cast<bf16*>(smem + L::KD);
+    bf16* Pb = reinterpret_cast<bf16*>(smem + L::P);
+    bf16* Sb = reinterpret_cast<bf16*>(smem + L::SB);
+    bf16* VNb = reinterpret_cast<bf16*>(smem + L::VN);
+
+    const int h = blockIdx.x, v0 = blockIdx.y * VS;
+    const int NCC = NC * C;
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const int gq = lane / 4, tq = lane % 4;
+
+    const bf16* w_g = ws.w + (size_t)h * NCC * D;
+    const bf16* u_g = ws.u + (size_t)h * NCC * D + v0;
+    const bf16* qd_g = ws.qd + (size_t)h * NCC * D;
+    const bf16* kd_g = ws.kd + (size_t)h * NCC * D;
+    const bf16* p_g = ws.p + (size_t)h * NC * C * C;
+    const float* decay_g = ws.decay + (size_t)h * NC;
+
+    auto load_wu = [&](int c) {
+        bf16* wd = Wb + (c & 1) * C * LDH;
+        bf16* ud = Ub + (c & 1) * C * LDV;
+        const bf16* wsrc = w_g + (size_t)c * C * D;
+        const bf16* usrc = u_g + (size_t)c * C * D;
+        for (int i = tid; i < C * (D / 8); i += SCAN_THREADS) {
+            const int r = i / (D / 8), col = (i % (D / 8)) * 8;
+            cp_async16(wd + r * LDH + col, wsrc + (size_t)r * D + col);
+        }
+        for (int i = tid; i < C * (VS / 8); i += SCAN_THREADS) {
+            const int r = i / (VS / 8), col = (i % (VS / 8)) * 8;
+            cp_async16(ud + r * LDV + col, usrc + (size_t)r * D + col);
+        }
+    };
+    auto load_qpk = [&](int c) {
+        const bf16* qsrc = qd_g + (size_t)c * C * D;
+        const bf16* ksrc = kd_g + (size_t)c * C * D;
+        const bf16* psrc = p_g + (size_t)c * C * C;
+        for (int i = tid; i < C * (D / 8); i += SCAN_THREADS) {
+            const int r = i / (D / 8), col = (i % (D / 8)) * 8;
+            cp_async16(QDb + r * LDH + col, qsrc + (size_t)r * D + col);
+            cp_async16(KDb + r * LDH + col, ksrc + (size_t)r * D + col);
+        }
+        for (int i = tid; i < C * (C / 8); i += SCAN_THREADS) {
+            const int r = i / (C / 8), col = (i % (C / 8)) * 8;
+            cp_async16(Pb + r * LDT + col, psrc + (size_t)r * C + col);
+        }
+    };
+
+    load_wu(0);
+    cp_async_commit();
+    load_qpk(0);
+    cp_async_commit();
+
+    // state rows [32 warp, 32 warp + 32) x VS columns, float32, in mma accumulator layout
+    float S[2][NT][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int kr = warp * 32 + mt * 16 + gq + (e >> 1) * 8;
+                const int vc = v0 + nt * 8 + 2 * tq + (e & 1);
+                S[mt][nt][e] = s_in ? s_in[((size_t)h * D + kr) * D + vc] : 0.f;
+            }
+
+    for (int c = 0; c < NC; c++) {
+        // (1) bf16 copy of the chunk-entry state
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const int kr = warp * 32 + mt * 16 + gq, vc = nt * 8 + 2 * tq;
+                *reinterpret_cast<uint32_t*>(Sb + kr * LDV + vc) = pack2(S[mt][nt][0], S[mt][nt][1]);
+                *reinterpret_cast<uint32_t*>(Sb + (kr + 8) * LDV + vc) = pack2(S[mt][nt][2], S[mt][nt][3]);
+            }
+        cp_async_wait<1>();  // w, u of this chunk have landed
+        __syncthreads();
+        if (c + 1 < NC) load_wu(c + 1);
+        cp_async_commit();
+
+        const bf16* Wc = Wb + (c & 1) * C * LDH;
+        const bf16* Uc = Ub + (c & 1) * C * LDV;
+        const float decay = decay_g[c];
+
+        // (2) v_new = u - w S
+        {
+            float acc[NT][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; kk++) {
+                uint32_t a[4];
+                load_a_rm(a, Wc, LDH, warp * 16, kk * 16, lane);
+#pragma unroll
+                for (int np = 0; np < NT / 2; np++) {
+                    uint32_t b[4];
+                    load_b_kn(b, Sb, LDV, kk * 16, np * 16, lane);
+                    mma_bf16(acc[2 * np], a, b[0], b[1]);
+                    mma_bf16(acc[2 * np + 1], a, b[2], b[3]);
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const int r = warp * 16 + gq, vc = nt * 8 + 2 * tq;
+                const uint32_t u0 = *reinterpret_cast<const uint32_t*>(Uc + r * LDV + vc);
+                const uint32_t u1 = *reinterpret_cast<const uint32_t*>(Uc + (r + 8) * LDV + vc);
+                *reinterpret_cast<uint32_t*>(VNb + r * LDV + vc) =
+                    pack2(__uint_as_float(u0 << 16) - acc[nt][0], __uint_as_float(u0 & 0xffff0000u) - acc[nt][1]);
+                *reinterpret_cast<uint32_t*>(VNb + (r + 8) * LDV + vc) =
+                    pack2(__uint_as_float(u1 << 16) - acc[nt][2], __uint_as_float(u1 & 0xffff0000u) - acc[nt][3]);
+            }
+        }
+        cp_async_wait<1>();  // qd, kd, P of this chunk have landed
+        __syncthreads();
+
+        // (3) o = qd S + P v_new
+        {
+            float acc[NT][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; kk++) {
+                uint32_t a[4];
+                load_a_rm(a, QDb, LDH, warp * 16, kk * 16, lane);
+#pragma unroll
+                for (int np = 0; np < NT / 2; np++) {
+                    uint32_t b[4];
+                    load_b_kn(b, Sb, LDV, kk * 16, np * 16, lane);
+                    mma_bf16(acc[2 * np], a, b[0], b[1]);
+                    mma_bf16(acc[2 * np + 1], a, b[2], b[3]);
+                }
+            }
+#pragma unroll
+            for (int kk = 0; kk < C / 16; kk++) {
+                uint32_t a[4];
+                load_a_rm(a, Pb, LDT, warp * 16, kk * 16, lane);
+#pragma unroll
+                for (int np = 0; np < NT / 2; np++) {
+                    uint32_t b[4];
+                    load_b_kn(b, VNb, LDV, kk * 16, np * 16, lane);
+                    mma_bf16(acc[2 * np], a, b[0], b[1]);
+                    mma_bf16(acc[2 * np + 1], a, b[2], b[3]);
+                }
+            }
+            const int row = c * C + warp * 16 + gq;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const int vc = v0 + nt * 8 + 2 * tq;
+                if (row < T)
+                    *reinterpret_cast<uint32_t*>(o + ((size_t)row * H + h) * D + vc) = pack2(acc[nt][0], acc[nt][1]);
+                if (row + 8 < T)
+                    *reinterpret_cast<uint32_t*>(o + ((size_t)(row + 8) * H + h) * D + vc) =
+                        pack2(acc[nt][2], acc[nt][3]);
+            }
+        }
+
+        // (4) S = decay S + kd^T v_new
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) S[mt][nt][e] *= decay;
+#pragma unroll
+        for (int kk = 0; kk < C / 16; kk++) {
+            uint32_t b[NT / 2][4];
+#pragma unroll
+            for (int np = 0; np < NT / 2; np++) load_b_kn(b[np], VNb, LDV, kk * 16, np * 16, lane);
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++) {
+                uint32_t a[4];
+                load_a_tr(a, KDb, LDH, warp * 32 + mt * 16, kk * 16, lane);
+#pragma unroll
+                for (int np = 0; np < NT / 2; np++) {
+                    mma_bf16(S[mt][2 * np], a, b[np][0], b[np][1]);
+                    mma_bf16(S[mt][2 * np + 1], a, b[np][2], b[np][3]);
+                }
+            }
+        }
+        __syncthreads();  // all reads of this chunk's tiles are done
+        if (c + 1 < NC) load_qpk(c + 1);
+        cp_async_commit();
+    }
+    cp_async_wait<0>();
+
+    if (s_out) {
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int kr = warp * 32 + mt * 16 + gq + (e >> 1) * 8;
+                    const int vc = v0 + nt * 8 + 2 * tq + (e & 1);
+                    s_out[((size_t)h * D + kr) * D + vc] = S[mt][nt][e];
+                }
+    }
+}
+
+template <typename F>
+cudaError_t set_smem_once(F* kernel, int bytes, bool* done_per_device) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 64) return cudaErrorInvalidDevice;
+    if (done_per_device[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) done_per_device[dev] = true;
+    return e;
+}
+
+int gdn_run(const void* q, const void* k, const void* v, const float* g, const void* beta, void* o,
+            float* workspace, int T, int H, int HK, float scale, const void* s_in, void* s_out, void* stream) {
+    if (T < 0 || H <= 0 || HK <= 0 || H % HK != 0) return cudaErrorInvalidValue;
+    const float* si = static_cast<const float*>(s_in);
+    float* so = static_cast<float*>(s_out);
+    cudaStream_t st = as_stream(stream);
+    if (T == 0) {
+        // no tokens: the state passes through unchanged
+        if (so == nullptr) return cudaSuccess;
+        const size_t bytes = (size_t)H * D * D * sizeof(float);
+        return si != nullptr ? cudaMemcpyAsync(so, si, bytes, cudaMemcpyDeviceToDevice, st)
+                             : cudaMemsetAsync(so, 0, bytes, st);
+    }
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(workspace) ||
+        (reinterpret_cast<uintptr_t>(o) & 3))
+        return cudaErrorInvalidValue;
+    static bool prep_done[64] = {}, scan16_done[64] = {}, scan32_done[64] = {};
+    cudaError_t e = set_smem_once(gdn_prep, PREP_SMEM, prep_done);
+    if (e != cudaSuccess) return e;
+    const int NC = (T + C - 1) / C;
+    const Work ws = split(workspace, T, H);
+    gdn_prep<<<dim3(NC, H), PREP_THREADS, PREP_SMEM, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(k),
+                                                          static_cast<const bf16*>(v), g,
+                                                          static_cast<const bf16*>(beta), ws, T, H, HK, scale);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    // Narrow slices when there are few heads, so that the scan still covers the SMs.
+    if (H * (D / 32) >= 96) {
+        e = set_smem_once(gdn_scan<32>, ScanSmem<32>::BYTES, scan32_done);
+        if (e != cudaSuccess) return e;
+        gdn_scan<32><<<dim3(H, D / 32), SCAN_THREADS, ScanSmem<32>::BYTES, st>>>(ws, static_cast<bf16*>(o), T, H, NC,
+                                                                                si, so);
+    } else {
+        e = set_smem_once(gdn_scan<16>, ScanSmem<16>::BYTES, scan16_done);
+        if (e != cudaSuccess) return e;
+        gdn_scan<16><<<dim3(H, D / 16), SCAN_THREADS, ScanSmem<16>::BYTES, st>>>(ws, static_cast<bf16*>(o), T, H, NC,
+                                                                                si, so);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace
+}  // namespace s1
+
+using namespace s1;
+
+extern "C" size_t cs1_gdn_workspace_floats(int T, int H) {
+    if (T < 0 || H < 0) return 0;
+    return (Layout(T, H).total + 3) / 4;
+}
+
+extern "C" int cs1_gdn_prefill(const void* q, const void* k, const void* v, const float* g, const void* beta, void* o,
+                               float* workspace, int T, int H, int HK, float scale, void* stream) {
+    return gdn_run(q, k, v, g, beta, o, workspace, T, H, HK, scale, nullptr, nullptr, stream);
+}
+
+extern "C" int cs1_gdn_prefill_x(const void* q, const void* k, const void* v, const float* g, const void* beta,
+                                 void* o, float* workspace, int T, int H, int HK, float scale, const void* s_in,
+                                 void* s_out, void* stream) {
+    return gdn_run(q, k, v, g, beta, o, workspace, T, H, HK, scale, s_in, s_out, stream);
+}

@@ -1,0 +1,149 @@
+// y [M, N] (rows of ldy) = x [M, K] * w [N, K]^T in bf16 with float32 accumulation: every
+// projection of the decoder (reference entry: src/backends/cuda/qwen3_5/gemm.cu:103-135).
+//
+// Two engines sit behind cs1_gemm and are chosen per handle when it is created:
+//   * the hand-written tcgen05 kernel of gemm_tc5.cu (TMA-fed, TMEM accumulators), used for
+//     every shape it supports (K % 64 == 0, 16-byte aligned rows);
+//   * cuBLASLt with its first heuristic choice, excluding split-K schemes that reduce into
+//     the output in place, exactly as the reference configures it. It serves the shapes the
+//     tcgen05 kernel declines and is the comparison arm of the GEMM benchmark.
+// S1_GEMM=cublaslt in the environment forces the library engine for a whole process.
+#include <cublasLt.h>
+#include <cuda_runtime.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "cs1_ops.h"
+#include "gemm_tc5.h"
+
+namespace {
+
+struct Plan {
+    cublasLtMatmulDesc_t op = nullptr;
+    cublasLtMatrixLayout_t a = nullptr, b = nullptr, c = nullptr;
+    cublasLtMatmulAlgo_t algo{};
+};
+
+using Key = std::tuple<int, int, int, int>;  // M, N, K, ldy
+
+struct Gemm {
+    cublasLtHandle_t handle = nullptr;
+    void* workspace = nullptr;
+    size_t workspace_bytes = 0;
+    bool use_tc5 = true;
+    std::map<Key, Plan> plans;
+    std::mutex lock;
+};
+
+int status(cublasStatus_t s) { return s == CUBLAS_STATUS_SUCCESS ? 0 : CS1_ERR_GEMM_BASE + (int)s; }
+
+void destroy(Plan& p) {
+    if (p.a) cublasLtMatrixLayoutDestroy(p.a);
+    if (p.b) cublasLtMatrixLayoutDestroy(p.b);
+    if (p.c) cublasLtMatrixLayoutDestroy(p.c);
+    if (p.op) cublasLtMatmulDescDestroy(p.op);
+    p = Plan{};
+}
+
+// Row-major y = x w^T is the column-major product y^T [N, M] = (w as [K, N])^T (x as [K, M]).
+int make_plan(Gemm& g, int M, int N, int K, int ldy, Plan& p) {
+    cublasStatus_t s = cublasLtMatmulDescCreate(&p.op, CUBLAS_COMPUTE_32F, CUDA_R_32F);
+    if (s != CUBLAS_STATUS_SUCCESS) return status(s);
+    const cublasOperation_t ta = CUBLAS_OP_T, tb = CUBLAS_OP_N;
+    cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_TRANSA, &ta, sizeof(ta));
+    cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_TRANSB, &tb, sizeof(tb));
+    if ((s = cublasLtMatrixLayoutCreate(&p.a, CUDA_R_16BF, K, N, K)) != CUBLAS_STATUS_SUCCESS) return status(s);
+    if ((s = cublasLtMatrixLayoutCreate(&p.b, CUDA_R_16BF, K, M, K)) != CUBLAS_STATUS_SUCCESS) return status(s);
+    if ((s = cublasLtMatrixLayoutCreate(&p.c, CUDA_R_16BF, N, M, ldy)) != CUBLAS_STATUS_SUCCESS) return status(s);
+    cublasLtMatmulPreference_t pref;
+    if ((s = cublasLtMatmulPreferenceCreate(&pref)) != CUBLAS_STATUS_SUCCESS) return status(s);
+    cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &g.workspace_bytes,
+                                         sizeof(g.workspace_bytes));
+    const uint32_t schemes = CUBLASLT_REDUCTION_SCHEME_MASK & ~CUBLASLT_REDUCTION_SCHEME_INPLACE;
+    cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_REDUCTION_SCHEME_MASK, &schemes, sizeof(schemes));
+    cublasLtMatmulHeuristicResult_t r{};
+    int found = 0;
+    s = cublasLtMatmulAlgoGetHeuristic(g.handle, p.op, p.a, p.b, p.c, p.c, pref, 1, &r, &found);
+    cublasLtMatmulPreferenceDestroy(pref);
+    if (s != CUBLAS_STATUS_SUCCESS) return status(s);
+    if (found == 0 || r.state != CUBLAS_STATUS_SUCCESS) return status(CUBLAS_STATUS_NOT_SUPPORTED);
+    p.algo = r.algo;
+    return 0;
+}
+
+int lt_gemm(Gemm& g, const void* x, const void* w, void* y, int M, int N, int K, int ldy, cudaStream_t st) {
+    Plan* p = nullptr;
+    {
+        std::lock_guard<std::mutex> hold(g.lock);
+        const Key key{M, N, K, ldy};
+        auto it = g.plans.find(key);
+        if (it == g.plans.end()) {
+            Plan fresh;
+            const int rc = make_plan(g, M, N, K, ldy, fresh);
+            if (rc != 0) {
+                destroy(fresh);
+                return rc;
+            }
+            it = g.plans.emplace(key, fresh).first;
+        }
+        p = &it->second;
+    }
+    const float alpha = 1.f, beta = 0.f;
+    return status(cublasLtMatmul(g.handle, p->op, &alpha, w, p->a, x, p->b, &beta, y, p->c, y, p->c, &p->algo,
+                                 g.workspace, g.workspace_bytes, st));
+}
+
+}  // namespace
+
+extern "C" void* cs1_gemm_create(size_t workspace_bytes) {
+    Gemm* g = new Gemm();
+    if (cublasLtCreate(&g->handle) != CUBLAS_STATUS_SUCCESS ||
+        (workspace_bytes > 0 && cudaMalloc(&g->workspace, workspace_bytes) != cudaSuccess)) {
+        if (g->handle) cublasLtDestroy(g->handle);
+        delete g;
+        return nullptr;
+    }
+    g->workspace_bytes = workspace_bytes;
+    const char* engine = getenv("S1_GEMM");
+    g->use_tc5 = engine && strcmp(engine, "tcgen05") == 0;
+    return g;
+}
+
+extern "C" void cs1_gemm_destroy(void* gemm) {
+    Gemm* g = static_cast<Gemm*>(gemm);
+    if (!g) return;
+    for (auto& kv : g->plans) destroy(kv.second);
+    if (g->workspace) cudaFree(g->workspace);
+    cublasLtDestroy(g->handle);
+    delete g;
+}
+
+extern "C" int cs1_gemm(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy,
+                        void* stream) {
+    Gemm* g = static_cast<Gemm*>(gemm);
+    if (!g || M < 0 || N <= 0 || K <= 0 || ldy < N) return cudaErrorInvalidValue;
+    if (M == 0) return cudaSuccess;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (g->use_tc5 && s1_gemm_tc5_supported(x, w, y, M, N, K, ldy)) return s1_gemm_tc5(x, w, y, M, N, K, ldy, st);
+    return lt_gemm(*g, x, w, y, M, N, K, ldy, st);
+}
+
+// Engine-pinned entry points for the GEMM benchmark and the parity tests.
+extern "C" int s1_gemm_cublaslt(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy,
+                                void* stream) {
+    Gemm* g = static_cast<Gemm*>(gemm);
+    if (!g || M < 0 || N <= 0 || K <= 0 || ldy < N) return cudaErrorInvalidValue;
+    if (M == 0) return cudaSuccess;
+    return lt_gemm(*g, x, w, y, M, N, K, ldy, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int s1_gemm_tcgen05(const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream) {
+    if (M < 0 || N <= 0 || K <= 0 || ldy < N) return cudaErrorInvalidValue;
+    if (M == 0) return cudaSuccess;
+    if (!s1_gemm_tc5_supported(x, w, y, M, N, K, ldy)) return CS1_ERR_UNSUPPORTED;
+    return s1_gemm_tc5(x, w, y, M, N, K, ldy, static_cast<cudaStream_t>(stream));
+}

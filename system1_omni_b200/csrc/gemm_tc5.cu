@@ -1,0 +1,359 @@
+// bf16 GEMM y = x w^T for sm_100a on tcgen05: a persistent, warp-specialised kernel.
+//
+//   warp 0    TMA producer: streams 128 x 64 tiles of x and BN x 64 tiles of w (both K-major,
+//             128-byte swizzled) through a ring of shared-memory stages
+//   warp 1    one thread issues tcgen05.mma (128 x BN x 16 per instruction) into one of two
+//             float32 accumulators in tensor memory and commits stage / accumulator barriers
+//   warps 2-5 epilogue: tcgen05.ld the finished accumulator (one row per thread), round to
+//             bf16 and store, while the MMA warp already fills the other accumulator
+//
+// Tiles are assigned round-robin to the resident blocks with all row-blocks of one column
+// block adjacent, so a w tile is fetched from HBM once and then served from L2. Rows past M,
+// columns past N and a K tail are zero-filled by TMA and masked in the epilogue. No load is
+// cluster-multicast. Every barrier wait is bounded; a wait that runs out records a code in
+// a device error word (read with s1_gemm_tc5_status) and the block winds down.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "cs1_ops.h"
+#include "gemm_tc5.h"
+#include "tc5.cuh"
+
+namespace s1 {
+namespace {
+
+constexpr int BM = 128, BK = 64;
+constexpr int GEMM_THREADS = 192;
+
+template <int BN>
+struct Cfg {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (192 * 1024) / STAGE;
+    static constexpr int TMEM_COLS = 2 * BN;  // two accumulators; 128, 256 or 512 columns
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int SMEM = STAGES * STAGE + BAR_BYTES + 1024;  // + slack to align to 1024
+};
+
+__device__ int g_gemm_error = 0;
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
+                    bf16* __restrict__ y, int M, int N, int K, int ldy, int vec_ok) {
+    using namespace tc5;
+    using G = Cfg<BN>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + G::STAGES * G::STAGE);
+    uint64_t* empty = full + G::STAGES;
+    uint64_t* tfull = empty + G::STAGES;
+    uint64_t* tempty = tfull + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < G::STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(&tfull[a], 1);
+            mbar_init(&tempty[a], 4);
+        }
+        *abort_flag = 0;
+        mbar_init_fence();
+        prefetch_tmap(&tma_x);
+        prefetch_tmap(&tma_w);
+    }
+    if (warp == 2) {
+        tmem_alloc(tmem_slot, G::TMEM_COLS);
+        tmem_relinquish();
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN;
+    const int tiles = num_m * num_n, kblocks = (K + BK - 1) / BK;
+    auto fail = [&](int code) {
+        atomicCAS(&g_gemm_error, 0, code);
+        *abort_flag = 1;
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
+                const int m_idx = tile % num_m, n_idx = tile / num_m;
+                for (int kb = 0; kb < kblocks; kb++) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+                        fail(1);
+                        ok = false;
+                        break;
+                    }
+                    unsigned char* dst = smem + stage * G::STAGE;
+                    mbar_expect_tx(&full[stage], G::STAGE);
+                    tma_load_2d(dst, &tma_x, kb * BK, m_idx * BM, &full[stage]);
+                    tma_load_2d(dst + G::A_BYTES, &tma_w, kb * BK, n_idx * BN, &full[stage]);
+                    if (++stage == G::STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(1, BM, BN);
+            uint32_t stage = 0, phase = 0, it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x, it++) {
+                const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+                if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
+                    fail(3);
+                    break;
+                }
+                fence_after_sync();
+                const uint32_t d = tmem_base + acc * BN;
+                for (int kb = 0; kb < kblocks; kb++) {
+                    if (!mbar_wait(&full[stage], phase, abort_flag)) {
+                        fail(2);
+                        ok = false;
+                        break;
+                    }
+                    fence_after_sync();
+                    const uint32_t a_addr = smem_addr(smem + stage * G::STAGE);
+                    const uint32_t b_addr = a_addr + G::A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++) {
+                        mma_bf16_ss(d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
+                                    (kb | k) != 0);
+                    }
+                    mma_commit(&empty[stage]);
+                    if (++stage == G::STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (ok) mma_commit(&tfull[acc]);
+            }
+        }
+        __syncwarp();
+    } else {
+        const int quarter = warp & 3;  // tensor-memory lanes [32 quarter, 32 quarter + 32) belong to this warp
+        uint32_t it = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, it++) {
+            const int m_idx = tile % num_m, n_idx = tile / num_m;
+            const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+            if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) {
+                fail(4);
+                break;
+            }
+            fence_after_sync();
+            const int row = m_idx * BM + quarter * 32 + lane;
+#pragma unroll 1
+            for (int cc = 0; cc < BN / 32; cc++) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + cc * 32, v);
+                tmem_ld_wait();
+                const int col0 = n_idx * BN + cc * 32;
+                if (row < M && col0 < N) {
+                    bf16* dst = y + (size_t)row * ldy + col0;
+                    if (vec_ok && col0 + 32 <= N) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            uint4 o;
+                            o.x = pack2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+                            o.y = pack2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+                            o.z = pack2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+                            o.w = pack2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+                            st16(dst + 8 * j, o);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (col0 + j < N) dst[j] = to_bf16(__uint_as_float(v[j]));
+                    }
+                }
+            }
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty[acc]);
+        }
+    }
+
+    // wind down: after an abort give copies and MMAs in flight time to land before the
+    // shared memory and tensor memory are released
+    if (*abort_flag) __nanosleep(1000000);
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 2) tmem_dealloc(tmem_base, G::TMEM_COLS);
+}
+
+// ---- host side ----
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiled>(p);
+    }();
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    int rows, K, box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && K == o.K && box_rows == o.box_rows;
+    }
+};
+struct MapHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = reinterpret_cast<size_t>(k.ptr);
+        h = h * 1000003u ^ (size_t)k.rows;
+        h = h * 1000003u ^ (size_t)k.K;
+        h = h * 1000003u ^ (size_t)k.box_rows;
+        return h;
+    }
+};
+
+// Tensor map of a row-major [rows, K] bf16 matrix with a [box_rows, 64] box, 128-byte swizzle.
+bool tensor_map(const void* ptr, int rows, int K, int box_rows, CUtensorMap* out) {
+    static std::mutex lock;
+    static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
+    const MapKey key{ptr, rows, K, box_rows};
+    std::lock_guard<std::mutex> hold(lock);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return true;
+    }
+    EncodeTiled fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUtensorMap map;
+    const CUresult r = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return false;
+    if (cache.size() > 8192) cache.clear();
+    cache.emplace(key, map);
+    *out = map;
+    return true;
+}
+
+struct DeviceInfo {
+    int sms = 0;
+    bool smem_set[3] = {false, false, false};
+};
+
+DeviceInfo* device_info(cudaError_t* err) {
+    static DeviceInfo info[64];
+    int dev = 0;
+    *err = cudaGetDevice(&dev);
+    if (*err != cudaSuccess) return nullptr;
+    if (dev >= 64) {
+        *err = cudaErrorInvalidDevice;
+        return nullptr;
+    }
+    if (info[dev].sms == 0) {
+        *err = cudaDeviceGetAttribute(&info[dev].sms, cudaDevAttrMultiProcessorCount, dev);
+        if (*err != cudaSuccess) return nullptr;
+    }
+    return &info[dev];
+}
+
+template <int BN>
+int launch(const void* x, const void* w, void* y, int M, int N, int K, int ldy, DeviceInfo* info, int slot,
+           cudaStream_t st) {
+    using G = Cfg<BN>;
+    if (!info->smem_set[slot]) {
+        const cudaError_t e =
+            cudaFuncSetAttribute(gemm_tc5_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM);
+        if (e != cudaSuccess) return e;
+        info->smem_set[slot] = true;
+    }
+    CUtensorMap mx, mw;
+    if (!tensor_map(x, M, K, BM, &mx) || !tensor_map(w, N, K, BN, &mw)) return CS1_ERR_TENSOR_MAP;
+    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = tiles < info->sms ? tiles : info->sms;
+    const int vec_ok = (ldy % 8 == 0) && aligned16(y);
+    gemm_tc5_kernel<BN><<<grid, GEMM_THREADS, G::SMEM, st>>>(mx, mw, static_cast<bf16*>(y), M, N, K, ldy, vec_ok);
+    return cudaGetLastError();
+}
+
+}  // namespace
+}  // namespace s1
+
+using namespace s1;
+
+bool s1_gemm_tc5_supported(const void* x, const void* w, const void* y, int M, int N, int K, int ldy) {
+    (void)y;
+    (void)ldy;
+    return M > 0 && N > 0 && K >= 64 && K % 8 == 0 && aligned16(x) && aligned16(w);
+}
+
+int s1_gemm_tc5(const void* x, const void* w, void* y, int M, int N, int K, int ldy, cudaStream_t st) {
+    cudaError_t err;
+    DeviceInfo* info = device_info(&err);
+    if (!info) return err;
+    // Pick the widest column block that still gives every SM work; a wider block moves less
+    // shared-memory traffic per flop, a narrower one fills partial waves better.
+    const int num_m = (M + BM - 1) / BM;
+    int best = 256;
+    double best_score = -1.0;
+    const int widths[3] = {256, 128, 64};
+    const double weight[3] = {1.0, 0.85, 0.6};
+    for (int i = 0; i < 3; i++) {
+        const int bn = widths[i];
+        const long tiles = (long)num_m * ((N + bn - 1) / bn);
+        const long waves = (tiles + info->sms - 1) / info->sms;
+        const double useful = (double)N / (double)(((N + bn - 1) / bn) * bn);
+        const double score = weight[i] * useful * (double)tiles / (double)(waves * info->sms);
+        if (score > best_score) {
+            best_score = score;
+            best = bn;
+        }
+    }
+    if (best == 256) return launch<256>(x, w, y, M, N, K, ldy, info, 0, st);
+    if (best == 128) return launch<128>(x, w, y, M, N, K, ldy, info, 1, st);
+    return launch<64>(x, w, y, M, N, K, ldy, info, 2, st);
+}
+
+// Returns the device error word of the current device (0 = no bounded wait ever gave up)
+// after waiting for all queued work, and clears it.
+extern "C" int s1_gemm_tc5_status(int* code) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return e;
+    int v = 0;
+    e = cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int));
+    if (e != cudaSuccess) return e;
+    if (v != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
+    }
+    *code = v;
+    return e;
+}
