@@ -81,10 +81,22 @@ int s1_model_forward_batch(void* model, const int32_t* ids, const int* lengths, 
  * the device as bf16 [nseq, hidden] at *last_rows (owned by the model, valid until the next
  * call); queue-only, no host synchronisation. */
 int s1_model_forward_device(void* model, const int32_t* ids_device, const int* lengths, int nseq, void** last_rows);
-/* A single Gated DeltaNet or attention layer's mixer on caller-provided hidden states is
- * not exposed; parity of single layers goes through layer_out above. */
 int s1_model_sync(void* model);
-/* Device time of each operator family over the last eager forward is not tracked here; use events. */
+
+/* Operator families of the layer loop, for launch counts and per-family device time. */
+enum {
+    S1_FAMILY_GEMM = 0, S1_FAMILY_GDN = 1, S1_FAMILY_ATTENTION = 2, S1_FAMILY_CONV = 3, S1_FAMILY_GATES = 4,
+    S1_FAMILY_NORM = 5, S1_FAMILY_GATED_NORM = 6, S1_FAMILY_SILU_MUL = 7, S1_FAMILY_ATTN_PREP = 8,
+    S1_FAMILY_OTHER = 9, S1_FAMILIES = 10
+};
+/* Profile mode brackets every operator of eager passes with events on the model's stream. */
+int s1_model_profile(void* model, int on);
+/* Waits for the stream, then returns and resets: device milliseconds per family since the
+ * last read (profile mode only; ms nullable), kernels of this library launched per family
+ * (nullable) and launches handed to cuBLASLt (nullable). Graph replays are not counted. */
+int s1_model_profile_read(void* model, float* ms, long long* launches, long long* library_launches);
+/* 1 if cs1_gemm would run this problem on the tcgen05 kernel of this library, 0 if on cuBLASLt. */
+int s1_gemm_engine(void* gemm, const void* x, const void* w, int M, int N, int K);
 
 /* DecisionHead::score (open_jev executor.rs:56-68) and letter_logits (cua_s1 executor.rs:61-78):
  * float64 accumulation on the host rounded to float32, bias added in float32 (bias nullable).

@@ -54,8 +54,19 @@ struct Layer {
     Tensor qkv, o, q_norm, k_norm;                    // full attention
 };
 
+struct ProfRecord {
+    int family;
+    cudaEvent_t start, stop;
+};
+
 struct Model {
     S1Config cfg{};
+    bool profiling = false;
+    std::vector<ProfRecord> prof;
+    std::vector<cudaEvent_t> events;
+    size_t events_used = 0;
+    long long launches[S1_FAMILIES] = {};
+    long long library_launches = 0;
     std::vector<unsigned char> full;
     int device = 0;
     void* arena = nullptr;
@@ -266,8 +277,37 @@ int prepare_scratch(Model* m, size_t t) {
     return 0;
 }
 
+cudaEvent_t next_event(Model* m) {
+    if (m->events_used == m->events.size()) {
+        cudaEvent_t e = nullptr;
+        if (cudaEventCreate(&e) != cudaSuccess) return nullptr;
+        m->events.push_back(e);
+    }
+    return m->events[m->events_used++];
+}
+
+// Every device operator of the layer loop goes through here: counts the kernels it launches
+// per operator family and, in profile mode, brackets it with events on the model's stream.
+template <typename F>
+int op(Model* m, int family, int kernels, F&& call) {
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    cudaStream_t st = static_cast<cudaStream_t>(m->stream);
+    if (m->profiling && (e0 = next_event(m))) cudaEventRecord(e0, st);
+    const int rc = call();
+    if (m->profiling && e0 && (e1 = next_event(m))) {
+        cudaEventRecord(e1, st);
+        m->prof.push_back({family, e0, e1});
+    }
+    m->launches[family] += kernels;
+    return rc;
+}
+#define S1_OP(family, kernels, expr) S1_TRY(op(m, family, kernels, [&] { return (expr); }))
+
 int gemm(Model* m, size_t x, const Tensor& w, size_t y, int rows, int n, int k) {
-    return cs1_gemm(m->gemm, m->s.at(x), m->w(w), m->s.at(y), rows, n, k, n, m->stream);
+    const bool own = s1_gemm_engine(m->gemm, m->s.at(x), m->w(w), rows, n, k) == 1;
+    if (!own) m->library_launches++;
+    return op(m, S1_FAMILY_GEMM, own ? 1 : 0,
+              [&] { return cs1_gemm(m->gemm, m->s.at(x), m->w(w), m->s.at(y), rows, n, k, n, m->stream); });
 }
 
 // The layer loop (model.rs:1119-1338). Pointwise operators and every GEMM run once over the
@@ -285,7 +325,7 @@ int run(Model* m, const int* lengths, int nseq, char* dump) {
     const int hq = c.heads, hk = c.kv_heads, hd = c.head_dim, I = c.intermediate;
     const int gdn_in = m->gdn_in_w(), attn_in = m->attn_in_w(), attn_q = m->attn_q_w(), conv = m->conv_w();
     const float eps = c.eps;
-    S1_TRY(cs1_rms_norm(s.at(s.res), m->w(m->layers[0].input_norm), s.at(s.x), t, h, eps, st));
+    S1_OP(S1_FAMILY_NORM, 1, cs1_rms_norm(s.at(s.res), m->w(m->layers[0].input_norm), s.at(s.x), t, h, eps, st));
     for (size_t li = 0; li < m->layers.size(); li++) {
         const Layer& ly = m->layers[li];
         if (!ly.full) {
@@ -295,24 +335,28 @@ int run(Model* m, const int* lengths, int nseq, char* dump) {
             const size_t a = b + (size_t)hv * BF16;
             size_t off = 0;
             for (int q = 0; q < nseq; q++) {
-                S1_TRY(cs1_gdn_conv(s.at(s.gdn_in + off * gdn_in * BF16), gdn_in, m->w(ly.conv),
-                                    s.at(s.lq + off * kd * BF16), s.at(s.lk + off * kd * BF16),
-                                    s.at(s.lv + off * vd * BF16), lengths[q], kd, vd, st));
+                S1_OP(S1_FAMILY_CONV, 1,
+                      cs1_gdn_conv(s.at(s.gdn_in + off * gdn_in * BF16), gdn_in, m->w(ly.conv),
+                                   s.at(s.lq + off * kd * BF16), s.at(s.lk + off * kd * BF16),
+                                   s.at(s.lv + off * vd * BF16), lengths[q], kd, vd, st));
                 off += lengths[q];
             }
-            S1_TRY(cs1_gdn_gates(s.at(b), s.at(a), gdn_in, m->w(ly.a_log), m->w(ly.dt_bias), s.at(s.beta),
-                                 reinterpret_cast<float*>(s.at(s.g)), t, hv, st));
+            S1_OP(S1_FAMILY_GATES, 1,
+                  cs1_gdn_gates(s.at(b), s.at(a), gdn_in, m->w(ly.a_log), m->w(ly.dt_bias), s.at(s.beta),
+                                reinterpret_cast<float*>(s.at(s.g)), t, hv, st));
             off = 0;
             for (int q = 0; q < nseq; q++) {
-                S1_TRY(cs1_gdn_prefill(s.at(s.lq + off * kd * BF16), s.at(s.lk + off * kd * BF16),
-                                       s.at(s.lv + off * vd * BF16),
-                                       reinterpret_cast<const float*>(s.at(s.g + off * hv * F32)),
-                                       s.at(s.beta + off * hv * BF16), s.at(s.lo + off * vd * BF16),
-                                       reinterpret_cast<float*>(s.at(s.workspace)), lengths[q], hv, c.lin_k_heads,
-                                       1.0f / sqrtf(128.0f), st));
+                S1_OP(S1_FAMILY_GDN, 2,
+                      cs1_gdn_prefill(s.at(s.lq + off * kd * BF16), s.at(s.lk + off * kd * BF16),
+                                      s.at(s.lv + off * vd * BF16),
+                                      reinterpret_cast<const float*>(s.at(s.g + off * hv * F32)),
+                                      s.at(s.beta + off * hv * BF16), s.at(s.lo + off * vd * BF16),
+                                      reinterpret_cast<float*>(s.at(s.workspace)), lengths[q], hv, c.lin_k_heads,
+                                      1.0f / sqrtf(128.0f), st));
                 off += lengths[q];
             }
-            S1_TRY(cs1_gated_rms_norm(s.at(s.lo), s.at(z), gdn_in, m->w(ly.norm), s.at(s.ln), t, hv, 128, eps, st));
+            S1_OP(S1_FAMILY_GATED_NORM, 1,
+                  cs1_gated_rms_norm(s.at(s.lo), s.at(z), gdn_in, m->w(ly.norm), s.at(s.ln), t, hv, 128, eps, st));
             S1_TRY(gemm(m, s.ln, ly.out, s.delta, t, h, vd));
         } else {
             S1_TRY(gemm(m, s.x, ly.qkv, s.attn_in, t, attn_in, h));
@@ -321,25 +365,28 @@ int run(Model* m, const int* lengths, int nseq, char* dump) {
             size_t off = 0;
             for (int q = 0; q < nseq; q++) {
                 // the unshifted table base restarts positions at 0 for every sequence (model.rs:1244-1251)
-                S1_TRY(cs1_attn_prep(s.at(s.attn_in + off * attn_in * BF16), s.at(k + off * attn_in * BF16), attn_in,
-                                     m->w(ly.q_norm), m->w(ly.k_norm), s.at(s.cos), s.at(s.sin),
-                                     s.at(s.aq + off * hq * hd * BF16), s.at(s.agate + off * hq * hd * BF16),
-                                     s.at(s.ak + off * hk * hd * BF16), lengths[q], hq, hk, hd, c.rotary_half, eps,
-                                     st));
-                S1_TRY(cs1_attention_gated(s.at(s.aq + off * hq * hd * BF16), s.at(s.ak + off * hk * hd * BF16),
-                                           s.at(v + off * attn_in * BF16), attn_in,
-                                           s.at(s.agate + off * hq * hd * BF16), s.at(s.ao + off * hq * hd * BF16),
-                                           lengths[q], hq, hk, hd, 1.0f / sqrtf((float)hd), st));
+                S1_OP(S1_FAMILY_ATTN_PREP, 1,
+                      cs1_attn_prep(s.at(s.attn_in + off * attn_in * BF16), s.at(k + off * attn_in * BF16), attn_in,
+                                    m->w(ly.q_norm), m->w(ly.k_norm), s.at(s.cos), s.at(s.sin),
+                                    s.at(s.aq + off * hq * hd * BF16), s.at(s.agate + off * hq * hd * BF16),
+                                    s.at(s.ak + off * hk * hd * BF16), lengths[q], hq, hk, hd, c.rotary_half, eps,
+                                    st));
+                S1_OP(S1_FAMILY_ATTENTION, 1,
+                      cs1_attention_gated(s.at(s.aq + off * hq * hd * BF16), s.at(s.ak + off * hk * hd * BF16),
+                                          s.at(v + off * attn_in * BF16), attn_in,
+                                          s.at(s.agate + off * hq * hd * BF16), s.at(s.ao + off * hq * hd * BF16),
+                                          lengths[q], hq, hk, hd, 1.0f / sqrtf((float)hd), st));
                 off += lengths[q];
             }
             S1_TRY(gemm(m, s.ao, ly.o, s.delta, t, h, hq * hd));
         }
-        S1_TRY(cs1_add_rms_norm(s.at(s.res), s.at(s.delta), m->w(ly.post_norm), s.at(s.x), t, h, eps, st));
+        S1_OP(S1_FAMILY_NORM, 1,
+              cs1_add_rms_norm(s.at(s.res), s.at(s.delta), m->w(ly.post_norm), s.at(s.x), t, h, eps, st));
         S1_TRY(gemm(m, s.x, ly.gate_up, s.gate_up, t, 2 * I, h));
-        S1_TRY(cs1_silu_mul(s.at(s.gate_up), 2 * I, s.at(s.act), t, I, st));
+        S1_OP(S1_FAMILY_SILU_MUL, 1, cs1_silu_mul(s.at(s.gate_up), 2 * I, s.at(s.act), t, I, st));
         S1_TRY(gemm(m, s.act, ly.down, s.delta, t, h, I));
         const Tensor& next = li + 1 < m->layers.size() ? m->layers[li + 1].input_norm : m->final_norm;
-        S1_TRY(cs1_add_rms_norm(s.at(s.res), s.at(s.delta), m->w(next), s.at(s.x), t, h, eps, st));
+        S1_OP(S1_FAMILY_NORM, 1, cs1_add_rms_norm(s.at(s.res), s.at(s.delta), m->w(next), s.at(s.x), t, h, eps, st));
         if (dump) S1_TRY(cs1_download(dump + li * (size_t)t * h * BF16, s.at(s.res), (size_t)t * h * BF16, st));
     }
     return 0;
@@ -448,6 +495,7 @@ void s1_model_destroy(void* model) {
     if (m->arena) cs1_free(m->arena);
     if (m->ends_host) cudaFreeHost(m->ends_host);
     if (m->last_host) cudaFreeHost(m->last_host);
+    for (cudaEvent_t e : m->events) cudaEventDestroy(e);
     if (m->stream) cs1_stream_destroy(m->stream);
     delete m;
 }
@@ -537,14 +585,16 @@ int s1_model_forward_batch(void* model, const int32_t* ids, const int* lengths, 
     const int h = m->cfg.hidden;
     S1_TRY(cs1_upload(s.at(s.ids), ids, (size_t)total * 4, m->stream));
     S1_TRY(stage_ends(m, lengths, nseq));
-    S1_TRY(cs1_embed(reinterpret_cast<const int32_t*>(s.at(s.ids)), m->w(m->embed), s.at(s.res), (int)total, h,
-                     m->stream));
+    S1_OP(S1_FAMILY_OTHER, 1,
+          cs1_embed(reinterpret_cast<const int32_t*>(s.at(s.ids)), m->w(m->embed), s.at(s.res), (int)total, h,
+                    m->stream));
     if (layer_out)
         S1_TRY(run(m, lengths, nseq, static_cast<char*>(layer_out)));
     else
         S1_TRY(run_or_replay(m, lengths, nseq));
-    S1_TRY(s1::gather_rows(s.at(s.x), reinterpret_cast<const int*>(s.at(s.ends)), s.at(s.last), nseq, h,
-                           static_cast<cudaStream_t>(m->stream)));
+    S1_OP(S1_FAMILY_OTHER, 1,
+          s1::gather_rows(s.at(s.x), reinterpret_cast<const int*>(s.at(s.ends)), s.at(s.last), nseq, h,
+                          static_cast<cudaStream_t>(m->stream)));
     const size_t bytes = (size_t)nseq * h * BF16;
     if (m->last_host_bytes < bytes) {
         if (m->last_host) cudaFreeHost(m->last_host);
@@ -568,11 +618,40 @@ int s1_model_forward_device(void* model, const int32_t* ids_device, const int* l
     const Scratch& s = m->s;
     const int h = m->cfg.hidden;
     S1_TRY(stage_ends(m, lengths, nseq));
-    S1_TRY(cs1_embed(ids_device, m->w(m->embed), s.at(s.res), (int)total, h, m->stream));
+    S1_OP(S1_FAMILY_OTHER, 1, cs1_embed(ids_device, m->w(m->embed), s.at(s.res), (int)total, h, m->stream));
     S1_TRY(run_or_replay(m, lengths, nseq));
-    S1_TRY(s1::gather_rows(s.at(s.x), reinterpret_cast<const int*>(s.at(s.ends)), s.at(s.last), nseq, h,
-                           static_cast<cudaStream_t>(m->stream)));
+    S1_OP(S1_FAMILY_OTHER, 1,
+          s1::gather_rows(s.at(s.x), reinterpret_cast<const int*>(s.at(s.ends)), s.at(s.last), nseq, h,
+                          static_cast<cudaStream_t>(m->stream)));
     if (last_rows) *last_rows = s.at(s.last);
+    return 0;
+}
+
+int s1_model_profile(void* model, int on) {
+    Model* m = static_cast<Model*>(model);
+    if (!m) return S1_ERR_ARGUMENT;
+    m->profiling = on != 0;
+    return 0;
+}
+
+int s1_model_profile_read(void* model, float* ms, long long* launches, long long* library_launches) {
+    Model* m = static_cast<Model*>(model);
+    if (!m) return S1_ERR_ARGUMENT;
+    S1_TRY(cs1_set_device(m->device));
+    S1_TRY(cs1_stream_sync(m->stream));
+    if (ms) {
+        for (int f = 0; f < S1_FAMILIES; f++) ms[f] = 0.f;
+        for (const ProfRecord& r : m->prof) {
+            float t = 0.f;
+            if (cudaEventElapsedTime(&t, r.start, r.stop) == cudaSuccess) ms[r.family] += t;
+        }
+    }
+    if (launches) memcpy(launches, m->launches, sizeof(m->launches));
+    if (library_launches) *library_launches = m->library_launches;
+    m->prof.clear();
+    m->events_used = 0;
+    memset(m->launches, 0, sizeof(m->launches));
+    m->library_launches = 0;
     return 0;
 }
 

@@ -19,6 +19,7 @@
 
 #include "cs1_ops.h"
 #include "gemm_tc5.h"
+#include "s1_executor.h"
 
 namespace {
 
@@ -130,6 +131,11 @@ extern "C" int cs1_gemm(void* gemm, const void* x, const void* w, void* y, int M
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (g->use_tc5 && s1_gemm_tc5_supported(x, w, y, M, N, K, ldy)) return s1_gemm_tc5(x, w, y, M, N, K, ldy, st);
     return lt_gemm(*g, x, w, y, M, N, K, ldy, st);
+}
+
+extern "C" int s1_gemm_engine(void* gemm, const void* x, const void* w, int M, int N, int K) {
+    Gemm* g = static_cast<Gemm*>(gemm);
+    return g && g->use_tc5 && s1_gemm_tc5_supported(x, w, nullptr, M, N, K, N) ? 1 : 0;
 }
 
 // Engine-pinned entry points for the GEMM benchmark and the parity tests.

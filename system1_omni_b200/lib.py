@@ -101,6 +101,9 @@ SIGNATURES = {
     "s1_model_forward_batch": (i32, [vp, vp, vp, i32, vp, vp]),
     "s1_model_forward_device": (i32, [vp, vp, vp, i32, vpp]),
     "s1_model_sync": (i32, [vp]),
+    "s1_model_profile": (i32, [vp, i32]),
+    "s1_model_profile_read": (i32, [vp, vp, vp, vp]),
+    "s1_gemm_engine": (i32, [vp, vp, vp, i32, i32, i32]),
     "s1_head_logits": (i32, [vp, vp, vp, i32, i32, vp]),
     "s1_decide": (i32, [vp, i32, f64, vp]),
     "s1_batch_ranges": (i32, [vp, i32, vp]),

@@ -393,7 +393,7 @@ def test_gated_delta_rule_matches_recurrent_reference(cs1, stream, t, h, hk, dec
     assert worst <= 2e-2 * scale, (worst, scale)
     # and close to the chunked float32 restatement with the same rounding points
     chunked = f32(O.gdn_chunked(q, k, v, g, beta, t, h, hk, 128 ** -0.5)).astype(np.float64)
-    assert np.abs(got - chunked).max() <= 4e-3 * scale + 1e-38
+    assert np.abs(got - chunked).max() <= 4 * 2.0 ** -8 * scale + 1e-38      # a few bf16 steps of the largest value
 
 
 @pytest.mark.parametrize("h,hk", [(16, 16), (32, 16), (48, 16), (24, 8)])
