@@ -110,7 +110,7 @@ extern "C" void* cs1_gemm_create(size_t workspace_bytes) {
     }
     g->workspace_bytes = workspace_bytes;
     const char* engine = getenv("S1_GEMM");
-    g->use_tc5 = engine && strcmp(engine, "tcgen05") == 0;
+    g->use_tc5 = !(engine && strcmp(engine, "cublaslt") == 0);
     return g;
 }
 

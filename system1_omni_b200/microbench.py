@@ -1,0 +1,250 @@
+"""Per-operator device timings through the C ABI, against each operator's roofline.
+
+    python -m system1_omni_b200.microbench --what elementwise|gemm|gdn|attention|all [--out file.jsonl]
+
+elementwise  the sweep of BASELINE.json's fifth config: bf16 N(0,1)-like activations with
+             tokens in {1k, 4k, 16k, 64k} x channels in {2048, 4096, 8192} for causal
+             conv1d(k=4)+SiLU, softplus/exp decay gates, gated RMSNorm, residual add + RMSNorm,
+             RMSNorm and SiLU*up; achieved GB/s = algorithmic bytes / device time.
+gemm         the projection shapes of the 4B-, 9B- and 27B-shaped decoders at 1024 tokens
+             (and 128 / 4096), tcgen05 kernel and cuBLASLt side by side; TFLOP/s.
+gdn          the chunked gated delta rule (both kernels of cs1_gdn_prefill) at the reference's
+             published shapes (H=48, HK=16, T in {107, 936, 3399}) and the model shapes; microseconds.
+attention    causal GQA flash attention at head dims 128 and 256.
+
+Calls rotate over enough copies of their buffers to exceed the 126 MB L2, so a timing is
+not flattered by a warm cache; every figure is the mean of `--iters` launches between two
+events on one stream after `--warmup` launches.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import sys
+
+import numpy as np
+
+from . import lib as L
+
+L2_BYTES = 126 << 20
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return p.get("hbm_gbs", 6543.7), p.get("bf16_tflops", 1646.8), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class Bench:
+    def __init__(self, warmup, iters):
+        self.lib = L.load()
+        L.set_device(0)
+        self.stream = L.Stream()
+        self.warmup, self.iters = warmup, iters
+        self.e0, self.e1 = L.Event(), L.Event()
+        self.rng = np.random.default_rng(0)
+        self.gemm_shape = None
+
+    def bf16(self, n, scale=1.0):
+        """n bf16 values ~ N(0, scale) as a device buffer (bit patterns made on the host)."""
+        a = (self.rng.standard_normal(min(n, 1 << 22), dtype=np.float32) * np.float32(scale))
+        bits = (a.view(np.uint32) >> 16).astype(np.uint16)
+        bits = np.resize(bits, n)
+        return L.to_device(bits, self.stream)
+
+    def copies(self, bytes_per_call):
+        return int(min(64, max(1, -(-2 * L2_BYTES // max(bytes_per_call, 1)))))
+
+    def time(self, call, ncopies):
+        """call(i) launches on copy i; returns mean microseconds per launch."""
+        st = self.stream.handle
+        for i in range(self.warmup):
+            L.check(call(i % ncopies), "warmup")
+        self.stream.sync()
+        self.e0.record(st)
+        for i in range(self.iters):
+            code = call(i % ncopies)
+        self.e1.record(st)
+        self.stream.sync()
+        L.check(code, "timed call")
+        return self.e0.elapsed_ms(self.e1) * 1e3 / self.iters
+
+
+def elementwise(b, out):
+    lib, st = b.lib, b.stream.handle
+    hbm, _, src = peaks()
+    for tokens in (1024, 4096, 16384, 65536):
+        for ch in (2048, 4096, 8192):
+            H = ch // 128
+            cases = []
+            # conv: ch channels in total, q|k|v = ch/4 | ch/4 | ch/2
+            kd, vd = ch // 4, ch // 2
+            nbytes = 4 * tokens * ch
+            n = b.copies(nbytes)
+            xs = [b.bf16(tokens * ch) for _ in range(n)]
+            w = b.bf16(ch * 4, 0.5)
+            qs = [(L.DeviceBuffer(tokens * kd * 2), L.DeviceBuffer(tokens * kd * 2), L.DeviceBuffer(tokens * vd * 2))
+                  for _ in range(n)]
+            cases.append(("gdn_conv_silu", nbytes + 8 * ch, n, lambda i: lib.cs1_gdn_conv(
+                xs[i].at(), ch, w.at(), qs[i][0].at(), qs[i][1].at(), qs[i][2].at(), tokens, kd, vd, st)))
+            # gates: H = ch / 128 heads
+            gb = 10 * tokens * H
+            ng = b.copies(gb)
+            ba = [b.bf16(tokens * 2 * H) for _ in range(ng)]
+            al, dt = b.bf16(H), b.bf16(H, 0.1)
+            go = [(L.DeviceBuffer(tokens * H * 2), L.DeviceBuffer(tokens * H * 4)) for _ in range(ng)]
+            cases.append(("gdn_gates", gb, ng, lambda i: lib.cs1_gdn_gates(
+                ba[i].at(), ba[i].at(H * 2), 2 * H, al.at(), dt.at(), go[i][0].at(), go[i][1].at(), tokens, H, st)))
+            # gated RMSNorm: value_dim = ch
+            nb = 6 * tokens * ch
+            nn = b.copies(nb)
+            gx = [b.bf16(tokens * ch) for _ in range(nn)]
+            gz = [b.bf16(tokens * ch) for _ in range(nn)]
+            gw = b.bf16(128, 0.1)
+            gy = [L.DeviceBuffer(tokens * ch * 2) for _ in range(nn)]
+            cases.append(("gated_rms_norm", nb, nn, lambda i: lib.cs1_gated_rms_norm(
+                gx[i].at(), gz[i].at(), ch, gw.at(), gy[i].at(), tokens, H, 128, 1e-6, st)))
+            # add + RMSNorm: hidden = ch
+            ab = 8 * tokens * ch
+            na = b.copies(ab)
+            res = [b.bf16(tokens * ch) for _ in range(na)]
+            dl = [b.bf16(tokens * ch, 0.01) for _ in range(na)]
+            nw = b.bf16(ch, 0.1)
+            no = [L.DeviceBuffer(tokens * ch * 2) for _ in range(na)]
+            cases.append(("add_rms_norm", ab, na, lambda i: lib.cs1_add_rms_norm(
+                res[i].at(), dl[i].at(), nw.at(), no[i].at(), tokens, ch, 1e-6, st)))
+            cases.append(("rms_norm", 4 * tokens * ch, na, lambda i: lib.cs1_rms_norm(
+                res[i].at(), nw.at(), no[i].at(), tokens, ch, 1e-6, st)))
+            # SiLU * up: intermediate = ch
+            sb = 6 * tokens * ch
+            ns = b.copies(sb)
+            gu = [b.bf16(tokens * 2 * ch) for _ in range(ns)]
+            so = [L.DeviceBuffer(tokens * ch * 2) for _ in range(ns)]
+            cases.append(("silu_mul", sb, ns, lambda i: lib.cs1_silu_mul(gu[i].at(), 2 * ch, so[i].at(), tokens, ch, st)))
+            for name, nbytes, ncopies, call in cases:
+                us = b.time(call, ncopies)
+                gbs = nbytes / us / 1e3
+                out({"op": name, "tokens": tokens, "channels": ch, "us": us, "algorithmic_bytes": nbytes,
+                     "GB/s": gbs, "frac_of_hbm": gbs / hbm, "hbm_peak_GB/s": hbm, "peak_source": src,
+                     "frac_of_8TB/s": gbs / 8000.0, "buffer_copies": ncopies})
+            del xs, qs, ba, go, gx, gz, gy, res, dl, no, gu, so
+
+
+MODEL_SHAPES = {
+    # name: (hidden, intermediate, gdn_in, value_dim, attn_in, attn_out)
+    "4B": (2560, 9728, 12352, 4096, 5120, 2048),
+    "9B": (4096, 12288, 12352, 4096, 10240, 4096),
+    "27B": (5120, 17408, 16480, 6144, 7168, 3072),
+}
+
+
+def gemm(b, out):
+    lib, st = b.lib, b.stream.handle
+    _, tf, src = peaks()
+    handle = lib.cs1_gemm_create(32 << 20)
+    shapes = []
+    for name, (h, I, gdn_in, vd, attn_in, attn_out) in MODEL_SHAPES.items():
+        for M in ((128, 1024, 4096) if name == "4B" else (1024,)):
+            shapes += [(name, "gdn_in_proj", M, gdn_in, h), (name, "gdn_out_proj", M, h, vd),
+                       (name, "attn_qkv", M, attn_in, h), (name, "attn_o", M, h, attn_out),
+                       (name, "mlp_gate_up", M, 2 * I, h), (name, "mlp_down", M, h, I)]
+    shapes.append(("square", "8192^3", 8192, 8192, 8192))
+    if b.gemm_shape:
+        shapes = [("custom", "custom", *b.gemm_shape)]
+    for model, proj, M, N, K in shapes:
+        wbytes = N * K * 2
+        n = b.copies(wbytes + M * K * 2 + M * N * 2)
+        n = min(n, 8)
+        ws = [b.bf16(N * K, 0.02) for _ in range(n)]
+        x = b.bf16(M * K)
+        y = L.DeviceBuffer(M * N * 2)
+        row = {"model": model, "proj": proj, "M": M, "N": N, "K": K, "flops": 2.0 * M * N * K, "weight_copies": n}
+        for engine, call in (("tcgen05", lambda i: lib.s1_gemm_tcgen05(x.at(), ws[i].at(), y.at(), M, N, K, N, st)),
+                             ("cublaslt", lambda i: lib.s1_gemm_cublaslt(handle, x.at(), ws[i].at(), y.at(), M, N, K,
+                                                                         N, st))):
+            us = b.time(call, n)
+            row[engine + "_us"] = us
+            row[engine + "_TFLOP/s"] = row["flops"] / us / 1e6
+        row["tcgen05_frac_of_peak"] = row["tcgen05_TFLOP/s"] / tf
+        row["tcgen05_vs_cublaslt"] = row["cublaslt_us"] / row["tcgen05_us"]
+        row["peak_TFLOP/s"] = tf
+        row["peak_source"] = src
+        out(row)
+        del ws, x, y
+    code = L.gemm_status()
+    if code:
+        raise RuntimeError(f"tcgen05 GEMM recorded a bounded-wait failure: {code}")
+    lib.cs1_gemm_destroy(handle)
+
+
+def gdn(b, out):
+    lib, st = b.lib, b.stream.handle
+    shapes = [(48, 16, 107), (48, 16, 936), (48, 16, 3399), (16, 16, 2048), (32, 16, 1024), (32, 16, 4096),
+              (48, 16, 1024), (48, 16, 16384)]
+    if b.gdn_shape:
+        shapes = [tuple(b.gdn_shape)]
+    for H, HK, T in shapes:
+        q, k = b.bf16(T * HK * 128), b.bf16(T * HK * 128)
+        v = b.bf16(T * H * 128)
+        g = L.to_device((-np.abs(b.rng.standard_normal(T * H).astype(np.float32)) * 0.3), b.stream)
+        beta = b.bf16(T * H, 0.2)
+        o = L.DeviceBuffer(T * H * 128 * 2)
+        ws = L.DeviceBuffer(lib.cs1_gdn_workspace_floats(T, H) * 4)
+        us = b.time(lambda i: lib.cs1_gdn_prefill(q.at(), k.at(), v.at(), g.at(), beta.at(), o.at(), ws.at(), T, H,
+                                                  HK, 128 ** -0.5, st), 1)
+        chunks = -(-T // 64)
+        flops = chunks * H * (2 * 64 * 64 * (3 * 128 + 2 * 128) + 6 * 64 * 128 * 128)
+        io = T * (4 * HK * 128 + 4 * H * 128 + 6 * H)
+        out({"op": "gdn_prefill", "H": H, "HK": HK, "T": T, "us": us, "tokens_per_s": T / us * 1e6,
+             "dense_TFLOP/s": flops / us / 1e6, "algorithmic_GB/s": io / us / 1e3,
+             "workspace_MiB": lib.cs1_gdn_workspace_floats(T, H) * 4 / 2 ** 20})
+
+
+def attention(b, out):
+    lib, st = b.lib, b.stream.handle
+    for dh, hq, hk in [(128, 16, 4), (128, 24, 4), (256, 16, 4), (256, 24, 4)]:
+        for T in (1024, 4096, 16384):
+            q, k, v = b.bf16(T * hq * dh), b.bf16(T * hk * dh), b.bf16(T * hk * dh)
+            gate = b.bf16(T * hq * dh)
+            o = L.DeviceBuffer(T * hq * dh * 2)
+            us = b.time(lambda i: lib.cs1_attention_gated(q.at(), k.at(), v.at(), hk * dh, gate.at(), o.at(), T, hq,
+                                                          hk, dh, dh ** -0.5, st), 1)
+            flops = 4.0 * hq * dh * T * (T + 1) / 2
+            out({"op": "attention_gated", "Dh": dh, "Hq": hq, "Hk": hk, "T": T, "us": us,
+                 "causal_TFLOP/s": flops / us / 1e6})
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--what", default="all", choices=["elementwise", "gemm", "gdn", "attention", "all"])
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--iters", type=int, default=30)
+    ap.add_argument("--out", default=None)
+    ap.add_argument("--gemm-shape", type=int, nargs=3, metavar=("M", "N", "K"), default=None,
+                    help="time this one GEMM problem only (for a profiler capture)")
+    ap.add_argument("--gdn-shape", type=int, nargs=3, metavar=("H", "HK", "T"), default=None,
+                    help="time this one delta-rule problem only (for a profiler capture)")
+    args = ap.parse_args()
+    b = Bench(args.warmup, args.iters)
+    b.gemm_shape = args.gemm_shape
+    b.gdn_shape = args.gdn_shape
+    sink = open(args.out, "w") if args.out else None
+
+    def out(row):
+        line = json.dumps({k: (round(v, 4) if isinstance(v, float) else v) for k, v in row.items()})
+        print(line, flush=True)
+        if sink:
+            sink.write(line + "\n")
+
+    for name, fn in (("elementwise", elementwise), ("gemm", gemm), ("gdn", gdn), ("attention", attention)):
+        if args.what in (name, "all"):
+            fn(b, out)
+    if sink:
+        sink.close()
+
+
+if __name__ == "__main__":
+    sys.exit(main())

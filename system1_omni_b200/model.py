@@ -216,6 +216,16 @@ class Model:
         L.check(code, "forward_batch")
         return (last, layers) if want_layers else last
 
+    def forward_flat(self, ids, lengths):
+        """The same pass on an int32 array used in place (e.g. a view of pinned host memory)."""
+        assert ids.dtype == np.int32 and ids.flags["C_CONTIGUOUS"]
+        lengths = np.ascontiguousarray(lengths, dtype=np.int32)
+        last = np.zeros((lengths.size, self.cfg.hidden), np.float32)
+        L.check(L.load().s1_model_forward_batch(self.handle, ids.ctypes.data_as(C.c_void_p),
+                                                lengths.ctypes.data_as(C.c_void_p), lengths.size,
+                                                last.ctypes.data_as(C.c_void_p), None), "forward_batch")
+        return last
+
     def forward(self, ids):
         return self.forward_batch([ids])[0]
 
