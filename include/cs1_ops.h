@@ -25,6 +25,7 @@
 #define CS1_ERR_UNSUPPORTED 2000    /* entry point present for the loader, operation not built */
 #define CS1_ERR_DEVICE_CHECK 2001   /* a device-side bounded wait gave up */
 #define CS1_ERR_TENSOR_MAP 2002     /* a TMA tensor map could not be encoded */
+#define CS1_ERR_STATIC_SCRATCH 2003 /* the window does not fit the fixed scratch of cs1_gdn_prefill_static */
 
 #ifdef __cplusplus
 extern "C" {
@@ -88,6 +89,20 @@ int cs1_gdn_prefill(const void* q, const void* k, const void* v, const float* g,
 int cs1_gdn_prefill_x(const void* q, const void* k, const void* v, const float* g, const void* beta, void* o,
                       float* workspace, int T, int H, int HK, float scale, const void* s_in, void* s_out,
                       void* stream);
+
+/* No counterpart in the reference. cs1_gdn_prefill for callers that cannot provide the
+ * workspace because they cannot allocate device memory (a worker confined to buffers it was
+ * handed, a plugin inside a process whose memory pool it does not own, a path where
+ * cudaMalloc is forbidden because it synchronises the device): the workspace is a fixed
+ * CS1_GDN_STATIC_SCRATCH_BYTES array inside the library, one per GPU, held until the library
+ * is unloaded. The call allocates nothing. It fails with CS1_ERR_STATIC_SCRATCH when
+ * cs1_gdn_workspace_floats(T, H) * 4 exceeds that size. All calls on a GPU share the array:
+ * calls that can overlap on the GPU race; the array keeps the last call's contents, and
+ * none of it has to be cleared. The first call on each GPU resolves the array's device
+ * address and should be made before any stream capture. */
+#define CS1_GDN_STATIC_SCRATCH_BYTES (64u << 20)
+int cs1_gdn_prefill_static(const void* q, const void* k, const void* v, const float* g, const void* beta, void* o,
+                           int T, int H, int HK, float scale, void* stream);
 
 /* ops.h:89-94: per-head RMSNorm(1+w) of q and k and rotary embedding on the first 2*half
  * dims; qg [T, Hq, 2*Dh] (query | gate per head) and kr [T, Hk, Dh] in rows of ld. The

@@ -18,6 +18,8 @@
 // (TF32 operands), inverse and state; bf16 qd, kd, P, T*beta, k*exp(cum), u, w, v_new and
 // the chunk-entry state. The state is float32 across calls (s_in / s_out), so a window that
 // starts on a multiple of 64 tokens continues a previous one bit for bit.
+#include <mutex>
+
 #include "common.cuh"
 #include "cs1_ops.h"
 #include "mma.cuh"
@@ -613,4 +615,65 @@ extern "C" int cs1_gdn_prefill_x(const void* q, const void* k, const void* v, co
                                  void* o, float* workspace, int T, int H, int HK, float scale, const void* s_in,
                                  void* s_out, void* stream) {
     return gdn_run(q, k, v, g, beta, o, workspace, T, H, HK, scale, s_in, s_out, stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// cs1_gdn_prefill_static: the same delta rule for callers that cannot hand over scratch
+// ---------------------------------------------------------------------------------------
+// Some hosts of this library have no way to give cs1_gdn_prefill its workspace: a worker
+// that received a fixed set of device buffers from another runtime and is not allowed to
+// grow it, a plugin slot inside a serving process whose memory pool belongs to the host
+// framework, or code on a path where cudaMalloc is off limits because it synchronises the
+// whole device. For them this entry point keeps the workspace inside the library, in a
+// fixed array in device memory that exists once per GPU for as long as the library is
+// loaded. It allocates nothing: no cudaMalloc, no cudaFree, no library call that allocates.
+//
+// Limits and rules, all consequences of the array being one fixed, shared block:
+//   * the window must fit: cs1_gdn_workspace_floats(T, H) * 4 <= CS1_GDN_STATIC_SCRATCH_BYTES
+//     (64 MiB: for example 1792 tokens at 32 value heads, 1152 at 48, 3584 at 16); anything
+//     larger is refused with CS1_ERR_STATIC_SCRATCH before any launch;
+//   * every call on a GPU uses the same bytes, so two calls that may run at the same time
+//     on one GPU (different streams, or different threads) race on it; calls on one stream
+//     are ordered and safe;
+//   * the array still holds what the previous call left there. Nothing in it needs to start
+//     at zero: the first kernel of a call writes every byte the second one reads, including
+//     the rows that pad the last chunk;
+//   * the first call on each GPU looks up the array's device address (the name below is only
+//     a host-side handle, not an address a kernel could use) with that GPU current. Make
+//     that first call before any stream capture begins.
+static __device__ __align__(256) unsigned char g_gdn_static_scratch[CS1_GDN_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+// Device address of the array for the current device, resolved on first use.
+int static_scratch_address(float** out) {
+    static float* address[64] = {};
+    static std::mutex lock;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> hold(lock);
+    if (address[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_gdn_static_scratch);
+        if (e != cudaSuccess) return e;
+        if (p == nullptr) return cudaErrorInvalidSymbol;
+        address[dev] = static_cast<float*>(p);
+    }
+    *out = address[dev];
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int cs1_gdn_prefill_static(const void* q, const void* k, const void* v, const float* g, const void* beta,
+                                      void* o, int T, int H, int HK, float scale, void* stream) {
+    if (T < 0 || H <= 0 || HK <= 0 || H % HK != 0) return cudaErrorInvalidValue;
+    if (T == 0) return cudaSuccess;
+    if (s1::Layout(T, H).total > (size_t)CS1_GDN_STATIC_SCRATCH_BYTES) return CS1_ERR_STATIC_SCRATCH;
+    float* scratch = nullptr;
+    const int rc = static_scratch_address(&scratch);
+    if (rc != 0) return rc;
+    return s1::gdn_run(q, k, v, g, beta, o, scratch, T, H, HK, scale, nullptr, nullptr, stream);
 }

@@ -52,6 +52,7 @@ SIGNATURES = {
     "cs1_gdn_workspace_floats": (sz, [i32, i32]),
     "cs1_gdn_prefill": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, vp]),
     "cs1_gdn_prefill_x": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, vp, vp, vp]),
+    "cs1_gdn_prefill_static": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, vp]),
     "cs1_attn_prep": (i32, [vp, vp, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, vp]),
     "cs1_attention": (i32, [vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, vp]),
     "cs1_attention_gated": (i32, [vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, f32, vp]),
@@ -111,6 +112,8 @@ SIGNATURES = {
 }
 
 _LIB = None
+# cs1_* entry points of this library that the reference's ABI does not have
+NOT_IN_REFERENCE = {"cs1_gdn_prefill_static"}
 
 
 class CudaError(RuntimeError):
@@ -241,7 +244,7 @@ def load_other(path):
     side-by-side runs). Only the cs1_* symbols are bound; nothing is cached."""
     other = C.CDLL(path)
     for name, (res, args) in SIGNATURES.items():
-        if name.startswith("cs1_"):
+        if name.startswith("cs1_") and name not in NOT_IN_REFERENCE:
             fn = getattr(other, name)
             fn.restype = res
             fn.argtypes = args
