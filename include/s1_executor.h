@@ -31,7 +31,10 @@ int s1_mem_info(size_t* free_bytes, size_t* total_bytes);
 
 /* ---- GEMM engines behind cs1_gemm, pinned (benchmark arms and parity tests) ---- */
 int s1_gemm_cublaslt(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream);
-int s1_gemm_tcgen05(const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream);
+/* cs1_gemm with the K-split path switched off for this call. */
+int s1_gemm_unsplit(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream);
+/* gemm: a cs1_gemm_create handle whose workspace the K-split path may use, or null (no split). */
+int s1_gemm_tcgen05(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream);
 /* Waits for the device, returns in *code the error word of the tcgen05 GEMM (0 = no bounded
  * wait gave up) and clears it. */
 int s1_gemm_tc5_status(int* code);
@@ -67,6 +70,12 @@ void* s1_model_stream(void* model);
  * miss; a failed capture switches replay off): model.rs:797-897. Off by default, or on when
  * CUA_S1_GRAPH=1 is in the environment at creation, as in the reference (model.rs:695). */
 int s1_model_enable_graphs(void* model, int on);
+/* Exact packing (off by default): a prompt's hidden states come out bit-identical whether it
+ * runs alone or inside a pack. The projections back to the hidden size then run per sequence,
+ * as the reference does (model.rs:723-739), and the packed GEMMs run without a K split. With
+ * it off every GEMM runs once over the pack and may split K by the row count: faster, and
+ * equal to single execution within rounding (the reference's gate is 0.01 on the logits). */
+int s1_model_set_exact_packing(void* model, int on);
 int s1_model_graph_stats(void* model, int* replays, int* captures, int* enabled);
 
 /* Model::forward_batch (model.rs:769-823): prefill a pack of independent prompts

@@ -63,21 +63,23 @@ __global__ void __launch_bounds__(CONV_THREADS)
         dst = v, dld = value_dim, dc = c0 - 2 * key_dim;
     }
 
-    float x0[8], x1[8], x2[8], x3[8];
-    auto load_row = [&](int t, float (&x)[8]) {
-        if (t >= 0) {
-            unpack8(ld16_stream(qkv + (size_t)t * ld + c0), x);
-        } else {
+    // All rows of the block (and the 3-row halo) are requested before any arithmetic, so a
+    // thread keeps 19 independent 16-byte loads in flight instead of one.
+    uint4 rows[CONV_TT + 3];
 #pragma unroll
-            for (int e = 0; e < 8; e++) x[e] = 0.f;
-        }
-    };
-    load_row(t0 - 3, x0);
-    load_row(t0 - 2, x1);
-    load_row(t0 - 1, x2);
-    const int tend = min(T, t0 + CONV_TT);
-    for (int t = t0; t < tend; t++) {
-        load_row(t, x3);
+    for (int i = 0; i < CONV_TT + 3; i++) {
+        const int t = t0 - 3 + i;
+        rows[i] = (t >= 0 && t < T) ? ld16_stream(qkv + (size_t)t * ld + c0) : make_uint4(0, 0, 0, 0);
+    }
+    float x0[8], x1[8], x2[8], x3[8];
+    unpack8(rows[0], x0);
+    unpack8(rows[1], x1);
+    unpack8(rows[2], x2);
+#pragma unroll
+    for (int i = 0; i < CONV_TT; i++) {
+        const int t = t0 + i;
+        if (t >= T) break;
+        unpack8(rows[i + 3], x3);
         float y[8];
 #pragma unroll
         for (int e = 0; e < 8; e++) {
@@ -86,7 +88,7 @@ __global__ void __launch_bounds__(CONV_THREADS)
             acc = fmaf(wf[e][1], x1[e], acc);
             acc = fmaf(wf[e][2], x2[e], acc);
             acc = fmaf(wf[e][3], x3[e], acc);
-            y[e] = silu(rbf(acc));
+            y[e] = silu_fast(rbf(acc));
         }
         st16(dst + (size_t)t * dld + dc, pack8(y));
 #pragma unroll
@@ -111,7 +113,7 @@ __global__ void gdn_conv_scalar_kernel(const bf16* __restrict__ qkv, int ld, con
         const int s = t - 3 + j;
         if (s >= 0) acc = fmaf(f32(w[c * 4 + j]), f32(qkv[(size_t)s * ld + c]), acc);
     }
-    const bf16 y = to_bf16(silu(rbf(acc)));
+    const bf16 y = to_bf16(silu_fast(rbf(acc)));
     if (c < key_dim)
         q[(size_t)t * key_dim + c] = y;
     else if (c < 2 * key_dim)
@@ -158,7 +160,7 @@ __global__ void silu_mul_kernel(const bf16* __restrict__ gate_up, int ld, bf16* 
     if (i >= n) return;
     const size_t t = i / I, j = i % I;
     const bf16* row = gate_up + t * ld;
-    out[i] = to_bf16(rbf(silu(f32(row[j]))) * f32(row[I + j]));
+    out[i] = to_bf16(rbf(silu_fast(f32(row[j]))) * f32(row[I + j]));
 }
 
 // Two packs per thread keep more loads in flight per warp.
@@ -184,7 +186,7 @@ __global__ void __launch_bounds__(THREADS)
             unpack8(g[r], gv);
             unpack8(u[r], uv);
 #pragma unroll
-            for (int e = 0; e < 8; e++) gv[e] = rbf(silu(gv[e])) * uv[e];
+            for (int e = 0; e < 8; e++) gv[e] = rbf(silu_fast(gv[e])) * uv[e];
             out[idx[r]] = pack8(gv);
         }
     }

@@ -79,6 +79,7 @@ struct Model {
     void* gemm = nullptr;
     Scratch s;
     bool graph_enabled = false;
+    bool exact_packing = false;
     int replays = 0, captures = 0;
     std::deque<std::pair<std::vector<int>, void*>> graphs;
     int* ends_host = nullptr;  // pinned ring of ENDS_RING slots of cap ints
@@ -303,17 +304,37 @@ int op(Model* m, int family, int kernels, F&& call) {
 }
 #define S1_OP(family, kernels, expr) S1_TRY(op(m, family, kernels, [&] { return (expr); }))
 
-int gemm(Model* m, size_t x, const Tensor& w, size_t y, int rows, int n, int k) {
+int gemm(Model* m, size_t x, const Tensor& w, size_t y, int rows, int n, int k, bool packed = true) {
     const bool own = s1_gemm_engine(m->gemm, m->s.at(x), m->w(w), rows, n, k) == 1;
     if (!own) m->library_launches++;
-    return op(m, S1_FAMILY_GEMM, own ? 1 : 0,
-              [&] { return cs1_gemm(m->gemm, m->s.at(x), m->w(w), m->s.at(y), rows, n, k, n, m->stream); });
+    return op(m, S1_FAMILY_GEMM, own ? 1 : 0, [&] {
+        // packed rows under exact packing: no K split, so a row's sum does not depend on the pack
+        if (m->exact_packing && packed)
+            return s1_gemm_unsplit(m->gemm, m->s.at(x), m->w(w), m->s.at(y), rows, n, k, n, m->stream);
+        return cs1_gemm(m->gemm, m->s.at(x), m->w(w), m->s.at(y), rows, n, k, n, m->stream);
+    });
 }
 
-// The layer loop (model.rs:1119-1338). Pointwise operators and every GEMM run once over the
-// packed rows; conv, delta rule, attention prep and attention run per sequence. (The
-// reference also splits the out/down GEMMs per sequence, only to pin cuBLASLt's
-// shape-dependent reduction order; here a row's result does not depend on the row count.)
+// The projections back to the hidden size (out / o / down). With exact packing they run per
+// sequence, as the reference does (gemm_sequences, model.rs:723-739), so that a prompt sees
+// the same GEMM shape - and the same K-split plan - packed or alone; otherwise once over
+// the whole pack, which is faster and equal within rounding.
+int gemm_rows(Model* m, size_t x, const Tensor& w, size_t y, const int* lengths, int nseq, int n, int k) {
+    if (!m->exact_packing) {
+        int t = 0;
+        for (int i = 0; i < nseq; i++) t += lengths[i];
+        return gemm(m, x, w, y, t, n, k);
+    }
+    size_t off = 0;
+    for (int i = 0; i < nseq; i++) {
+        S1_TRY(gemm(m, x + off * k * BF16, w, y + off * n * BF16, lengths[i], n, k, /*packed=*/false));
+        off += lengths[i];
+    }
+    return 0;
+}
+
+// The layer loop (model.rs:1119-1338). Pointwise operators and the input / gate-up GEMMs run
+// once over the packed rows; conv, delta rule, attention prep and attention run per sequence.
 // dump (nullable, host) receives the residual stream after each layer.
 int run(Model* m, const int* lengths, int nseq, char* dump) {
     const S1Config& c = m->cfg;
@@ -357,7 +378,7 @@ int run(Model* m, const int* lengths, int nseq, char* dump) {
             }
             S1_OP(S1_FAMILY_GATED_NORM, 1,
                   cs1_gated_rms_norm(s.at(s.lo), s.at(z), gdn_in, m->w(ly.norm), s.at(s.ln), t, hv, 128, eps, st));
-            S1_TRY(gemm(m, s.ln, ly.out, s.delta, t, h, vd));
+            S1_TRY(gemm_rows(m, s.ln, ly.out, s.delta, lengths, nseq, h, vd));
         } else {
             S1_TRY(gemm(m, s.x, ly.qkv, s.attn_in, t, attn_in, h));
             const size_t k = s.attn_in + (size_t)attn_q * BF16;
@@ -378,13 +399,13 @@ int run(Model* m, const int* lengths, int nseq, char* dump) {
                                           lengths[q], hq, hk, hd, 1.0f / sqrtf((float)hd), st));
                 off += lengths[q];
             }
-            S1_TRY(gemm(m, s.ao, ly.o, s.delta, t, h, hq * hd));
+            S1_TRY(gemm_rows(m, s.ao, ly.o, s.delta, lengths, nseq, h, hq * hd));
         }
         S1_OP(S1_FAMILY_NORM, 1,
               cs1_add_rms_norm(s.at(s.res), s.at(s.delta), m->w(ly.post_norm), s.at(s.x), t, h, eps, st));
         S1_TRY(gemm(m, s.x, ly.gate_up, s.gate_up, t, 2 * I, h));
         S1_OP(S1_FAMILY_SILU_MUL, 1, cs1_silu_mul(s.at(s.gate_up), 2 * I, s.at(s.act), t, I, st));
-        S1_TRY(gemm(m, s.act, ly.down, s.delta, t, h, I));
+        S1_TRY(gemm_rows(m, s.act, ly.down, s.delta, lengths, nseq, h, I));
         const Tensor& next = li + 1 < m->layers.size() ? m->layers[li + 1].input_norm : m->final_norm;
         S1_OP(S1_FAMILY_NORM, 1, cs1_add_rms_norm(s.at(s.res), s.at(s.delta), m->w(next), s.at(s.x), t, h, eps, st));
         if (dump) S1_TRY(cs1_download(dump + li * (size_t)t * h * BF16, s.at(s.res), (size_t)t * h * BF16, st));
@@ -554,6 +575,14 @@ int s1_model_init_random(void* model, uint64_t seed, float std) {
 
 size_t s1_model_weight_bytes(void* model) { return model ? static_cast<Model*>(model)->arena_bytes : 0; }
 void* s1_model_stream(void* model) { return model ? static_cast<Model*>(model)->stream : nullptr; }
+
+int s1_model_set_exact_packing(void* model, int on) {
+    Model* m = static_cast<Model*>(model);
+    if (!m) return S1_ERR_ARGUMENT;
+    if (m->exact_packing != (on != 0)) clear_graphs(m);
+    m->exact_packing = on != 0;
+    return 0;
+}
 
 int s1_model_enable_graphs(void* model, int on) {
     Model* m = static_cast<Model*>(model);

@@ -89,8 +89,9 @@ constexpr int P_SM = P_TB + C * LDT * 2;         // float [6][64]    g/cum, beta
 constexpr int PREP_SMEM = P_SM + 6 * C * 4;
 // after the pair products the operand tiles are dead: v and k*exp(cum) reuse them
 constexpr int P_VS = P_KF;                       // bf16 [64][LDH]
-constexpr int P_KE = P_QF;                       // bf16 [64][LDH]
+constexpr int P_KE = P_QF + C * D * 2;           // bf16 [64][LDH], after the unpadded raw k rows
 static_assert(C * LDH * 2 <= C * LDF * 4, "bf16 tile fits over a float tile");
+static_assert(C * D * 2 + C * LDH * 2 <= C * LDF * 4, "raw k rows and k*exp(cum) fit over the q tile");
 
 __global__ void __launch_bounds__(PREP_THREADS, 2)
     gdn_prep(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
@@ -113,6 +114,22 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
     const int r0 = c * C, n = min(C, T - r0);
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
 
+    // The q and k rows of the norm phase are requested first of all, so that their latency
+    // hides behind the decay phase.
+    const int sub = tid & 15, rsel = tid >> 4;
+    const int d0 = sub * 4;
+    uint2 raw[8][2];
+#pragma unroll
+    for (int pass = 0; pass < 8; pass++) {
+        const int i = (pass & 3) * 16 + rsel;
+        raw[pass][0] = raw[pass][1] = make_uint2(0, 0);
+        if (i < n) {
+            const bf16* src = (pass < 4 ? k : q) + ((size_t)(r0 + i) * HK + hk) * D + d0;
+            raw[pass][0] = *reinterpret_cast<const uint2*>(src);
+            raw[pass][1] = *reinterpret_cast<const uint2*>(src + 64);
+        }
+    }
+
     // ---- log-decays: sequential float32 prefix sum, rows past the end have g = beta = 0 ----
     if (tid < C) {
         cum[tid] = tid < n ? g[(size_t)(r0 + tid) * H + h] : 0.f;
@@ -120,11 +137,20 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
     }
     __syncthreads();
     if (tid == 0) {
+        // in registers: 16 wide loads, 64 dependent adds, 16 wide stores
+        float4 part[C / 4];
+#pragma unroll
+        for (int i = 0; i < C / 4; i++) part[i] = reinterpret_cast<const float4*>(cum)[i];
         float run = 0.f;
-        for (int i = 0; i < C; i++) {
-            run += cum[i];
-            cum[i] = run;
+#pragma unroll
+        for (int i = 0; i < C / 4; i++) {
+            part[i].x = (run += part[i].x);
+            part[i].y = (run += part[i].y);
+            part[i].z = (run += part[i].z);
+            part[i].w = (run += part[i].w);
         }
+#pragma unroll
+        for (int i = 0; i < C / 4; i++) reinterpret_cast<float4*>(cum)[i] = part[i];
     }
     __syncthreads();
     if (tid < C) {
@@ -137,8 +163,9 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
 
     // ---- L2 norms; TF32 operand tiles; qd and kd to the workspace ----
     {
-        const int sub = tid & 15, rsel = tid >> 4;  // 16 lanes per row, 16 rows per pass
-        const int d0 = sub * 8;
+        // 16 lanes per row, 16 rows per pass; a lane owns dims [4 sub, 4 sub + 4) and
+        // [64 + 4 sub, 64 + 4 sub + 4), so that the float4 stores of a quarter warp fall in one
+        // contiguous 128-byte run of shared memory. All 16 loads are requested up front.
         bf16* qd_out = ws.qd + ((size_t)h * NCC + r0) * D;
         bf16* kd_out = ws.kd + ((size_t)h * NCC + r0) * D;
 #pragma unroll
@@ -146,41 +173,41 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
             const bool is_k = pass < 4;
             const int i = (pass & 3) * 16 + rsel;
             float x[8];
-            if (i < n) {
-                const bf16* src = (is_k ? k : q) + ((size_t)(r0 + i) * HK + hk) * D + d0;
-                unpack8(ld16(src), x);
-            } else {
 #pragma unroll
-                for (int e = 0; e < 8; e++) x[e] = 0.f;
+            for (int half = 0; half < 2; half++) {
+                x[4 * half + 0] = __uint_as_float(raw[pass][half].x << 16);
+                x[4 * half + 1] = __uint_as_float(raw[pass][half].x & 0xffff0000u);
+                x[4 * half + 2] = __uint_as_float(raw[pass][half].y << 16);
+                x[4 * half + 3] = __uint_as_float(raw[pass][half].y & 0xffff0000u);
             }
             float ss = 0.f;
 #pragma unroll
             for (int e = 0; e < 8; e++) ss += x[e] * x[e];
             ss = warp_sum<16>(ss);
             float inv = rsqrtf(ss + 1e-6f);
-            float y[8];
             if (is_k) {
                 if (sub == 0) kinv[i] = inv;
-                const float er = erem[i];
-                float* dst = kf + i * LDF + d0;
-#pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    const float kn = x[e] * inv;
-                    dst[e] = __uint_as_float(to_tf32(kn));
-                    y[e] = kn * er;
-                }
-                st16(kd_out + (size_t)i * D + d0, pack8(y));
             } else {
                 inv *= scale;
-                const float ec = ecum[i];
-                float* dst = qf + i * LDF + d0;
+            }
+            const float mult = is_k ? erem[i] : ecum[i];
+            float* tile = (is_k ? kf : qf) + i * LDF;
+            bf16* dout = (is_k ? kd_out : qd_out) + (size_t)i * D;
 #pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    const float qn = x[e] * inv;
-                    dst[e] = __uint_as_float(to_tf32(qn));
-                    y[e] = qn * ec;
-                }
-                st16(qd_out + (size_t)i * D + d0, pack8(y));
+            for (int half = 0; half < 2; half++) {
+                float4 t;
+                float nrm[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) nrm[e] = x[4 * half + e] * inv;
+                t.x = __uint_as_float(to_tf32(nrm[0]));
+                t.y = __uint_as_float(to_tf32(nrm[1]));
+                t.z = __uint_as_float(to_tf32(nrm[2]));
+                t.w = __uint_as_float(to_tf32(nrm[3]));
+                *reinterpret_cast<float4*>(tile + 64 * half + d0) = t;
+                uint2 o;
+                o.x = pack2(nrm[0] * mult, nrm[1] * mult);
+                o.y = pack2(nrm[2] * mult, nrm[3] * mult);
+                *reinterpret_cast<uint2*>(dout + 64 * half + d0) = o;
             }
         }
     }
@@ -241,47 +268,55 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
     }
     __syncthreads();
 
+    // ---- v and the raw k rows come in by asynchronous copies over the dead operand tiles
+    //      (every thread requests four 16-byte pieces of each and later converts only the k
+    //      pieces it requested itself, so no barrier is needed in between) ----
+    bf16* kraw = reinterpret_cast<bf16*>(smem + P_QF);  // [64][128], no padding
+#pragma unroll
+    for (int piece = 0; piece < 4; piece++) {
+        const int cidx = tid + piece * PREP_THREADS;
+        const int i = cidx / (D / 8), d0 = (cidx % (D / 8)) * 8;
+        const int row = r0 + min(i, n - 1);
+        cp_async16(vs + i * LDH + d0, v + ((size_t)row * H + h) * D + d0, i < n);
+        cp_async16(kraw + i * D + d0, k + ((size_t)row * HK + hk) * D + d0, i < n);
+    }
+    cp_async_commit();
+
     // ---- warps 0-1: T = (I + A)^-1 by forward substitution, one column per thread held in
-    //      registers; warps 2-7 meanwhile stage v and k*exp(cum) over the dead operand tiles ----
+    //      registers, while the copies land ----
     if (warp < 2) {
         const int j = tid;
         float col[C];
 #pragma unroll
         for (int i = 0; i < C; i++) {
-            float acc = i == j ? 1.f : 0.f;
+            // four independent partial sums (m mod 4) keep the dependent chain a quarter as long
+            float a0 = i == j ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
             const float* arow = A + i * LDA;
 #pragma unroll
             for (int m4 = 0; m4 < (i + 3) / 4; m4++) {
                 const float4 a4 = *reinterpret_cast<const float4*>(arow + m4 * 4);
-                if (m4 * 4 + 0 < i) acc -= a4.x * col[m4 * 4 + 0];
-                if (m4 * 4 + 1 < i) acc -= a4.y * col[m4 * 4 + 1];
-                if (m4 * 4 + 2 < i) acc -= a4.z * col[m4 * 4 + 2];
-                if (m4 * 4 + 3 < i) acc -= a4.w * col[m4 * 4 + 3];
+                if (m4 * 4 + 0 < i) a0 -= a4.x * col[m4 * 4 + 0];
+                if (m4 * 4 + 1 < i) a1 -= a4.y * col[m4 * 4 + 1];
+                if (m4 * 4 + 2 < i) a2 -= a4.z * col[m4 * 4 + 2];
+                if (m4 * 4 + 3 < i) a3 -= a4.w * col[m4 * 4 + 3];
             }
-            col[i] = acc;
+            col[i] = (a0 + a1) + (a2 + a3);
         }
         const float bj = bt[j];
 #pragma unroll
         for (int i = 0; i < C; i++) Tb[i * LDT + j] = to_bf16(col[i] * bj);
-    } else {
-        const int t2 = tid - 64;  // 0..191
-        for (int cidx = t2; cidx < C * (D / 8); cidx += PREP_THREADS - 64) {
-            const int i = cidx / (D / 8), d0 = (cidx % (D / 8)) * 8;
-            uint4 vv = make_uint4(0, 0, 0, 0);
-            float y[8];
+    }
+    cp_async_wait<0>();
 #pragma unroll
-            for (int e = 0; e < 8; e++) y[e] = 0.f;
-            if (i < n) {
-                vv = ld16(v + ((size_t)(r0 + i) * H + h) * D + d0);
-                float x[8];
-                unpack8(ld16(k + ((size_t)(r0 + i) * HK + hk) * D + d0), x);
-                const float inv = kinv[i], ec = ecum[i];
+    for (int piece = 0; piece < 4; piece++) {  // k * exp(cum) in bf16 from this thread's own pieces
+        const int cidx = tid + piece * PREP_THREADS;
+        const int i = cidx / (D / 8), d0 = (cidx % (D / 8)) * 8;
+        float x[8], y[8];
+        unpack8(ld16(kraw + i * D + d0), x);
+        const float inv = kinv[i], ec = ecum[i];
 #pragma unroll
-                for (int e = 0; e < 8; e++) y[e] = (x[e] * inv) * ec;
-            }
-            st16(vs + i * LDH + d0, vv);
-            st16(ke + i * LDH + d0, pack8(y));
-        }
+        for (int e = 0; e < 8; e++) y[e] = (x[e] * inv) * ec;
+        st16(ke + i * LDH + d0, pack8(y));
     }
     __syncthreads();
 
@@ -319,7 +354,6 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
 // ---------------------------------------------------------------------------------------
 // gdn_scan
 // ---------------------------------------------------------------------------------------
-constexpr int SCAN_THREADS = 128;
 
 template <int VS>
 struct ScanSmem {
@@ -334,13 +368,20 @@ struct ScanSmem {
     static constexpr int BYTES = VN + C * LDV * 2;
 };
 
-template <int VS>
-__global__ void __launch_bounds__(SCAN_THREADS, 2)
+// WARPS is 4 or 8. The 64 chunk rows split into four 16-row tiles (rt); with 8 warps the
+// slice's columns additionally split into two halves (cb) for the row products, and the 128
+// state rows split 16 per warp instead of 32.
+template <int VS, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 2)
     gdn_scan(Work ws, bf16* __restrict__ o, int T, int H, int NC, const float* __restrict__ s_in,
              float* __restrict__ s_out) {
     using L = ScanSmem<VS>;
     constexpr int LDV = L::LDV;
-    constexpr int NT = VS / 8;  // 8-column tiles across the slice
+    constexpr int NT = VS / 8;               // 8-column tiles across the slice
+    constexpr int THREADS = WARPS * 32;
+    constexpr int MT = 8 / WARPS;            // 16-row tiles of the state per warp
+    constexpr int NTL = NT / (WARPS / 4);    // column tiles per warp in the row products
+    static_assert(NTL >= 2 && NTL % 2 == 0, "column tiles are loaded in pairs");
     extern __shared__ __align__(16) unsigned char smem[];
     bf16* Wb = reinterpret_cast<bf16*>(smem + L::W);
     bf16* Ub = reinterpret_cast<bf16*>(smem + L::U);
@@ -354,6 +395,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2)
     const int NCC = NC * C;
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const int gq = lane / 4, tq = lane % 4;
+    const int rt = warp & 3, cb = (warp >> 2) * NTL * 8;
 
     const bf16* w_g = ws.w + (size_t)h * NCC * D;
     const bf16* u_g = ws.u + (size_t)h * NCC * D + v0;
@@ -367,11 +409,11 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2)
         bf16* ud = Ub + (c & 1) * C * LDV;
         const bf16* wsrc = w_g + (size_t)c * C * D;
         const bf16* usrc = u_g + (size_t)c * C * D;
-        for (int i = tid; i < C * (D / 8); i += SCAN_THREADS) {
+        for (int i = tid; i < C * (D / 8); i += THREADS) {
             const int r = i / (D / 8), col = (i % (D / 8)) * 8;
             cp_async16(wd + r * LDH + col, wsrc + (size_t)r * D + col);
         }
-        for (int i = tid; i < C * (VS / 8); i += SCAN_THREADS) {
+        for (int i = tid; i < C * (VS / 8); i += THREADS) {
             const int r = i / (VS / 8), col = (i % (VS / 8)) * 8;
             cp_async16(ud + r * LDV + col, usrc + (size_t)r * D + col);
         }
@@ -380,12 +422,12 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2)
         const bf16* qsrc = qd_g + (size_t)c * C * D;
         const bf16* ksrc = kd_g + (size_t)c * C * D;
         const bf16* psrc = p_g + (size_t)c * C * C;
-        for (int i = tid; i < C * (D / 8); i += SCAN_THREADS) {
+        for (int i = tid; i < C * (D / 8); i += THREADS) {
             const int r = i / (D / 8), col = (i % (D / 8)) * 8;
             cp_async16(QDb + r * LDH + col, qsrc + (size_t)r * D + col);
             cp_async16(KDb + r * LDH + col, ksrc + (size_t)r * D + col);
         }
-        for (int i = tid; i < C * (C / 8); i += SCAN_THREADS) {
+        for (int i = tid; i < C * (C / 8); i += THREADS) {
             const int r = i / (C / 8), col = (i % (C / 8)) * 8;
             cp_async16(Pb + r * LDT + col, psrc + (size_t)r * C + col);
         }
@@ -397,14 +439,14 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2)
     cp_async_commit();
 
     // state rows [32 warp, 32 warp + 32) x VS columns, float32, in mma accumulator layout
-    float S[2][NT][4];
+    float S[MT][NT][4];
 #pragma unroll
-    for (int mt = 0; mt < 2; mt++)
+    for (int mt = 0; mt < MT; mt++)
 #pragma unroll
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                const int kr = warp * 32 + mt * 16 + gq + (e >> 1) * 8;
+                const int kr = warp * (MT * 16) + mt * 16 + gq + (e >> 1) * 8;
                 const int vc = v0 + nt * 8 + 2 * tq + (e & 1);
                 S[mt][nt][e] = s_in ? s_in[((size_t)h * D + kr) * D + vc] : 0.f;
             }
@@ -412,10 +454,10 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2)
     for (int c = 0; c < NC; c++) {
         // (1) bf16 copy of the chunk-entry state
 #pragma unroll
-        for (int mt = 0; mt < 2; mt++)
+        for (int mt = 0; mt < MT; mt++)
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                const int kr = warp * 32 + mt * 16 + gq, vc = nt * 8 + 2 * tq;
+                const int kr = warp * (MT * 16) + mt * 16 + gq, vc = nt * 8 + 2 * tq;
                 *reinterpret_cast<uint32_t*>(Sb + kr * LDV + vc) = pack2(S[mt][nt][0], S[mt][nt][1]);
                 *reinterpret_cast<uint32_t*>(Sb + (kr + 8) * LDV + vc) = pack2(S[mt][nt][2], S[mt][nt][3]);
             }
@@ -430,24 +472,24 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2)
 
         // (2) v_new = u - w S
         {
-            float acc[NT][4];
+            float acc[NTL][4];
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+            for (int nt = 0; nt < NTL; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 #pragma unroll
             for (int kk = 0; kk < D / 16; kk++) {
                 uint32_t a[4];
-                load_a_rm(a, Wc, LDH, warp * 16, kk * 16, lane);
+                load_a_rm(a, Wc, LDH, rt * 16, kk * 16, lane);
 #pragma unroll
-                for (int np = 0; np < NT / 2; np++) {
+                for (int np = 0; np < NTL / 2; np++) {
                     uint32_t b[4];
-                    load_b_kn(b, Sb, LDV, kk * 16, np * 16, lane);
+                    load_b_kn(b, Sb, LDV, kk * 16, cb + np * 16, lane);
                     mma_bf16(acc[2 * np], a, b[0], b[1]);
                     mma_bf16(acc[2 * np + 1], a, b[2], b[3]);
                 }
             }
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-                const int r = warp * 16 + gq, vc = nt * 8 + 2 * tq;
+            for (int nt = 0; nt < NTL; nt++) {
+                const int r = rt * 16 + gq, vc = cb + nt * 8 + 2 * tq;
                 const uint32_t u0 = *reinterpret_cast<const uint32_t*>(Uc + r * LDV + vc);
                 const uint32_t u1 = *reinterpret_cast<const uint32_t*>(Uc + (r + 8) * LDV + vc);
                 *reinterpret_cast<uint32_t*>(VNb + r * LDV + vc) =
@@ -461,17 +503,17 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2)
 
         // (3) o = qd S + P v_new
         {
-            float acc[NT][4];
+            float acc[NTL][4];
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+            for (int nt = 0; nt < NTL; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 #pragma unroll
             for (int kk = 0; kk < D / 16; kk++) {
                 uint32_t a[4];
-                load_a_rm(a, QDb, LDH, warp * 16, kk * 16, lane);
+                load_a_rm(a, QDb, LDH, rt * 16, kk * 16, lane);
 #pragma unroll
-                for (int np = 0; np < NT / 2; np++) {
+                for (int np = 0; np < NTL / 2; np++) {
                     uint32_t b[4];
-                    load_b_kn(b, Sb, LDV, kk * 16, np * 16, lane);
+                    load_b_kn(b, Sb, LDV, kk * 16, cb + np * 16, lane);
                     mma_bf16(acc[2 * np], a, b[0], b[1]);
                     mma_bf16(acc[2 * np + 1], a, b[2], b[3]);
                 }
@@ -479,19 +521,19 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2)
 #pragma unroll
             for (int kk = 0; kk < C / 16; kk++) {
                 uint32_t a[4];
-                load_a_rm(a, Pb, LDT, warp * 16, kk * 16, lane);
+                load_a_rm(a, Pb, LDT, rt * 16, kk * 16, lane);
 #pragma unroll
-                for (int np = 0; np < NT / 2; np++) {
+                for (int np = 0; np < NTL / 2; np++) {
                     uint32_t b[4];
-                    load_b_kn(b, VNb, LDV, kk * 16, np * 16, lane);
+                    load_b_kn(b, VNb, LDV, kk * 16, cb + np * 16, lane);
                     mma_bf16(acc[2 * np], a, b[0], b[1]);
                     mma_bf16(acc[2 * np + 1], a, b[2], b[3]);
                 }
             }
-            const int row = c * C + warp * 16 + gq;
+            const int row = c * C + rt * 16 + gq;
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-                const int vc = v0 + nt * 8 + 2 * tq;
+            for (int nt = 0; nt < NTL; nt++) {
+                const int vc = v0 + cb + nt * 8 + 2 * tq;
                 if (row < T)
                     *reinterpret_cast<uint32_t*>(o + ((size_t)row * H + h) * D + vc) = pack2(acc[nt][0], acc[nt][1]);
                 if (row + 8 < T)
@@ -502,7 +544,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2)
 
         // (4) S = decay S + kd^T v_new
 #pragma unroll
-        for (int mt = 0; mt < 2; mt++)
+        for (int mt = 0; mt < MT; mt++)
 #pragma unroll
             for (int nt = 0; nt < NT; nt++)
 #pragma unroll
@@ -513,9 +555,9 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2)
 #pragma unroll
             for (int np = 0; np < NT / 2; np++) load_b_kn(b[np], VNb, LDV, kk * 16, np * 16, lane);
 #pragma unroll
-            for (int mt = 0; mt < 2; mt++) {
+            for (int mt = 0; mt < MT; mt++) {
                 uint32_t a[4];
-                load_a_tr(a, KDb, LDH, warp * 32 + mt * 16, kk * 16, lane);
+                load_a_tr(a, KDb, LDH, warp * (MT * 16) + mt * 16, kk * 16, lane);
 #pragma unroll
                 for (int np = 0; np < NT / 2; np++) {
                     mma_bf16(S[mt][2 * np], a, b[np][0], b[np][1]);
@@ -531,12 +573,12 @@ __global__ void __launch_bounds__(SCAN_THREADS, 2)
 
     if (s_out) {
 #pragma unroll
-        for (int mt = 0; mt < 2; mt++)
+        for (int mt = 0; mt < MT; mt++)
 #pragma unroll
             for (int nt = 0; nt < NT; nt++)
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
-                    const int kr = warp * 32 + mt * 16 + gq + (e >> 1) * 8;
+                    const int kr = warp * (MT * 16) + mt * 16 + gq + (e >> 1) * 8;
                     const int vc = v0 + nt * 8 + 2 * tq + (e & 1);
                     s_out[((size_t)h * D + kr) * D + vc] = S[mt][nt][e];
                 }
@@ -583,15 +625,13 @@ int gdn_run(const void* q, const void* k, const void* v, const float* g, const v
     if (e != cudaSuccess) return e;
     // Narrow slices when there are few heads, so that the scan still covers the SMs.
     if (H * (D / 32) >= 96) {
-        e = set_smem_once(gdn_scan<32>, ScanSmem<32>::BYTES, scan32_done);
+        e = set_smem_once(gdn_scan<32, 8>, ScanSmem<32>::BYTES, scan32_done);
         if (e != cudaSuccess) return e;
-        gdn_scan<32><<<dim3(H, D / 32), SCAN_THREADS, ScanSmem<32>::BYTES, st>>>(ws, static_cast<bf16*>(o), T, H, NC,
-                                                                                si, so);
+        gdn_scan<32, 8><<<dim3(H, D / 32), 256, ScanSmem<32>::BYTES, st>>>(ws, static_cast<bf16*>(o), T, H, NC, si, so);
     } else {
-        e = set_smem_once(gdn_scan<16>, ScanSmem<16>::BYTES, scan16_done);
+        e = set_smem_once(gdn_scan<16, 4>, ScanSmem<16>::BYTES, scan16_done);
         if (e != cudaSuccess) return e;
-        gdn_scan<16><<<dim3(H, D / 16), SCAN_THREADS, ScanSmem<16>::BYTES, st>>>(ws, static_cast<bf16*>(o), T, H, NC,
-                                                                                si, so);
+        gdn_scan<16, 4><<<dim3(H, D / 16), 128, ScanSmem<16>::BYTES, st>>>(ws, static_cast<bf16*>(o), T, H, NC, si, so);
     }
     return cudaGetLastError();
 }

@@ -30,12 +30,14 @@ struct Plan {
 };
 
 using Key = std::tuple<int, int, int, int>;  // M, N, K, ldy
+constexpr int COUNTER_SLOTS = 16384;
 
 struct Gemm {
     cublasLtHandle_t handle = nullptr;
     void* workspace = nullptr;
     size_t workspace_bytes = 0;
     bool use_tc5 = true;
+    int* counters = nullptr;
     std::map<Key, Plan> plans;
     std::mutex lock;
 };
@@ -109,6 +111,15 @@ extern "C" void* cs1_gemm_create(size_t workspace_bytes) {
         return nullptr;
     }
     g->workspace_bytes = workspace_bytes;
+    // counters of the tcgen05 kernel's K-split path; zero between launches
+    if (cudaMalloc(reinterpret_cast<void**>(&g->counters), COUNTER_SLOTS * sizeof(int)) != cudaSuccess ||
+        cudaMemset(g->counters, 0, COUNTER_SLOTS * sizeof(int)) != cudaSuccess) {
+        if (g->counters) cudaFree(g->counters);
+        if (g->workspace) cudaFree(g->workspace);
+        cublasLtDestroy(g->handle);
+        delete g;
+        return nullptr;
+    }
     const char* engine = getenv("S1_GEMM");
     g->use_tc5 = !(engine && strcmp(engine, "cublaslt") == 0);
     return g;
@@ -119,9 +130,16 @@ extern "C" void cs1_gemm_destroy(void* gemm) {
     if (!g) return;
     for (auto& kv : g->plans) destroy(kv.second);
     if (g->workspace) cudaFree(g->workspace);
+    if (g->counters) cudaFree(g->counters);
     cublasLtDestroy(g->handle);
     delete g;
 }
+
+namespace {
+S1GemmScratch scratch_of(Gemm* g) {
+    return S1GemmScratch{g->workspace, g->workspace_bytes, g->counters, COUNTER_SLOTS};
+}
+}  // namespace
 
 extern "C" int cs1_gemm(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy,
                         void* stream) {
@@ -129,7 +147,21 @@ extern "C" int cs1_gemm(void* gemm, const void* x, const void* w, void* y, int M
     if (!g || M < 0 || N <= 0 || K <= 0 || ldy < N) return cudaErrorInvalidValue;
     if (M == 0) return cudaSuccess;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (g->use_tc5 && s1_gemm_tc5_supported(x, w, y, M, N, K, ldy)) return s1_gemm_tc5(x, w, y, M, N, K, ldy, st);
+    if (g->use_tc5 && s1_gemm_tc5_supported(x, w, y, M, N, K, ldy)) {
+        const S1GemmScratch scratch = scratch_of(g);
+        return s1_gemm_tc5(x, w, y, M, N, K, ldy, &scratch, st);
+    }
+    return lt_gemm(*g, x, w, y, M, N, K, ldy, st);
+}
+
+// cs1_gemm without the K-split path: every row's sum runs over K in one fixed order, whatever M is.
+extern "C" int s1_gemm_unsplit(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy,
+                               void* stream) {
+    Gemm* g = static_cast<Gemm*>(gemm);
+    if (!g || M < 0 || N <= 0 || K <= 0 || ldy < N) return cudaErrorInvalidValue;
+    if (M == 0) return cudaSuccess;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (g->use_tc5 && s1_gemm_tc5_supported(x, w, y, M, N, K, ldy)) return s1_gemm_tc5(x, w, y, M, N, K, ldy, nullptr, st);
     return lt_gemm(*g, x, w, y, M, N, K, ldy, st);
 }
 
@@ -147,9 +179,13 @@ extern "C" int s1_gemm_cublaslt(void* gemm, const void* x, const void* w, void* 
     return lt_gemm(*g, x, w, y, M, N, K, ldy, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int s1_gemm_tcgen05(const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream) {
+extern "C" int s1_gemm_tcgen05(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy,
+                               void* stream) {
     if (M < 0 || N <= 0 || K <= 0 || ldy < N) return cudaErrorInvalidValue;
     if (M == 0) return cudaSuccess;
     if (!s1_gemm_tc5_supported(x, w, y, M, N, K, ldy)) return CS1_ERR_UNSUPPORTED;
-    return s1_gemm_tc5(x, w, y, M, N, K, ldy, static_cast<cudaStream_t>(stream));
+    Gemm* g = static_cast<Gemm*>(gemm);  // null: no scratch, so no K split
+    if (!g) return s1_gemm_tc5(x, w, y, M, N, K, ldy, nullptr, static_cast<cudaStream_t>(stream));
+    const S1GemmScratch scratch = scratch_of(g);
+    return s1_gemm_tc5(x, w, y, M, N, K, ldy, &scratch, static_cast<cudaStream_t>(stream));
 }

@@ -9,9 +9,18 @@
 //
 // Tiles are assigned round-robin to the resident blocks with all row-blocks of one column
 // block adjacent, so a w tile is fetched from HBM once and then served from L2. Rows past M,
-// columns past N and a K tail are zero-filled by TMA and masked in the epilogue. No load is
-// cluster-multicast. Every barrier wait is bounded; a wait that runs out records a code in
-// a device error word (read with s1_gemm_tc5_status) and the block winds down.
+// columns past N and a K tail are zero-filled by TMA and masked in the epilogue. Every block
+// fetches its own tiles (no load is shared across blocks by the copy engine). Every barrier
+// wait is bounded; a wait that runs out records a code in a device error word (read with
+// s1_gemm_tc5_status) and the block winds down.
+//
+// Two kernels: gemm_tc5_kernel, one block per 128 x BN tile, for up to 128 rows; and
+// gemm_tc5_pair_kernel for more rows, where the two blocks of a cluster work as a pair on a
+// 256 x BN tile (tcgen05 cta_group::2): each block loads its 128 rows of x and only half of
+// the w tile, the pair leader issues one MMA that reads both halves, and each block keeps and
+// stores its own 128 rows of the result. That cuts the shared-memory fill per flop by a third
+// and lets BN be any multiple of 32, chosen per problem so that the tile count fills whole
+// waves of the 74 pairs.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -201,6 +210,259 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     if (warp == 2) tmem_dealloc(tmem_base, G::TMEM_COLS);
 }
 
+// ---- CTA-pair kernel: 256 x BN tiles on two blocks of a cluster ----
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_A_BYTES = BM * BK * 2;          // this block's 128 rows of x
+constexpr int PAIR_B_MAX = 128 * BK * 2;           // this block's half of the w tile, BN / 2 <= 128 rows
+constexpr int PAIR_STAGE = PAIR_A_BYTES + PAIR_B_MAX;
+constexpr int PAIR_SMEM = PAIR_STAGES * PAIR_STAGE + 256 + 1024;
+constexpr int PAIR_TMEM_COLS = 512;                // two accumulators 256 columns apart
+constexpr int PAIR_ACC_STRIDE = 256;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+    gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
+                         bf16* __restrict__ y, int M, int N, int K, int ldy, int vec_ok, int BN, int splits,
+                         float* __restrict__ partials, int* __restrict__ counters) {
+    using namespace tc5;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + PAIR_STAGES * PAIR_STAGE);  // used in the leader only
+    uint64_t* empty = full + PAIR_STAGES;                                           // one copy per block
+    uint64_t* tfull = empty + PAIR_STAGES;                                          // one copy per block
+    uint64_t* tempty = tfull + 2;                                                   // used in the leader only
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PAIR_STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(&tfull[a], 1);
+            mbar_init(&tempty[a], 8);  // four epilogue warps in each block of the pair
+        }
+        *abort_flag = 0;
+        mbar_init_fence();
+        prefetch_tmap(&tma_x);
+        prefetch_tmap(&tma_w);
+    }
+    if (warp == 2) {
+        tmem_alloc_pair(tmem_slot, PAIR_TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    fence_before_sync();
+    __syncthreads();
+    cluster_sync();  // both blocks' barriers exist before anything arrives on them
+    fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_m = (M + 2 * BM - 1) / (2 * BM), num_n = (N + BN - 1) / BN;
+    const int tiles = num_m * num_n, kblocks = (K + BK - 1) / BK;
+    // A work unit is one tile's k-blocks [kb0, kb1): the whole K range, or one of `splits`
+    // equal parts whose float32 partial sums are combined by the last unit to finish.
+    const int units = tiles * splits, kb_per = (kblocks + splits - 1) / splits;
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const int half_n = BN / 2;
+    const uint32_t stage_bytes = PAIR_A_BYTES + half_n * BK * 2;
+    auto fail = [&](int code) {
+        atomicCAS(&g_gemm_error, 0, code);
+        *abort_flag = 1;
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int unit = pair; ok && unit < units; unit += npairs) {
+                const int tile = unit / splits, part = unit % splits;
+                const int m0 = (tile % num_m) * 2 * BM + (int)rank * BM;
+                const int n0 = (tile / num_m) * BN + (int)rank * half_n;
+                const int kb0 = part * kb_per, kb1 = min(kblocks, (part + 1) * kb_per);
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+                        fail(11);
+                        ok = false;
+                        break;
+                    }
+                    unsigned char* dst = smem + stage * PAIR_STAGE;
+                    if (leader) mbar_expect_tx(&full[stage], 2 * stage_bytes);  // both blocks' bytes land on it
+                    tma_load_2d_pair(dst, &tma_x, kb * BK, m0, &full[stage]);
+                    tma_load_2d_pair(dst + PAIR_A_BYTES, &tma_w, kb * BK, n0, &full[stage]);
+                    if (++stage == PAIR_STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (leader && lane == 0) {
+            const uint32_t idesc = instr_desc(1, 2 * BM, BN);
+            uint32_t stage = 0, phase = 0, it = 0;
+            bool ok = true;
+            for (int unit = pair; ok && unit < units; unit += npairs, it++) {
+                const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+                if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
+                    fail(13);
+                    break;
+                }
+                fence_after_sync();
+                const uint32_t d = tmem_base + acc * PAIR_ACC_STRIDE;
+                const int part = unit % splits;
+                const int kb0 = part * kb_per, kb1 = min(kblocks, (part + 1) * kb_per);
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!mbar_wait(&full[stage], phase, abort_flag)) {
+                        fail(12);
+                        ok = false;
+                        break;
+                    }
+                    fence_after_sync();
+                    const uint32_t a_addr = smem_addr(smem + stage * PAIR_STAGE);
+                    const uint32_t b_addr = a_addr + PAIR_A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++) {
+                        mma_bf16_ss_pair(d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
+                                         (kb > kb0 || k > 0) ? 1u : 0u);
+                    }
+                    mma_commit_pair(&empty[stage], 3);  // frees the stage in both blocks
+                    if (++stage == PAIR_STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (ok) mma_commit_pair(&tfull[acc], 3);  // wakes both blocks' epilogues
+            }
+        }
+        __syncwarp();
+    } else {
+        const int quarter = warp & 3;
+        uint32_t it = 0;
+        int* last_flag = const_cast<int*>(abort_flag) + 1;  // shared word next to the abort flag
+        for (int unit = pair; unit < units; unit += npairs, it++) {
+            const int tile = unit / splits, part = unit % splits;
+            const int m_idx = tile % num_m, n_idx = tile / num_m;
+            const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+            if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) {
+                fail(14);
+                break;
+            }
+            fence_after_sync();
+            const int row_local = quarter * 32 + lane;
+            const int row = m_idx * 2 * BM + (int)rank * BM + row_local;
+            // this block's 128 x BN float32 partial of (tile, part), stored as [BN / 4][128][4] so
+            // that the 32 rows a warp holds make one contiguous 512-byte access per column group
+            float* mine = partials + (((size_t)tile * splits + part) * 2 + rank) * (size_t)(BM * BN) +
+                          (size_t)row_local * 4;
+#pragma unroll 1
+            for (int cc = 0; cc < BN / 32; cc++) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * PAIR_ACC_STRIDE + cc * 32, v);
+                tmem_ld_wait();
+                const int col0 = n_idx * BN + cc * 32;
+                if (splits > 1) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++)
+                        *reinterpret_cast<uint4*>(mine + (size_t)(cc * 8 + j) * (BM * 4)) =
+                            make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                } else if (row < M && col0 < N) {
+                    bf16* dst = y + (size_t)row * ldy + col0;
+                    if (vec_ok && col0 + 32 <= N) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            uint4 o;
+                            o.x = pack2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+                            o.y = pack2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+                            o.z = pack2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+                            o.w = pack2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+                            st16(dst + 8 * j, o);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (col0 + j < N) dst[j] = to_bf16(__uint_as_float(v[j]));
+                    }
+                }
+            }
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                if (leader)
+                    mbar_arrive(&tempty[acc]);
+                else
+                    mbar_arrive_remote(&tempty[acc], 0);
+            }
+            if (splits > 1) {
+                // The unit that finishes last adds the tile's partial sums in part order (so the
+                // result does not depend on which unit that is) and writes the bf16 rows.
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps of this block
+                if (warp == 2 && lane == 0) {
+                    const int done = atomicAdd(&counters[tile * 2 + (int)rank], 1);
+                    *last_flag = done == splits - 1;
+                    if (done == splits - 1) counters[tile * 2 + (int)rank] = 0;  // ready for the next launch
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const bool last = *last_flag != 0;
+                asm volatile("bar.sync 1, 128;" ::: "memory");  // everyone has read the flag before it is reused
+                if (last && row < M) {
+                    __threadfence();
+                    const float* first = partials + (((size_t)tile * splits) * 2 + rank) * (size_t)(BM * BN) +
+                                         (size_t)row_local * 4;
+                    const size_t part_stride = (size_t)2 * BM * BN;
+#pragma unroll 1
+                    for (int cc = 0; cc < BN / 32; cc++) {
+                        const int col0 = n_idx * BN + cc * 32;
+                        if (col0 >= N) break;
+                        float sum[32];
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            const float4 p =
+                                __ldcg(reinterpret_cast<const float4*>(first + (size_t)(cc * 8 + j) * (BM * 4)));
+                            sum[4 * j] = p.x, sum[4 * j + 1] = p.y, sum[4 * j + 2] = p.z, sum[4 * j + 3] = p.w;
+                        }
+                        for (int s = 1; s < splits; s++) {
+#pragma unroll
+                            for (int j = 0; j < 8; j++) {
+                                const float4 p =
+                                    __ldcg(reinterpret_cast<const float4*>(first + s * part_stride +
+                                                                           (size_t)(cc * 8 + j) * (BM * 4)));
+                                sum[4 * j] += p.x, sum[4 * j + 1] += p.y, sum[4 * j + 2] += p.z, sum[4 * j + 3] += p.w;
+                            }
+                        }
+                        bf16* dst = y + (size_t)row * ldy + col0;
+                        if (vec_ok && col0 + 32 <= N) {
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                uint4 o;
+                                o.x = pack2(sum[8 * j + 0], sum[8 * j + 1]);
+                                o.y = pack2(sum[8 * j + 2], sum[8 * j + 3]);
+                                o.z = pack2(sum[8 * j + 4], sum[8 * j + 5]);
+                                o.w = pack2(sum[8 * j + 6], sum[8 * j + 7]);
+                                st16(dst + 8 * j, o);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (col0 + j < N) dst[j] = to_bf16(sum[j]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    if (*abort_flag) __nanosleep(1000000);
+    fence_before_sync();
+    __syncthreads();
+    cluster_sync();  // the leader's MMAs read the peer's shared memory until here
+    if (warp == 2) tmem_dealloc_pair(tmem_base, PAIR_TMEM_COLS);
+}
+
 // ---- host side ----
 
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -267,6 +529,7 @@ bool tensor_map(const void* ptr, int rows, int K, int box_rows, CUtensorMap* out
 struct DeviceInfo {
     int sms = 0;
     bool smem_set[3] = {false, false, false};
+    bool pair_smem_set = false;
 };
 
 DeviceInfo* device_info(cudaError_t* err) {
@@ -304,6 +567,75 @@ int launch(const void* x, const void* w, void* y, int M, int N, int K, int ldy, 
     return cudaGetLastError();
 }
 
+// Plan for the pair kernel: the column-block width (a multiple of 32) and the number of
+// K splits that minimise waves x k-blocks per unit x per-k-block cost. Measured: a
+// k-block's time depends only weakly on the width (the 128 rows of x each block loads
+// dominate), roughly as bn + 400; a unit costs about 6 k-blocks of fill, drain and partial
+// traffic on top of its own. Splitting needs float32 room for every partial tile.
+struct PairPlan {
+    int bn, splits;
+};
+
+PairPlan pair_plan(int M, int N, int K, int pairs, size_t partial_bytes, int counter_slots) {
+    const long num_m = (M + 2 * BM - 1) / (2 * BM);
+    const int kblocks = (K + BK - 1) / BK;
+    int force_bn = 0, force_s = 0;  // tuning knobs
+    if (const char* f = getenv("S1_GEMM_BN")) force_bn = atoi(f);
+    if (const char* f = getenv("S1_GEMM_SPLITS")) force_s = atoi(f);
+    PairPlan best{256, 1};
+    double best_cost = 1e30;
+    for (int bn = 256; bn >= 64; bn -= 32) {
+        if (force_bn && bn != force_bn) continue;
+        const long tiles = num_m * ((N + bn - 1) / bn);
+        for (int s = 1; s <= 8; s++) {
+            if (force_s && s != force_s) continue;
+            const int kb_per = (kblocks + s - 1) / s;
+            if (s > 1) {
+                if ((s - 1) * kb_per >= kblocks) continue;  // an empty part
+                if (kb_per < 8) continue;
+                if ((size_t)tiles * s * 2 * BM * bn * 4 > partial_bytes || tiles * 2 > counter_slots) continue;
+            }
+            const long waves = (tiles * s + pairs - 1) / pairs;
+            // measured: writing, fencing and re-reading the partial tiles costs about 25 k-blocks' time
+            const double cost = ((double)waves * (kb_per + 6) + (s > 1 ? 25.0 : 0.0)) * (bn + 400);
+            if (cost < best_cost - 1e-9) {
+                best_cost = cost;
+                best = PairPlan{bn, s};
+            }
+        }
+    }
+    return best;
+}
+
+int launch_pair(const void* x, const void* w, void* y, int M, int N, int K, int ldy, DeviceInfo* info,
+                void* partials, size_t partial_bytes, int* counters, int counter_slots, cudaStream_t st) {
+    if (!info->pair_smem_set) {
+        const cudaError_t e =
+            cudaFuncSetAttribute(gemm_tc5_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
+        if (e != cudaSuccess) return e;
+        info->pair_smem_set = true;
+    }
+    const int pairs = info->sms / 2;
+    const PairPlan plan = pair_plan(M, N, K, pairs, partials && counters ? partial_bytes : 0, counter_slots);
+    const int bn = plan.bn;
+    CUtensorMap mx, mw;
+    if (!tensor_map(x, M, K, BM, &mx) || !tensor_map(w, N, K, bn / 2, &mw)) return CS1_ERR_TENSOR_MAP;
+    const int units = ((M + 2 * BM - 1) / (2 * BM)) * ((N + bn - 1) / bn) * plan.splits;
+    const int grid = 2 * (units < pairs ? units : pairs);
+    const int vec_ok = (ldy % 8 == 0) && aligned16(y);
+    gemm_tc5_pair_kernel<<<grid, GEMM_THREADS, PAIR_SMEM, st>>>(mx, mw, static_cast<bf16*>(y), M, N, K, ldy, vec_ok, bn,
+                                                               plan.splits, static_cast<float*>(partials), counters);
+    return cudaGetLastError();
+}
+
+bool pair_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("S1_GEMM_PAIR");
+        return !(v && v[0] == '0');
+    }();
+    return on;
+}
+
 }  // namespace
 }  // namespace s1
 
@@ -315,10 +647,16 @@ bool s1_gemm_tc5_supported(const void* x, const void* w, const void* y, int M, i
     return M > 0 && N > 0 && K >= 64 && K % 8 == 0 && aligned16(x) && aligned16(w);
 }
 
-int s1_gemm_tc5(const void* x, const void* w, void* y, int M, int N, int K, int ldy, cudaStream_t st) {
+int s1_gemm_tc5(const void* x, const void* w, void* y, int M, int N, int K, int ldy, const S1GemmScratch* scratch,
+                cudaStream_t st) {
     cudaError_t err;
     DeviceInfo* info = device_info(&err);
     if (!info) return err;
+    // More than one row block: the CTA-pair kernel (S1_GEMM_PAIR=0 keeps the single-block one, for A/B runs).
+    if (M > BM && pair_enabled())
+        return launch_pair(x, w, y, M, N, K, ldy, info, scratch ? scratch->partials : nullptr,
+                           scratch ? scratch->partial_bytes : 0, scratch ? scratch->counters : nullptr,
+                           scratch ? scratch->counter_slots : 0, st);
     // Pick the widest column block that still gives every SM work; a wider block moves less
     // shared-memory traffic per flop, a narrower one fills partial waves better.
     const int num_m = (M + BM - 1) / BM;

@@ -1,10 +1,23 @@
 // Internal interface of the tcgen05 GEMM engine (gemm_tc5.cu), used by gemm.cu.
 #pragma once
 #include <cuda_runtime.h>
+#include <stddef.h>
+
+// Device memory a GEMM handle lends the engine for K-split problems: float32 partial tiles
+// and one counter per (tile, block of the pair). The counters must be zero when a launch
+// starts; the kernel leaves them zero. Two launches that may overlap on the GPU must not
+// share it (one handle serves one stream, as in the reference).
+struct S1GemmScratch {
+    void* partials;
+    size_t partial_bytes;
+    int* counters;
+    int counter_slots;
+};
 
 // True when the tcgen05 kernel can run this problem: K a multiple of 8 (16-byte rows for the
 // TMA tensor maps) and at least 64, x and w 16-byte aligned.
 bool s1_gemm_tc5_supported(const void* x, const void* w, const void* y, int M, int N, int K, int ldy);
-// Queues y [M, N] (rows of ldy) = x [M, K] * w [N, K]^T on `stream`. Returns 0, a cudaError_t
-// or CS1_ERR_TENSOR_MAP.
-int s1_gemm_tc5(const void* x, const void* w, void* y, int M, int N, int K, int ldy, cudaStream_t stream);
+// Queues y [M, N] (rows of ldy) = x [M, K] * w [N, K]^T on `stream`. scratch may be null (no
+// K split is used then). Returns 0, a cudaError_t or CS1_ERR_TENSOR_MAP.
+int s1_gemm_tc5(const void* x, const void* w, void* y, int M, int N, int K, int ldy, const S1GemmScratch* scratch,
+                cudaStream_t stream);

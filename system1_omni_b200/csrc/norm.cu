@@ -104,32 +104,47 @@ int launch_norm(void* residual, const void* delta, const void* w, void* out, int
 }
 
 // Gated RMSNorm, D = 128: 16 lanes per (token, head) row, 8 values per lane.
-constexpr int GN_ROWS_PER_BLOCK = 16;
+// Each lane group takes GN_ROWS_PER_GROUP rows 16 apart and requests all of them before
+// reducing, to keep eight 16-byte loads in flight per thread.
+constexpr int GN_GROUPS = 16, GN_ROWS_PER_GROUP = 4;
+constexpr int GN_ROWS_PER_BLOCK = GN_GROUPS * GN_ROWS_PER_GROUP;
 
-__global__ void __launch_bounds__(GN_ROWS_PER_BLOCK * 16)
+__global__ void __launch_bounds__(GN_GROUPS * 16)
     gated_rms_norm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ z, int ldz, const bf16* __restrict__ w,
                           bf16* __restrict__ out, int rows, int H, float eps) {
     constexpr int D = 128;
-    const int row = blockIdx.x * GN_ROWS_PER_BLOCK + threadIdx.x / 16, sub = threadIdx.x & 15;
-    const bool live = row < rows;
-    const int rr = live ? row : rows - 1;
-    const size_t base = (size_t)rr * D + sub * 8;
-    const size_t zbase = (size_t)(rr / H) * ldz + (size_t)(rr % H) * D + sub * 8;
-    float v[8], zv[8], wv[8];
-    unpack8(ld16_stream(x + base), v);
-    unpack8(ld16_stream(z + zbase), zv);
-    unpack8(ld16(w + sub * 8), wv);
-    float ss = 0.f;
+    const int group = threadIdx.x / 16, sub = threadIdx.x & 15;
+    uint4 xv[GN_ROWS_PER_GROUP], zv[GN_ROWS_PER_GROUP];
+    size_t base[GN_ROWS_PER_GROUP];
+    bool live[GN_ROWS_PER_GROUP];
 #pragma unroll
-    for (int e = 0; e < 8; e++) ss += v[e] * v[e];
-    const float inv = rsqrtf(warp_sum<16>(ss) / D + eps);
-#pragma unroll
-    for (int e = 0; e < 8; e++) {
-        const float normed = rbf(v[e] * inv);
-        const float scaled = rbf(wv[e] * normed);
-        v[e] = scaled * silu(zv[e]);
+    for (int r = 0; r < GN_ROWS_PER_GROUP; r++) {
+        const int row = blockIdx.x * GN_ROWS_PER_BLOCK + r * GN_GROUPS + group;
+        live[r] = row < rows;
+        const int rr = live[r] ? row : rows - 1;
+        base[r] = (size_t)rr * D + sub * 8;
+        xv[r] = ld16_stream(x + base[r]);
+        zv[r] = ld16_stream(z + (size_t)(rr / H) * ldz + (size_t)(rr % H) * D + sub * 8);
     }
-    if (live) st16(out + base, pack8(v));
+    float wv[8];
+    unpack8(ld16(w + sub * 8), wv);
+#pragma unroll
+    for (int r = 0; r < GN_ROWS_PER_GROUP; r++) {
+        float v[8], g[8];
+        unpack8(xv[r], v);
+        unpack8(zv[r], g);
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; e++) ss += v[e] * v[e];
+        const float inv = rsqrtf(warp_sum<16>(ss) / D + eps);
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const float normed = rbf(v[e] * inv);
+            const float scaled = rbf(wv[e] * normed);
+            v[e] = scaled * silu_fast(g[e]);
+        }
+        if (live[r]) st16(out + base[r], pack8(v));
+    }
 }
 
 __global__ void gated_rms_norm_scalar_kernel(const bf16* __restrict__ x, const bf16* __restrict__ z, int ldz,
@@ -152,7 +167,7 @@ __global__ void gated_rms_norm_scalar_kernel(const bf16* __restrict__ x, const b
     for (int i = 0; i < PER; i++) {
         const float normed = rbf(v[i] * inv);
         const float scaled = rbf(f32(w[lane * PER + i]) * normed);
-        out[base + i] = to_bf16(scaled * silu(f32(z[zbase + i])));
+        out[base + i] = to_bf16(scaled * silu_fast(f32(z[zbase + i])));
     }
 }
 
@@ -179,7 +194,7 @@ extern "C" int cs1_gated_rms_norm(const void* x, const void* z, int ldz, const v
     if (rows > 0x7fffffffLL) return cudaErrorInvalidValue;
     const bf16 *xp = static_cast<const bf16*>(x), *zp = static_cast<const bf16*>(z), *wp = static_cast<const bf16*>(w);
     if (ldz % 8 == 0 && aligned16(x) && aligned16(z) && aligned16(w) && aligned16(out)) {
-        gated_rms_norm_kernel<<<(unsigned)((rows + GN_ROWS_PER_BLOCK - 1) / GN_ROWS_PER_BLOCK), GN_ROWS_PER_BLOCK * 16,
+        gated_rms_norm_kernel<<<(unsigned)((rows + GN_ROWS_PER_BLOCK - 1) / GN_ROWS_PER_BLOCK), GN_GROUPS * 16,
                                 0, as_stream(stream)>>>(xp, zp, ldz, wp, static_cast<bf16*>(out), (int)rows, H, eps);
     } else {
         gated_rms_norm_scalar_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, as_stream(stream)>>>(

@@ -1,5 +1,5 @@
 // Blackwell (sm_100a) primitives in inline PTX: mbarriers with bounded waits, TMA tile
-// loads (never cluster-multicast), tensor-memory allocation, tcgen05 MMA issue / commit /
+// loads (each block fetches its own tiles), tensor-memory allocation, tcgen05 MMA issue / commit /
 // accumulator loads, and the shared-memory and instruction descriptors they take.
 //
 // Every wait is bounded by wall time: a wait that runs out returns false, the caller
@@ -150,6 +150,74 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- CTA pairs (cta_group::2): two blocks of a cluster share one MMA of 256 rows ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Within a cluster the shared::cluster address of rank r's copy of a shared::cta address is
+// the address with r in bits 24 and up; clearing bit 24 names the pair leader's copy.
+constexpr uint32_t PAIR_LEADER_MASK = 0xFEFFFFFFu;
+// Arrive on the barrier at the same offset in the shared memory of cluster rank `rank`.
+__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank) {
+    asm volatile(
+        "{\n"
+        ".reg .b32 remote;\n"
+        "mapa.shared::cluster.u32 remote, %0, %1;\n"
+        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remote];\n"
+        "}\n" ::"r"(smem_addr(bar)),
+        "r"(rank)
+        : "memory");
+}
+// Tile load into this block's shared memory whose bytes are counted on the pair leader's
+// barrier (same offset). Each block of the pair loads its own part; nothing is broadcast.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], "
+        "[%4];" ::"r"(smem_addr(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(smem_addr(bar) & PAIR_LEADER_MASK)
+        : "memory");
+}
+// One warp in each block of the pair allocates the same columns in both tensor memories.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(dst)), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+// D[256 x N over both blocks' tensor memory] (+)= A * B^T: A rows 0-127 from the leader's
+// shared memory and 128-255 from its peer's, B rows 0..N/2 from the leader and the rest
+// from the peer, all at the offsets the descriptors name. Issued by one thread of the leader.
+__device__ __forceinline__ void mma_bf16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// One arrival on the barrier at this offset in every block of `mask` once the MMAs issued so
+// far have finished.
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar, uint16_t mask) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+            smem_addr(bar)),
+        "h"(mask)
+        : "memory");
+}
 
 }  // namespace tc5
 }  // namespace s1

@@ -162,7 +162,7 @@ def gemm(b, out):
         x = b.bf16(M * K)
         y = L.DeviceBuffer(M * N * 2)
         row = {"model": model, "proj": proj, "M": M, "N": N, "K": K, "flops": 2.0 * M * N * K, "weight_copies": n}
-        for engine, call in (("tcgen05", lambda i: lib.s1_gemm_tcgen05(x.at(), ws[i].at(), y.at(), M, N, K, N, st)),
+        for engine, call in (("tcgen05", lambda i: lib.s1_gemm_tcgen05(handle, x.at(), ws[i].at(), y.at(), M, N, K, N, st)),
                              ("cublaslt", lambda i: lib.s1_gemm_cublaslt(handle, x.at(), ws[i].at(), y.at(), M, N, K,
                                                                          N, st))):
             us = b.time(call, n)

@@ -195,6 +195,10 @@ class Model:
     def enable_graphs(self, on=True):
         L.check(L.load().s1_model_enable_graphs(self.handle, int(on)), "graphs")
 
+    def set_exact_packing(self, on=True):
+        """Bit-identical results for a prompt alone or in a pack (slower); see s1_executor.h."""
+        L.check(L.load().s1_model_set_exact_packing(self.handle, int(on)), "exact packing")
+
     def graph_stats(self):
         r, c, e = C.c_int(), C.c_int(), C.c_int()
         L.check(L.load().s1_model_graph_stats(self.handle, C.byref(r), C.byref(c), C.byref(e)), "graph stats")

@@ -491,23 +491,46 @@ def test_gemm_cublaslt_matches_reference(cs1, stream, M, N, K, pad):
 def test_gemm_tcgen05_matches_reference(cs1, stream, M, N, K, pad):
     x, w, ldy = gemm_case(M, N, K, pad)
     xd, wd = dev(x, stream), dev(w, stream)
-    y = dev(np.full((M, ldy), 0x7FC0, np.uint16), stream)
-    L.check(cs1.s1_gemm_tcgen05(xd.at(), wd.at(), y.at(), M, N, K, ldy, stream.handle), "gemm")
-    got = host(y, (M, ldy), stream)
-    assert L.gemm_status() == 0, "a bounded wait inside the tcgen05 GEMM gave up"
-    check_gemm(got, x, w, N)
-    assert np.all(got[:, N:] == 0x7FC0)
+    handle = cs1.cs1_gemm_create(32 << 20)
+    # without a handle (no K split possible) and with one (the planner may split K), twice
+    # with the handle so that the split path's counters are seen to return to zero
+    for gemm in (None, handle, handle):
+        y = dev(np.full((M, ldy), 0x7FC0, np.uint16), stream)
+        L.check(cs1.s1_gemm_tcgen05(gemm, xd.at(), wd.at(), y.at(), M, N, K, ldy, stream.handle), "gemm")
+        got = host(y, (M, ldy), stream)
+        assert L.gemm_status() == 0, "a bounded wait inside the tcgen05 GEMM gave up"
+        check_gemm(got, x, w, N)
+        assert np.all(got[:, N:] == 0x7FC0)
+    cs1.cs1_gemm_destroy(handle)
+
+
+@pytest.mark.parametrize("M,N,K", [(1024, 2560, 4096), (1024, 2560, 9728), (512, 5120, 2560), (300, 2560, 2048)])
+def test_gemm_k_split_is_deterministic(cs1, stream, M, N, K):
+    """Shapes with too few tiles for the 74 block pairs split K; the partial sums are added in
+    a fixed order by whichever unit finishes last, so repeated runs agree bit for bit."""
+    x, w, _ = gemm_case(M, N, K, 0, seed=3)
+    xd, wd = dev(x, stream), dev(w, stream)
+    handle = cs1.cs1_gemm_create(32 << 20)
+    outs = []
+    for _ in range(3):
+        y = L.DeviceBuffer(M * N * 2)
+        L.check(cs1.cs1_gemm(handle, xd.at(), wd.at(), y.at(), M, N, K, N, stream.handle), "gemm")
+        outs.append(host(y, (M, N), stream))
+    assert L.gemm_status() == 0
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+    check_gemm(outs[0], x, w, N)
+    cs1.cs1_gemm_destroy(handle)
 
 
 def test_gemm_rows_do_not_depend_on_the_row_count(cs1, stream):
-    """A prompt's rows come out the same whether it runs alone or inside a pack: the property
-    the reference buys by splitting its out/down GEMMs per sequence (model.rs:723-739)."""
+    """Without a K split a row comes out the same however many rows the call has - the
+    property the reference buys by running its out/down GEMMs per sequence (model.rs:723-739)."""
     M, N, K = 300, 2560, 4096
     x, w, _ = gemm_case(M, N, K, 0, seed=5)
     xd, wd = dev(x, stream), dev(w, stream)
     full, part = L.DeviceBuffer(M * N * 2), L.DeviceBuffer(M * N * 2)
-    L.check(cs1.s1_gemm_tcgen05(xd.at(), wd.at(), full.at(), M, N, K, N, stream.handle), "gemm")
-    L.check(cs1.s1_gemm_tcgen05(xd.at(100 * K * 2), wd.at(), part.at(), 37, N, K, N, stream.handle), "gemm")
+    L.check(cs1.s1_gemm_tcgen05(None, xd.at(), wd.at(), full.at(), M, N, K, N, stream.handle), "gemm")
+    L.check(cs1.s1_gemm_tcgen05(None, xd.at(100 * K * 2), wd.at(), part.at(), 37, N, K, N, stream.handle), "gemm")
     assert L.gemm_status() == 0
     assert np.array_equal(host(full, (M, N), stream)[100:137], host(part, (37, N), stream))
 

@@ -73,6 +73,30 @@ def test_packed_equals_independent_execution(setup):
     assert np.array_equal(again, packed[perm])
 
 
+def test_exact_packing_on_a_shape_that_splits_k(cs1):
+    """A wider decoder whose hidden-size projections have too few tiles for the GPU and so
+    split K by the row count: with exact packing a prompt's result is bit-identical alone or
+    packed; without it the two agree within rounding (the reference gates 0.01 on logits)."""
+    cfg = tiny_config(layer_types=("linear_attention", "full_attention"), hidden=1024, intermediate=4096, heads=8,
+                      kv_heads=2, lin_k=4, lin_v=8, vocab=256)
+    model = M.Model(cfg, device=0)
+    model.init_random(seed=5)
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, cfg.vocab, n).tolist() for n in (300, 129, 40, 530)]
+    try:
+        model.set_exact_packing(True)
+        packed = model.forward_batch(prompts)
+        alone = np.stack([model.forward(p) for p in prompts])
+        assert np.array_equal(packed, alone)
+        model.set_exact_packing(False)
+        fast = model.forward_batch(prompts)
+        assert np.all(np.isfinite(fast))
+        for s in range(len(prompts)):
+            assert rel_l2(fast[s], alone[s]) < 1e-2
+    finally:
+        model.close()
+
+
 def test_graph_replay_equals_eager(setup):
     # multimodal_graph.rs: replay == eager bit-exact; changed ids under replay; 65 shapes evict first in first out
     cfg, weights, model = setup
