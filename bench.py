@@ -38,6 +38,8 @@ if ROOT not in sys.path:
 
 TOKENS = 1024
 N_CLASSES = 16
+WORKLOAD = ("cfg2: 4B-shaped hybrid decoder (32 layers 3:1 GDN/attention, hidden 2560, MLP 9728, vocab 151936, "
+            "16-class head), 1 request x 1024 uniform-random ids per GPU")
 FAMILIES = ["gemm", "gdn_prefill", "attention", "gdn_conv", "gdn_gates", "rms_norm", "gated_rms_norm", "silu_mul",
             "attn_prep", "other"]
 
@@ -176,7 +178,8 @@ def run_reference(args, rank, world):
     line = {"impl": "reference", "metric": "prefill tokens/s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
             "steps": len(secs), "warmup": min(args.warmup, 1), "ms_per_step": step * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "cfg2: 4B-shaped hybrid decoder, 1 request x 1024 tokens"},
+            "config": {"workload": WORKLOAD, "layers": 32, "tokens_per_gpu": TOKENS,
+                       "weights": "N(0,0.02) bf16, generated on the host"},
             "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -325,9 +328,7 @@ def main():
         "metric": "prefill tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "cfg2: 4B-shaped hybrid decoder (32 layers 3:1 GDN/attention, hidden 2560, MLP 9728, "
-                               "vocab 151936, 16-class head), 1 request x 1024 uniform-random ids per GPU",
-                   "layers": cfg.n_layers, "tokens_per_gpu": TOKENS, "weights": "N(0,0.02) bf16, generated on device",
+        "config": {"workload": WORKLOAD, "layers": cfg.n_layers, "tokens_per_gpu": TOKENS, "weights": "N(0,0.02) bf16, generated on device",
                    "l2": f"per step {model.weight_bytes / 1e9:.1f} GB of weights stream through a 126 MB L2",
                    "graphs": bool(args.graphs), "gemm_engine": engine},
         "e2e": {"value": world * TOKENS / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,

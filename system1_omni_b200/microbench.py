@@ -203,6 +203,31 @@ def gdn(b, out):
              "workspace_MiB": lib.cs1_gdn_workspace_floats(T, H) * 4 / 2 ** 20})
 
 
+def layer(b, out):
+    """Whole Gated DeltaNet layer (in_proj, conv, gates, delta rule, gated norm, out_proj) in microseconds."""
+    from .gdn_layer import GdnLayer
+    for name, hidden, hk, hv, T in [("cfg1", 2048, 16, 16, 2048), ("4B", 2560, 16, 32, 1024),
+                                    ("9B", 4096, 16, 32, 1024), ("27B", 5120, 16, 48, 1024),
+                                    ("27B", 5120, 16, 48, 4096)]:
+        lay = GdnLayer(hidden, hk, hv, max_tokens=T, stream=b.stream)
+        for buf, std in ((lay.w_in, 0.02), (lay.w_out, 0.02), (lay.w_conv, 0.3), (lay.a_log, 1.0), (lay.dt_bias, 0.1),
+                         (lay.w_norm, 1.0)):
+            a = np.abs(b.rng.standard_normal(buf.nbytes // 2, dtype=np.float32)) * np.float32(std)
+            bits = (a.view(np.uint32) >> 16).astype(np.uint16)
+            L.check(b.lib.cs1_upload(buf.at(), bits.ctypes.data_as(C.c_void_p), bits.nbytes, b.stream.handle), "upload")
+        x = b.bf16(T * hidden)
+
+        def call(i):
+            lay.forward(x.at(), T)
+            return 0
+
+        us = b.time(call, 1)
+        gf = 2.0 * T * hidden * (lay.gdn_in + lay.vd)
+        out({"op": "gdn_layer", "model": name, "hidden": hidden, "k_heads": hk, "v_heads": hv, "T": T, "us": us,
+             "tokens_per_s": T / us * 1e6, "projection_TFLOP/s_if_all_time": gf / us / 1e6})
+        lay.close()
+
+
 def attention(b, out):
     lib, st = b.lib, b.stream.handle
     for dh, hq, hk in [(128, 16, 4), (128, 24, 4), (256, 16, 4), (256, 24, 4)]:
@@ -219,7 +244,7 @@ def attention(b, out):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", default="all", choices=["elementwise", "gemm", "gdn", "attention", "all"])
+    ap.add_argument("--what", default="all", choices=["elementwise", "gemm", "gdn", "layer", "attention", "all"])
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--out", default=None)
@@ -239,7 +264,8 @@ def main():
         if sink:
             sink.write(line + "\n")
 
-    for name, fn in (("elementwise", elementwise), ("gemm", gemm), ("gdn", gdn), ("attention", attention)):
+    for name, fn in (("elementwise", elementwise), ("gemm", gemm), ("gdn", gdn), ("layer", layer),
+                     ("attention", attention)):
         if args.what in (name, "all"):
             fn(b, out)
     if sink:
