@@ -35,6 +35,11 @@ int s1_gemm_cublaslt(void* gemm, const void* x, const void* w, void* y, int M, i
 int s1_gemm_unsplit(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream);
 /* gemm: a cs1_gemm_create handle whose workspace the K-split path may use, or null (no split). */
 int s1_gemm_tcgen05(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream);
+/* act [M, I] (rows of ld) = silu(x w[0:I]^T) * (x w[I:2I]^T) in one kernel, bit-identical to cs1_gemm
+ * into [M, 2 I] followed by cs1_silu_mul (the reference's MLP sequence, model.rs:1301-1316).
+ * CS1_ERR_UNSUPPORTED when the tcgen05 engine cannot take the problem (M <= 128, K % 8 != 0, other
+ * engine selected): run the two operators then. */
+int s1_gemm_swiglu(void* gemm, const void* x, const void* w, void* act, int M, int I, int K, int ld, void* stream);
 /* Waits for the device, returns in *code the error word of the tcgen05 GEMM (0 = no bounded
  * wait gave up) and clears it. */
 int s1_gemm_tc5_status(int* code);
@@ -76,6 +81,9 @@ int s1_model_enable_graphs(void* model, int on);
  * it off every GEMM runs once over the pack and may split K by the row count: faster, and
  * equal to single execution within rounding (the reference's gate is 0.01 on the logits). */
 int s1_model_set_exact_packing(void* model, int on);
+/* The MLP's gate/up projection and SiLU-multiply as one kernel (s1_gemm_swiglu; on by default,
+ * same bits as the two operators). Off: always the reference's two-operator sequence. */
+int s1_model_set_fused_mlp(void* model, int on);
 int s1_model_graph_stats(void* model, int* replays, int* captures, int* enabled);
 
 /* Model::forward_batch (model.rs:769-823): prefill a pack of independent prompts

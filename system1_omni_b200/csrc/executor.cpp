@@ -80,6 +80,7 @@ struct Model {
     Scratch s;
     bool graph_enabled = false;
     bool exact_packing = false;
+    bool fuse_swiglu = true;  // gate/up GEMM and SiLU-multiply as one kernel where the engine supports it
     int replays = 0, captures = 0;
     std::deque<std::pair<std::vector<int>, void*>> graphs;
     int* ends_host = nullptr;  // pinned ring of ENDS_RING slots of cap ints
@@ -403,8 +404,20 @@ int run(Model* m, const int* lengths, int nseq, char* dump) {
         }
         S1_OP(S1_FAMILY_NORM, 1,
               cs1_add_rms_norm(s.at(s.res), s.at(s.delta), m->w(ly.post_norm), s.at(s.x), t, h, eps, st));
-        S1_TRY(gemm(m, s.x, ly.gate_up, s.gate_up, t, 2 * I, h));
-        S1_OP(S1_FAMILY_SILU_MUL, 1, cs1_silu_mul(s.at(s.gate_up), 2 * I, s.at(s.act), t, I, st));
+        // gate/up projection and SiLU-multiply: one kernel where the tcgen05 engine takes it
+        // (same bits as the two operators), else the reference's sequence
+        int fused = CS1_ERR_UNSUPPORTED;
+        if (m->fuse_swiglu) {
+            S1_TRY(op(m, S1_FAMILY_GEMM, 0, [&] {
+                fused = s1_gemm_swiglu(m->gemm, s.at(s.x), m->w(ly.gate_up), s.at(s.act), t, I, h, I, st);
+                return fused == CS1_ERR_UNSUPPORTED ? 0 : fused;
+            }));
+            if (fused == 0) m->launches[S1_FAMILY_GEMM] += 1;
+        }
+        if (fused == CS1_ERR_UNSUPPORTED) {
+            S1_TRY(gemm(m, s.x, ly.gate_up, s.gate_up, t, 2 * I, h));
+            S1_OP(S1_FAMILY_SILU_MUL, 1, cs1_silu_mul(s.at(s.gate_up), 2 * I, s.at(s.act), t, I, st));
+        }
         S1_TRY(gemm_rows(m, s.act, ly.down, s.delta, lengths, nseq, h, I));
         const Tensor& next = li + 1 < m->layers.size() ? m->layers[li + 1].input_norm : m->final_norm;
         S1_OP(S1_FAMILY_NORM, 1, cs1_add_rms_norm(s.at(s.res), s.at(s.delta), m->w(next), s.at(s.x), t, h, eps, st));
@@ -581,6 +594,14 @@ int s1_model_set_exact_packing(void* model, int on) {
     if (!m) return S1_ERR_ARGUMENT;
     if (m->exact_packing != (on != 0)) clear_graphs(m);
     m->exact_packing = on != 0;
+    return 0;
+}
+
+int s1_model_set_fused_mlp(void* model, int on) {
+    Model* m = static_cast<Model*>(model);
+    if (!m) return S1_ERR_ARGUMENT;
+    if (m->fuse_swiglu != (on != 0)) clear_graphs(m);
+    m->fuse_swiglu = on != 0;
     return 0;
 }
 

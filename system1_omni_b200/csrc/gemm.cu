@@ -31,6 +31,7 @@ struct Plan {
 
 using Key = std::tuple<int, int, int, int>;  // M, N, K, ldy
 constexpr int COUNTER_SLOTS = 16384;
+constexpr size_t PARTIAL_BYTES = (size_t)48 << 20;
 
 struct Gemm {
     cublasLtHandle_t handle = nullptr;
@@ -38,6 +39,8 @@ struct Gemm {
     size_t workspace_bytes = 0;
     bool use_tc5 = true;
     int* counters = nullptr;
+    void* partials = nullptr;  // float32 partial tiles of the tcgen05 kernel's shared-tile paths
+    size_t partial_bytes = 0;
     std::map<Key, Plan> plans;
     std::mutex lock;
 };
@@ -122,6 +125,12 @@ extern "C" void* cs1_gemm_create(size_t workspace_bytes) {
     }
     const char* engine = getenv("S1_GEMM");
     g->use_tc5 = !(engine && strcmp(engine, "cublaslt") == 0);
+    // Room for two 256 x 256 float32 partial tiles per block pair (37 MiB on 148 SMs). Without
+    // it (allocation refused) the kernel keeps to whole tiles.
+    if (g->use_tc5 && cudaMalloc(&g->partials, PARTIAL_BYTES) == cudaSuccess)
+        g->partial_bytes = PARTIAL_BYTES;
+    else
+        cudaGetLastError();
     return g;
 }
 
@@ -131,13 +140,14 @@ extern "C" void cs1_gemm_destroy(void* gemm) {
     for (auto& kv : g->plans) destroy(kv.second);
     if (g->workspace) cudaFree(g->workspace);
     if (g->counters) cudaFree(g->counters);
+    if (g->partials) cudaFree(g->partials);
     cublasLtDestroy(g->handle);
     delete g;
 }
 
 namespace {
 S1GemmScratch scratch_of(Gemm* g) {
-    return S1GemmScratch{g->workspace, g->workspace_bytes, g->counters, COUNTER_SLOTS};
+    return S1GemmScratch{g->partials, g->partial_bytes, g->counters, COUNTER_SLOTS};
 }
 }  // namespace
 
@@ -168,6 +178,19 @@ extern "C" int s1_gemm_unsplit(void* gemm, const void* x, const void* w, void* y
 extern "C" int s1_gemm_engine(void* gemm, const void* x, const void* w, int M, int N, int K) {
     Gemm* g = static_cast<Gemm*>(gemm);
     return g && g->use_tc5 && s1_gemm_tc5_supported(x, w, nullptr, M, N, K, N) ? 1 : 0;
+}
+
+// The MLP's first half as one kernel on the tcgen05 engine: act [M, I] (rows of ld) =
+// silu(x w[0:I]^T) * (x w[I:2I]^T), bit-identical to cs1_gemm into a [M, 2 I] buffer followed by
+// cs1_silu_mul. Returns CS1_ERR_UNSUPPORTED when the engine cannot take the problem (other
+// engine selected, at most 128 rows, K not a multiple of 8); the caller then runs the two operators.
+extern "C" int s1_gemm_swiglu(void* gemm, const void* x, const void* w, void* act, int M, int I, int K, int ld,
+                              void* stream) {
+    Gemm* g = static_cast<Gemm*>(gemm);
+    if (!g || M < 0 || I <= 0 || K <= 0 || ld < I) return cudaErrorInvalidValue;
+    if (M == 0) return cudaSuccess;
+    if (!g->use_tc5 || !s1_gemm_tc5_swiglu_supported(x, w, M, I, K)) return CS1_ERR_UNSUPPORTED;
+    return s1_gemm_tc5_swiglu(x, w, act, M, I, K, ld, static_cast<cudaStream_t>(stream));
 }
 
 // Engine-pinned entry points for the GEMM benchmark and the parity tests.

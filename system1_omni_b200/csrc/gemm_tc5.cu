@@ -211,24 +211,100 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 }
 
 // ---- CTA-pair kernel: 256 x BN tiles on two blocks of a cluster ----
-constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_MAX_STAGES = 12;
+constexpr int PAIR_DATA_BYTES = 7 * 32768;         // the stage ring: as many stages as fit (7 at BN = 256, 11 at 64)
 constexpr int PAIR_A_BYTES = BM * BK * 2;          // this block's 128 rows of x
-constexpr int PAIR_B_MAX = 128 * BK * 2;           // this block's half of the w tile, BN / 2 <= 128 rows
-constexpr int PAIR_STAGE = PAIR_A_BYTES + PAIR_B_MAX;
-constexpr int PAIR_SMEM = PAIR_STAGES * PAIR_STAGE + 256 + 1024;
+constexpr int PAIR_SMEM = PAIR_DATA_BYTES + 256 + 1024;
 constexpr int PAIR_TMEM_COLS = 512;                // two accumulators 256 columns apart
 constexpr int PAIR_ACC_STRIDE = 256;
 
+// Tile index -> (row block, column block) for the pair kernel. Blocks that run at the same time
+// take consecutive indices and fetch the same k-block at the same time; requests for one
+// x or w tile then coincide in L2. Walking 8 row blocks per column block (instead of all of
+// them) makes the 74 tiles in flight an 8 x 9 patch: 17 distinct operand tiles per k-block
+// rather than num_m + 74 / num_m.
+__device__ __forceinline__ void pair_tile_coords(int tile, int num_m, int num_n, int& m, int& n) {
+    constexpr int GM = 8;
+    const int per_group = GM * num_n;
+    const int group = tile / per_group, in = tile - group * per_group;
+    const int first = group * GM;
+    const int gm = min(GM, num_m - first);
+    m = first + in % gm;
+    n = in / gm;
+}
+
+// One piece of work of a block pair: k-blocks [kb0, kb1) of one output tile. When the tile's
+// K range is shared (nparts > 1) the piece is contributor `part` of `nparts` and leaves a
+// float32 partial tile in slot slot_of(part); whichever contributor finishes last adds the
+// slots in part order, so the sum does not depend on the arrival order.
+struct Piece {
+    int tile, kb0, kb1, part, nparts;
+    int mode, first, splits;
+    __device__ __forceinline__ size_t slot_of(int j) const {
+        return mode == 0 ? (size_t)tile * splits + j : (size_t)(first + j) * 2 + (j == 0 ? 1 : 0);
+    }
+};
+
+// Two ways of handing pieces to the pairs, identical in the three roles of a block.
+//   mode 0: a tile's k-blocks are cut into `splits` equal parts (1 = whole tiles); the parts
+//           go round-robin over the pairs.
+//   mode 1: the k-blocks of all tiles, laid end to end, are cut into one contiguous run per
+//           pair (lengths differ by at most one), and a run is cut at tile boundaries. A
+//           pair has at most two pieces that share their tile: its first (a tile entered
+//           part-way, slot 2*pair) and its last (a tile left before its end, slot 2*pair+1).
+struct PieceIter {
+    int mode, tiles, kblocks, splits, kb_per, npairs, pair;
+    int unit;
+    long long g, g1, per, extra;
+    __device__ __forceinline__ void init(int mode_, int tiles_, int kblocks_, int splits_, int pair_, int npairs_) {
+        mode = mode_, tiles = tiles_, kblocks = kblocks_, splits = splits_, pair = pair_, npairs = npairs_;
+        kb_per = (kblocks + splits - 1) / splits;
+        unit = pair;
+        const long long total = (long long)tiles * kblocks;
+        per = total / npairs, extra = total % npairs;
+        g = (long long)pair * per + (pair < extra ? pair : extra);
+        g1 = g + per + (pair < extra ? 1 : 0);
+    }
+    __device__ __forceinline__ int owner(long long at) const {
+        const long long cut = extra * (per + 1);
+        return (int)(at < cut ? at / (per + 1) : extra + (at - cut) / per);
+    }
+    __device__ __forceinline__ bool next(Piece& p) {
+        p.mode = mode, p.splits = splits;
+        if (mode == 0) {
+            if (unit >= tiles * splits) return false;
+            p.tile = unit / splits, p.part = unit % splits, p.nparts = splits, p.first = 0;
+            p.kb0 = p.part * kb_per;
+            p.kb1 = min(kblocks, (p.part + 1) * kb_per);
+            unit += npairs;
+            return true;
+        }
+        if (g >= g1) return false;
+        p.tile = (int)(g / kblocks);
+        p.kb0 = (int)(g - (long long)p.tile * kblocks);
+        p.kb1 = (int)min((long long)kblocks, p.kb0 + (g1 - g));
+        if (p.kb0 == 0 && p.kb1 == kblocks) {
+            p.part = 0, p.nparts = 1, p.first = pair;
+        } else {
+            p.first = owner((long long)p.tile * kblocks);
+            p.nparts = owner((long long)(p.tile + 1) * kblocks - 1) - p.first + 1;
+            p.part = pair - p.first;
+        }
+        g += p.kb1 - p.kb0;
+        return true;
+    }
+};
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
-                         bf16* __restrict__ y, int M, int N, int K, int ldy, int vec_ok, int BN, int splits,
-                         float* __restrict__ partials, int* __restrict__ counters) {
+                         bf16* __restrict__ y, int M, int N, int K, int ldy, int vec_ok, int BN, int splits, int mode,
+                         float* __restrict__ partials, int* __restrict__ counters, int swiglu) {
     using namespace tc5;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + PAIR_STAGES * PAIR_STAGE);  // used in the leader only
-    uint64_t* empty = full + PAIR_STAGES;                                           // one copy per block
-    uint64_t* tfull = empty + PAIR_STAGES;                                          // one copy per block
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + PAIR_DATA_BYTES);  // used in the leader only
+    uint64_t* empty = full + PAIR_MAX_STAGES;                              // one copy per block
+    uint64_t* tfull = empty + PAIR_MAX_STAGES;                             // one copy per block
     uint64_t* tempty = tfull + 2;                                                   // used in the leader only
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -237,7 +313,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < PAIR_STAGES; s++) {
+        for (int s = 0; s < PAIR_MAX_STAGES; s++) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
@@ -260,14 +336,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int num_m = (M + 2 * BM - 1) / (2 * BM), num_n = (N + BN - 1) / BN;
+    // swiglu: w is [gate (N rows) | up (N rows)]; a tile pairs BN / 2 gate columns (loaded by the
+    // pair's first block) with the same BN / 2 up columns (second block), so both land in one
+    // accumulator and the epilogue writes BN / 2 columns of silu(gate) * up.
+    const int num_m = (M + 2 * BM - 1) / (2 * BM), num_n = swiglu ? (N + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
     const int tiles = num_m * num_n, kblocks = (K + BK - 1) / BK;
-    // A work unit is one tile's k-blocks [kb0, kb1): the whole K range, or one of `splits`
-    // equal parts whose float32 partial sums are combined by the last unit to finish.
-    const int units = tiles * splits, kb_per = (kblocks + splits - 1) / splits;
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    PieceIter pieces;
+    pieces.init(mode, tiles, kblocks, splits, pair, npairs);
+    Piece pc;
     const int half_n = BN / 2;
+    // a stage holds this block's 128 rows of x and its half of the w tile; 1024-byte multiples
+    // (BN is a multiple of 32), as the 128-byte swizzle needs
     const uint32_t stage_bytes = PAIR_A_BYTES + half_n * BK * 2;
+    const uint32_t nstages = min((uint32_t)PAIR_MAX_STAGES, (uint32_t)PAIR_DATA_BYTES / stage_bytes);
     auto fail = [&](int code) {
         atomicCAS(&g_gemm_error, 0, code);
         *abort_flag = 1;
@@ -277,22 +359,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (int unit = pair; ok && unit < units; unit += npairs) {
-                const int tile = unit / splits, part = unit % splits;
-                const int m0 = (tile % num_m) * 2 * BM + (int)rank * BM;
-                const int n0 = (tile / num_m) * BN + (int)rank * half_n;
-                const int kb0 = part * kb_per, kb1 = min(kblocks, (part + 1) * kb_per);
-                for (int kb = kb0; kb < kb1; kb++) {
+            while (ok && pieces.next(pc)) {
+                int m_idx, n_idx;
+                pair_tile_coords(pc.tile, num_m, num_n, m_idx, n_idx);
+                const int m0 = m_idx * 2 * BM + (int)rank * BM;
+                const int n0 = swiglu ? n_idx * half_n + (int)rank * N : n_idx * BN + (int)rank * half_n;
+                for (int kb = pc.kb0; kb < pc.kb1; kb++) {
                     if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
                         fail(11);
                         ok = false;
                         break;
                     }
-                    unsigned char* dst = smem + stage * PAIR_STAGE;
+                    unsigned char* dst = smem + stage * stage_bytes;
                     if (leader) mbar_expect_tx(&full[stage], 2 * stage_bytes);  // both blocks' bytes land on it
                     tma_load_2d_pair(dst, &tma_x, kb * BK, m0, &full[stage]);
                     tma_load_2d_pair(dst + PAIR_A_BYTES, &tma_w, kb * BK, n0, &full[stage]);
-                    if (++stage == PAIR_STAGES) {
+                    if (++stage == nstages) {
                         stage = 0;
                         phase ^= 1;
                     }
@@ -305,7 +387,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
             const uint32_t idesc = instr_desc(1, 2 * BM, BN);
             uint32_t stage = 0, phase = 0, it = 0;
             bool ok = true;
-            for (int unit = pair; ok && unit < units; unit += npairs, it++) {
+            for (; ok && pieces.next(pc); it++) {
                 const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
                 if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
                     fail(13);
@@ -313,8 +395,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                 }
                 fence_after_sync();
                 const uint32_t d = tmem_base + acc * PAIR_ACC_STRIDE;
-                const int part = unit % splits;
-                const int kb0 = part * kb_per, kb1 = min(kblocks, (part + 1) * kb_per);
+                const int kb0 = pc.kb0, kb1 = pc.kb1;
                 for (int kb = kb0; kb < kb1; kb++) {
                     if (!mbar_wait(&full[stage], phase, abort_flag)) {
                         fail(12);
@@ -322,7 +403,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                         break;
                     }
                     fence_after_sync();
-                    const uint32_t a_addr = smem_addr(smem + stage * PAIR_STAGE);
+                    const uint32_t a_addr = smem_addr(smem + stage * stage_bytes);
                     const uint32_t b_addr = a_addr + PAIR_A_BYTES;
 #pragma unroll
                     for (int k = 0; k < BK / 16; k++) {
@@ -330,7 +411,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                                          (kb > kb0 || k > 0) ? 1u : 0u);
                     }
                     mma_commit_pair(&empty[stage], 3);  // frees the stage in both blocks
-                    if (++stage == PAIR_STAGES) {
+                    if (++stage == nstages) {
                         stage = 0;
                         phase ^= 1;
                     }
@@ -343,9 +424,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
         const int quarter = warp & 3;
         uint32_t it = 0;
         int* last_flag = const_cast<int*>(abort_flag) + 1;  // shared word next to the abort flag
-        for (int unit = pair; unit < units; unit += npairs, it++) {
-            const int tile = unit / splits, part = unit % splits;
-            const int m_idx = tile % num_m, n_idx = tile / num_m;
+        for (; pieces.next(pc); it++) {
+            const int tile = pc.tile;
+            const bool shared_tile = pc.nparts > 1;
+            int m_idx, n_idx;
+            pair_tile_coords(tile, num_m, num_n, m_idx, n_idx);
             const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
             if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) {
                 fail(14);
@@ -356,15 +439,137 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
             const int row = m_idx * 2 * BM + (int)rank * BM + row_local;
             // this block's 128 x BN float32 partial of (tile, part), stored as [BN / 4][128][4] so
             // that the 32 rows a warp holds make one contiguous 512-byte access per column group
-            float* mine = partials + (((size_t)tile * splits + part) * 2 + rank) * (size_t)(BM * BN) +
-                          (size_t)row_local * 4;
+            float* mine = partials + (pc.slot_of(pc.part) * 2 + rank) * (size_t)(BM * BN) + (size_t)row_local * 4;
+            if (swiglu) {
+                const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * PAIR_ACC_STRIDE;
+#pragma unroll 1
+                for (int cc = 0; cc < half_n / 32; cc++) {
+                    const int col0 = n_idx * half_n + cc * 32;
+                    if (col0 >= N) break;
+                    uint32_t g[32], u[32];
+                    tmem_ld_32x32(t_row + cc * 32, g);
+                    tmem_ld_32x32(t_row + half_n + cc * 32, u);
+                    tmem_ld_wait();
+                    if (row < M) {
+                        // the unfused sequence rounds both projections to bf16 first, then
+                        // bf16(bf16(silu(gate)) * up)
+                        float o32[32];
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            o32[j] = rbf(silu_fast(rbf(__uint_as_float(g[j])))) * rbf(__uint_as_float(u[j]));
+                        bf16* dst = y + (size_t)row * ldy + col0;
+                        if (vec_ok && col0 + 32 <= N) {
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                uint4 o;
+                                o.x = pack2(o32[8 * j + 0], o32[8 * j + 1]);
+                                o.y = pack2(o32[8 * j + 2], o32[8 * j + 3]);
+                                o.z = pack2(o32[8 * j + 4], o32[8 * j + 5]);
+                                o.w = pack2(o32[8 * j + 6], o32[8 * j + 7]);
+                                st16(dst + 8 * j, o);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (col0 + j < N) dst[j] = to_bf16(o32[j]);
+                        }
+                    }
+                }
+                fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    if (leader)
+                        mbar_arrive(&tempty[acc]);
+                    else
+                        mbar_arrive_remote(&tempty[acc], 0);
+                }
+                continue;
+            }
+            bool others_done = false;
+            if (shared_tile) {
+                // When every other contributor has already left its partial tile, this piece adds
+                // them to its accumulator, in the same part order, and writes the rows at once:
+                // no partial tile of its own, no second pass.
+                if (warp == 2 && lane == 0) {
+                    int seen;
+                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];"
+                                 : "=r"(seen)
+                                 : "l"(counters + tile * 2 + (int)rank)
+                                 : "memory");
+                    *last_flag = seen == pc.nparts - 1;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                others_done = *last_flag != 0;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+            if (others_done) {
+                __threadfence();
+                const float* base = partials + (size_t)rank * (BM * BN) + (size_t)row_local * 4;
+                const size_t slot_stride = (size_t)2 * BM * BN;
+#pragma unroll 1
+                for (int cc = 0; cc < BN / 32; cc++) {
+                    const int col0 = n_idx * BN + cc * 32;
+                    if (col0 >= N) break;
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * PAIR_ACC_STRIDE + cc * 32, v);
+                    float sum[32];
+                    for (int s = 0; s < pc.nparts; s++) {
+                        if (s == pc.part) {
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 32; j++) sum[j] = s == 0 ? __uint_as_float(v[j]) : sum[j] + __uint_as_float(v[j]);
+                        } else {
+                            const float* other = base + pc.slot_of(s) * slot_stride;
+                            float4 p[8];
+#pragma unroll
+                            for (int j = 0; j < 8; j++)
+                                p[j] = __ldcg(reinterpret_cast<const float4*>(other + (size_t)(cc * 8 + j) * (BM * 4)));
+#pragma unroll
+                            for (int j = 0; j < 8; j++) {
+                                sum[4 * j] = s == 0 ? p[j].x : sum[4 * j] + p[j].x;
+                                sum[4 * j + 1] = s == 0 ? p[j].y : sum[4 * j + 1] + p[j].y;
+                                sum[4 * j + 2] = s == 0 ? p[j].z : sum[4 * j + 2] + p[j].z;
+                                sum[4 * j + 3] = s == 0 ? p[j].w : sum[4 * j + 3] + p[j].w;
+                            }
+                        }
+                    }
+                    if (row < M) {
+                        bf16* dst = y + (size_t)row * ldy + col0;
+                        if (vec_ok && col0 + 32 <= N) {
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                uint4 o;
+                                o.x = pack2(sum[8 * j + 0], sum[8 * j + 1]);
+                                o.y = pack2(sum[8 * j + 2], sum[8 * j + 3]);
+                                o.z = pack2(sum[8 * j + 4], sum[8 * j + 5]);
+                                o.w = pack2(sum[8 * j + 6], sum[8 * j + 7]);
+                                st16(dst + 8 * j, o);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (col0 + j < N) dst[j] = to_bf16(sum[j]);
+                        }
+                    }
+                }
+                fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    if (leader)
+                        mbar_arrive(&tempty[acc]);
+                    else
+                        mbar_arrive_remote(&tempty[acc], 0);
+                }
+                if (warp == 2 && lane == 0) counters[tile * 2 + (int)rank] = 0;  // ready for the next launch
+                continue;
+            }
 #pragma unroll 1
             for (int cc = 0; cc < BN / 32; cc++) {
                 uint32_t v[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * PAIR_ACC_STRIDE + cc * 32, v);
                 tmem_ld_wait();
                 const int col0 = n_idx * BN + cc * 32;
-                if (splits > 1) {
+                if (shared_tile) {
 #pragma unroll
                     for (int j = 0; j < 8; j++)
                         *reinterpret_cast<uint4*>(mine + (size_t)(cc * 8 + j) * (BM * 4)) =
@@ -396,24 +601,24 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                 else
                     mbar_arrive_remote(&tempty[acc], 0);
             }
-            if (splits > 1) {
-                // The unit that finishes last adds the tile's partial sums in part order (so the
-                // result does not depend on which unit that is) and writes the bf16 rows.
+            if (shared_tile) {
+                // The piece that finishes last adds the tile's partial sums in part order (so the
+                // result does not depend on which piece that is) and writes the bf16 rows.
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps of this block
                 if (warp == 2 && lane == 0) {
                     const int done = atomicAdd(&counters[tile * 2 + (int)rank], 1);
-                    *last_flag = done == splits - 1;
-                    if (done == splits - 1) counters[tile * 2 + (int)rank] = 0;  // ready for the next launch
+                    *last_flag = done == pc.nparts - 1;
+                    if (done == pc.nparts - 1) counters[tile * 2 + (int)rank] = 0;  // ready for the next launch
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 const bool last = *last_flag != 0;
                 asm volatile("bar.sync 1, 128;" ::: "memory");  // everyone has read the flag before it is reused
                 if (last && row < M) {
                     __threadfence();
-                    const float* first = partials + (((size_t)tile * splits) * 2 + rank) * (size_t)(BM * BN) +
-                                         (size_t)row_local * 4;
-                    const size_t part_stride = (size_t)2 * BM * BN;
+                    const float* mine_base = partials + (size_t)rank * (BM * BN) + (size_t)row_local * 4;
+                    const size_t slot_stride = (size_t)2 * BM * BN;
+                    const float* first = mine_base + pc.slot_of(0) * slot_stride;
 #pragma unroll 1
                     for (int cc = 0; cc < BN / 32; cc++) {
                         const int col0 = n_idx * BN + cc * 32;
@@ -425,12 +630,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                                 __ldcg(reinterpret_cast<const float4*>(first + (size_t)(cc * 8 + j) * (BM * 4)));
                             sum[4 * j] = p.x, sum[4 * j + 1] = p.y, sum[4 * j + 2] = p.z, sum[4 * j + 3] = p.w;
                         }
-                        for (int s = 1; s < splits; s++) {
+                        for (int s = 1; s < pc.nparts; s++) {
+                            const float* other = mine_base + pc.slot_of(s) * slot_stride;
 #pragma unroll
                             for (int j = 0; j < 8; j++) {
                                 const float4 p =
-                                    __ldcg(reinterpret_cast<const float4*>(first + s * part_stride +
-                                                                           (size_t)(cc * 8 + j) * (BM * 4)));
+                                    __ldcg(reinterpret_cast<const float4*>(other + (size_t)(cc * 8 + j) * (BM * 4)));
                                 sum[4 * j] += p.x, sum[4 * j + 1] += p.y, sum[4 * j + 2] += p.z, sum[4 * j + 3] += p.w;
                             }
                         }
@@ -567,27 +772,37 @@ int launch(const void* x, const void* w, void* y, int M, int N, int K, int ldy, 
     return cudaGetLastError();
 }
 
-// Plan for the pair kernel: the column-block width (a multiple of 32) and the number of
-// K splits that minimise waves x k-blocks per unit x per-k-block cost. Measured: a
+// Plan for the pair kernel: the column-block width (a multiple of 32) and how the k-blocks
+// are handed out -- whole tiles, `splits` equal parts per tile, or one contiguous run of all
+// tiles' k-blocks per pair -- minimising k-blocks per pair x per-k-block cost. Measured: a
 // k-block's time depends only weakly on the width (the 128 rows of x each block loads
-// dominate), roughly as bn + 400; a unit costs about 6 k-blocks of fill, drain and partial
-// traffic on top of its own. Splitting needs float32 room for every partial tile.
+// dominate), roughly as bn + 400; a piece costs about 6 k-blocks of fill and drain on top of
+// its own, and combining float32 partial tiles costs a fixed amount at the end. Sharing a
+// tile needs float32 room for every partial tile.
 struct PairPlan {
-    int bn, splits;
+    int bn, splits, mode;
 };
+
+// exposed time of the partial-tile sums, in k-blocks: measured about 5 s^2 for s equal parts (the
+// last piece of a tile reads the other s - 1 partial tiles with few loads in flight)
+constexpr double SPLIT_FIXUP_KB = 5.0;
+constexpr double RUN_FIXUP_KB = 8.0;
+constexpr double RUN_KB_COST = 1.3;      // a k-block of a run costs more: pairs at different k share no operand tiles in L2
 
 PairPlan pair_plan(int M, int N, int K, int pairs, size_t partial_bytes, int counter_slots) {
     const long num_m = (M + 2 * BM - 1) / (2 * BM);
     const int kblocks = (K + BK - 1) / BK;
-    int force_bn = 0, force_s = 0;  // tuning knobs
+    // tuning knobs (S1_GEMM_RUNS: 0 never, 1 always, otherwise by the cost model)
+    int force_bn = 0, force_s = 0, force_run = 2;
     if (const char* f = getenv("S1_GEMM_BN")) force_bn = atoi(f);
     if (const char* f = getenv("S1_GEMM_SPLITS")) force_s = atoi(f);
-    PairPlan best{256, 1};
+    if (const char* f = getenv("S1_GEMM_RUNS")) force_run = atoi(f);
+    PairPlan best{256, 1, 0};
     double best_cost = 1e30;
     for (int bn = 256; bn >= 64; bn -= 32) {
         if (force_bn && bn != force_bn) continue;
         const long tiles = num_m * ((N + bn - 1) / bn);
-        for (int s = 1; s <= 8; s++) {
+        for (int s = 1; s <= 8 && force_run != 1; s++) {
             if (force_s && s != force_s) continue;
             const int kb_per = (kblocks + s - 1) / s;
             if (s > 1) {
@@ -596,11 +811,25 @@ PairPlan pair_plan(int M, int N, int K, int pairs, size_t partial_bytes, int cou
                 if ((size_t)tiles * s * 2 * BM * bn * 4 > partial_bytes || tiles * 2 > counter_slots) continue;
             }
             const long waves = (tiles * s + pairs - 1) / pairs;
-            // measured: writing, fencing and re-reading the partial tiles costs about 25 k-blocks' time
-            const double cost = ((double)waves * (kb_per + 6) + (s > 1 ? 25.0 : 0.0)) * (bn + 400);
+            const double cost = ((double)waves * (kb_per + 6) + (s > 1 ? SPLIT_FIXUP_KB * s * s : 0.0)) * (bn + 400);
             if (cost < best_cost - 1e-9) {
                 best_cost = cost;
-                best = PairPlan{bn, s};
+                best = PairPlan{bn, s, 0};
+            }
+        }
+        // contiguous runs: every pair gets total / pairs k-blocks in at most
+        // ceil(run / kblocks) + 1 pieces, two of which share their tile
+        const long total = tiles * kblocks;
+        // Only for problems of at most two tiles per pair: measured, with many tiles the pairs
+        // drift apart in k, stop sharing x and w tiles in L2, and every k-block gets slower.
+        if (force_run != 0 && total >= pairs && (force_run == 1 || tiles <= 2 * pairs) &&
+            (size_t)pairs * 2 * 2 * BM * bn * 4 <= partial_bytes && tiles * 2 <= counter_slots) {
+            const long run = (total + pairs - 1) / pairs;
+            const long pieces = (run + kblocks - 1) / kblocks + 1;
+            const double cost = ((double)run + 6.0 * pieces + RUN_FIXUP_KB) * (bn + 400) * RUN_KB_COST;
+            if (cost < best_cost - 1e-9) {
+                best_cost = cost;
+                best = PairPlan{bn, 1, 1};
             }
         }
     }
@@ -621,10 +850,41 @@ int launch_pair(const void* x, const void* w, void* y, int M, int N, int K, int 
     CUtensorMap mx, mw;
     if (!tensor_map(x, M, K, BM, &mx) || !tensor_map(w, N, K, bn / 2, &mw)) return CS1_ERR_TENSOR_MAP;
     const int units = ((M + 2 * BM - 1) / (2 * BM)) * ((N + bn - 1) / bn) * plan.splits;
-    const int grid = 2 * (units < pairs ? units : pairs);
+    const int grid = plan.mode == 1 ? 2 * pairs : 2 * (units < pairs ? units : pairs);
     const int vec_ok = (ldy % 8 == 0) && aligned16(y);
     gemm_tc5_pair_kernel<<<grid, GEMM_THREADS, PAIR_SMEM, st>>>(mx, mw, static_cast<bf16*>(y), M, N, K, ldy, vec_ok, bn,
-                                                               plan.splits, static_cast<float*>(partials), counters);
+                                                               plan.splits, plan.mode, static_cast<float*>(partials),
+                                                               counters, 0);
+    return cudaGetLastError();
+}
+
+// act [M, I] = silu(x w_gate^T) * (x w_up^T) with w = [gate; up] stacked, [2 I, K]: both
+// projections rounded to bf16 before the activation, as when they are stored and read back.
+int launch_pair_swiglu(const void* x, const void* w, void* act, int M, int I, int K, int ld, DeviceInfo* info,
+                       cudaStream_t st) {
+    if (!info->pair_smem_set) {
+        const cudaError_t e =
+            cudaFuncSetAttribute(gemm_tc5_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
+        if (e != cudaSuccess) return e;
+        info->pair_smem_set = true;
+    }
+    const int pairs = info->sms / 2;
+    const long num_m = (M + 2 * BM - 1) / (2 * BM);
+    const int kblocks = (K + BK - 1) / BK;
+    int bn = 256;
+    double best_cost = 1e30;
+    for (int c = 256; c >= 64; c -= 64) {  // half of it a multiple of 32
+        const long tiles = num_m * ((I + c / 2 - 1) / (c / 2));
+        const double cost = (double)((tiles + pairs - 1) / pairs) * (kblocks + 6) * (c + 400);
+        if (cost < best_cost - 1e-9) best_cost = cost, bn = c;
+    }
+    CUtensorMap mx, mw;
+    if (!tensor_map(x, M, K, BM, &mx) || !tensor_map(w, 2 * I, K, bn / 2, &mw)) return CS1_ERR_TENSOR_MAP;
+    const long tiles = num_m * ((I + bn / 2 - 1) / (bn / 2));
+    const int grid = 2 * (int)(tiles < pairs ? tiles : pairs);
+    const int vec_ok = (ld % 8 == 0) && aligned16(act);
+    gemm_tc5_pair_kernel<<<grid, GEMM_THREADS, PAIR_SMEM, st>>>(mx, mw, static_cast<bf16*>(act), M, I, K, ld, vec_ok, bn,
+                                                               1, 0, nullptr, nullptr, 1);
     return cudaGetLastError();
 }
 
@@ -678,6 +938,17 @@ int s1_gemm_tc5(const void* x, const void* w, void* y, int M, int N, int K, int 
     if (best == 256) return launch<256>(x, w, y, M, N, K, ldy, info, 0, st);
     if (best == 128) return launch<128>(x, w, y, M, N, K, ldy, info, 1, st);
     return launch<64>(x, w, y, M, N, K, ldy, info, 2, st);
+}
+
+bool s1_gemm_tc5_swiglu_supported(const void* x, const void* w, int M, int I, int K) {
+    return M > BM && I > 0 && K >= 64 && K % 8 == 0 && aligned16(x) && aligned16(w) && pair_enabled();
+}
+
+int s1_gemm_tc5_swiglu(const void* x, const void* w, void* act, int M, int I, int K, int ld, cudaStream_t st) {
+    cudaError_t err;
+    DeviceInfo* info = device_info(&err);
+    if (!info) return err;
+    return launch_pair_swiglu(x, w, act, M, I, K, ld, info, st);
 }
 
 // Returns the device error word of the current device (0 = no bounded wait ever gave up)

@@ -21,3 +21,9 @@ bool s1_gemm_tc5_supported(const void* x, const void* w, const void* y, int M, i
 // K split is used then). Returns 0, a cudaError_t or CS1_ERR_TENSOR_MAP.
 int s1_gemm_tc5(const void* x, const void* w, void* y, int M, int N, int K, int ldy, const S1GemmScratch* scratch,
                 cudaStream_t stream);
+
+// The MLP's first half in one kernel: act [M, I] (rows of ld) = silu(x w[0:I]^T) * (x w[I:2I]^T),
+// each projection rounded to bf16 before the activation (bit-identical to the GEMM followed
+// by the SiLU-multiply operator). Needs more than 128 rows (the pair kernel).
+bool s1_gemm_tc5_swiglu_supported(const void* x, const void* w, int M, int I, int K);
+int s1_gemm_tc5_swiglu(const void* x, const void* w, void* act, int M, int I, int K, int ld, cudaStream_t stream);

@@ -91,7 +91,9 @@ SIGNATURES = {
     "s1_gemm_tcgen05": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "s1_gemm_tc5_status": (i32, [ip]),
     "s1_gemm_unsplit": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+    "s1_gemm_swiglu": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "s1_model_set_exact_packing": (i32, [vp, i32]),
+    "s1_model_set_fused_mlp": (i32, [vp, i32]),
     "s1_model_create": (i32, [C.POINTER(S1Config), i32, vpp]),
     "s1_model_destroy": (None, [vp]),
     "s1_model_set_tensor": (i32, [vp, C.c_char_p, vp, sz]),

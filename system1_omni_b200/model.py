@@ -199,6 +199,10 @@ class Model:
         """Bit-identical results for a prompt alone or in a pack (slower); see s1_executor.h."""
         L.check(L.load().s1_model_set_exact_packing(self.handle, int(on)), "exact packing")
 
+    def set_fused_mlp(self, on=True):
+        """Gate/up projection + SiLU-multiply as one kernel (default) or as the two operators."""
+        L.check(L.load().s1_model_set_fused_mlp(self.handle, int(on)), "fused mlp")
+
     def graph_stats(self):
         r, c, e = C.c_int(), C.c_int(), C.c_int()
         L.check(L.load().s1_model_graph_stats(self.handle, C.byref(r), C.byref(c), C.byref(e)), "graph stats")

@@ -522,6 +522,57 @@ def test_gemm_k_split_is_deterministic(cs1, stream, M, N, K):
     cs1.cs1_gemm_destroy(handle)
 
 
+@pytest.mark.parametrize("M,N,K,pad", [(1024, 2560, 9728, 0), (1024, 2560, 4096, 8), (1000, 2500, 2048, 4),
+                                       (300, 5120, 2560, 0), (257, 96, 64 * 150, 0), (4096, 2560, 2048, 0)])
+@pytest.mark.parametrize("knobs", [{"S1_GEMM_RUNS": "1"}, {"S1_GEMM_RUNS": "1", "S1_GEMM_BN": "160"},
+                                   {"S1_GEMM_RUNS": "0", "S1_GEMM_SPLITS": "3"}])
+def test_gemm_shared_tile_schedules(cs1, stream, M, N, K, pad, knobs, monkeypatch):
+    """The pair kernel's two ways of sharing a tile's K range between block pairs - contiguous
+    runs over all tiles' k-blocks, and equal splits - forced through the tuning knobs: same
+    result as the oracle, repeatable bit for bit, padding untouched, counters back at zero."""
+    for k, v in knobs.items():
+        monkeypatch.setenv(k, v)
+    x, w, ldy = gemm_case(M, N, K, pad, seed=7)
+    xd, wd = dev(x, stream), dev(w, stream)
+    handle = cs1.cs1_gemm_create(32 << 20)
+    outs = []
+    for _ in range(3):
+        y = dev(np.full((M, ldy), 0x7FC0, np.uint16), stream)
+        L.check(cs1.s1_gemm_tcgen05(handle, xd.at(), wd.at(), y.at(), M, N, K, ldy, stream.handle), "gemm")
+        outs.append(host(y, (M, ldy), stream))
+    assert L.gemm_status() == 0
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+    check_gemm(outs[0], x, w, N)
+    assert np.all(outs[0][:, N:] == 0x7FC0)
+    cs1.cs1_gemm_destroy(handle)
+
+
+@pytest.mark.parametrize("M,I,K,pad", [(1024, 9728, 2560, 0), (300, 1000, 512, 8), (129, 96, 64, 0), (700, 17408, 1024, 0),
+                                       (257, 40, 128, 3)])
+def test_gemm_swiglu_equals_the_two_operators(cs1, stream, M, I, K, pad):
+    """gate/up projection + SiLU-multiply in one kernel against cs1_gemm then cs1_silu_mul
+    (model.rs:1301-1316 runs them as two operators): the same bits, padding untouched."""
+    x = O.random_bf16(M * K, 31, 1.0).reshape(M, K)
+    w = O.random_bf16(2 * I * K, 32, 0.08).reshape(2 * I, K)
+    xd, wd = dev(x, stream), dev(w, stream)
+    handle = cs1.cs1_gemm_create(32 << 20)
+    gate_up, want = L.DeviceBuffer(M * 2 * I * 2), L.DeviceBuffer(M * I * 2)
+    L.check(cs1.s1_gemm_tcgen05(handle, xd.at(), wd.at(), gate_up.at(), M, 2 * I, K, 2 * I, stream.handle), "gemm")
+    L.check(cs1.cs1_silu_mul(gate_up.at(), 2 * I, want.at(), M, I, stream.handle), "silu_mul")
+    ld = I + pad
+    got = dev(np.full((M, ld), 0x7FC0, np.uint16), stream)
+    L.check(cs1.s1_gemm_swiglu(handle, xd.at(), wd.at(), got.at(), M, I, K, ld, stream.handle), "swiglu")
+    g, wnt = host(got, (M, ld), stream), host(want, (M, I), stream)
+    assert L.gemm_status() == 0
+    assert np.array_equal(g[:, :I], wnt)
+    assert np.all(g[:, I:] == 0x7FC0)
+    # and against the oracle's two steps
+    ref = O.silu_mul(O.gemm(x, w), 2 * I, M, I)
+    assert (ulp_diff(g[:, :I], ref) <= 1).mean() > 0.995
+    assert cs1.s1_gemm_swiglu(handle, xd.at(), wd.at(), got.at(), 128, I, K, ld, stream.handle) == 2000
+    cs1.cs1_gemm_destroy(handle)
+
+
 def test_gemm_rows_do_not_depend_on_the_row_count(cs1, stream):
     """Without a K split a row comes out the same however many rows the call has - the
     property the reference buys by running its out/down GEMMs per sequence (model.rs:723-739)."""

@@ -73,6 +73,21 @@ def test_packed_equals_independent_execution(setup):
     assert np.array_equal(again, packed[perm])
 
 
+def test_fused_mlp_kernel_equals_the_two_operators(setup):
+    """The executor's one-kernel gate/up + SiLU-multiply against the reference's two-operator
+    sequence (model.rs:1301-1316): identical hidden states, eager and replayed."""
+    cfg, weights, model = setup
+    rng = np.random.default_rng(5)
+    prompts = [rng.integers(0, cfg.vocab, n).tolist() for n in (200, 131, 77)]
+    fused = model.forward_batch(prompts)
+    model.set_fused_mlp(False)
+    try:
+        plain = model.forward_batch(prompts)
+    finally:
+        model.set_fused_mlp(True)
+    assert np.array_equal(fused, plain)
+
+
 def test_exact_packing_on_a_shape_that_splits_k(cs1):
     """A wider decoder whose hidden-size projections have too few tiles for the GPU and so
     split K by the row count: with exact packing a prompt's result is bit-identical alone or
