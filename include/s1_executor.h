@@ -29,6 +29,17 @@ int s1_memset_async(void* dst, int value, size_t bytes, void* stream);
 int s1_device_sync(void);
 int s1_mem_info(size_t* free_bytes, size_t* total_bytes);
 
+/* ---- Attention over a window that continues a shared prefix ----
+ * Gated causal attention of positions [prefix_len, prefix_len + rows): q, gate, out [rows, Hq, Dh],
+ * k [rows, Hk, Dh] and v (row stride ldv) hold the window only; the prefix's post-prep keys
+ * [prefix_len, Hk, Dh] and values (row stride ldv_prefix) are read where they lie, so several
+ * windows share one copy. Same tiles and arithmetic as cs1_attention_gated_prefix on the
+ * concatenated rows, which is how the reference does it after copying the prefix rows back
+ * into its scratch (model.rs:1516-1523). prefix_len: a multiple of 64, 0 = no prefix. */
+int s1_attention_gated_shared_prefix(const void* q, const void* k, const void* v, int ldv, const void* gate, void* out,
+                                     const void* k_prefix, const void* v_prefix, int ldv_prefix, int prefix_len,
+                                     int rows, int Hq, int Hk, int Dh, float scale, void* stream);
+
 /* ---- GEMM engines behind cs1_gemm, pinned (benchmark arms and parity tests) ---- */
 int s1_gemm_cublaslt(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream);
 /* cs1_gemm with the K-split path switched off for this call. */
@@ -99,6 +110,30 @@ int s1_model_forward_batch(void* model, const int32_t* ids, const int* lengths, 
  * call); queue-only, no host synchronisation. */
 int s1_model_forward_device(void* model, const int32_t* ids_device, const int* lengths, int nseq, void** last_rows);
 int s1_model_sync(void* model);
+
+/* ---- Prefix capture and continuation (PrefixState, alloc_prefix, forward_multimodal_capture /
+ * _continue, model.rs:557-588, 954-1073; run_window, model.rs:1340-1638), for text positions.
+ * A prefix is rows [0, len) of a prompt, len a positive multiple of 64 (the delta rule's chunk):
+ * per full-attention layer the post-prep keys and raw values, per Gated DeltaNet layer the
+ * float32 state and the last three pre-conv rows. Capture runs those rows once; a continuation
+ * runs rows [len, len + c) seeded from them and repeats the one-shot arithmetic (bit for bit
+ * when the GEMMs do not split K, i.e. under exact packing; within rounding otherwise - the
+ * reference has the same caveat for cuBLASLt's row-count-dependent plans, model.rs:1349-1351).
+ * Unlike the reference, which continues one window per call, s1_model_forward_continue takes
+ * all candidates of a request at once and packs them through every GEMM. ---- */
+int s1_prefix_create(void* model, int len, void** prefix);
+void s1_prefix_destroy(void* prefix);
+size_t s1_prefix_bytes(void* prefix); /* device bytes held, for a cache budget */
+int s1_prefix_len(void* prefix);
+/* Run ids[0, len) (len == the prefix's length) and fill the prefix; waits for the device. */
+int s1_model_prefix_capture(void* model, const int32_t* ids, int len, void* prefix);
+/* nseq continuations of one captured prefix: ids concatenated, lengths[nseq]; candidate i sits at
+ * positions [len, len + lengths[i]). last_hidden: float32 [nseq, hidden] in host memory, the
+ * final-norm hidden state of each candidate's last token. S1_ERR_ARGUMENT for a prefix of
+ * another model, one not yet captured, an empty candidate or one that passes max_positions. */
+int s1_model_forward_continue(void* model, const void* prefix, const int32_t* ids, const int* lengths, int nseq,
+                              float* last_hidden);
+
 
 /* Operator families of the layer loop, for launch counts and per-family device time. */
 enum {

@@ -90,7 +90,10 @@ template <int DH, int BN, bool GATED>
 __global__ void __launch_bounds__(FA_THREADS)
     flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v, int ldv,
                  const bf16* __restrict__ gate, bf16* __restrict__ out, int T, int Hq, int Hk, float scale_log2,
-                 int q_base) {
+                 int q_base, const bf16* __restrict__ kpre, const bf16* __restrict__ vpre, int ldvpre, int own_base) {
+    // Rows are absolute positions. Keys and values of positions below own_base come from the
+    // shared prefix buffers (kpre, vpre); q, gate, out, k and v hold the positions from own_base
+    // on, indexed from zero. own_base = 0: everything in q, k, v (the plain and q_base entries).
     constexpr int LDS = FaSmem<DH, BN>::LDS;
     constexpr int NT = BN / 8;   // score tiles per warp row block
     constexpr int DT = DH / 8;   // output tiles
@@ -107,7 +110,7 @@ __global__ void __launch_bounds__(FA_THREADS)
     constexpr int CPR = DH / 8;  // 16-byte chunks per row
     for (int c = tid; c < BM * CPR; c += FA_THREADS) {
         const int r = c / CPR, col = (c % CPR) * 8, row = q0 + r;
-        cp_async16(qs + r * LDS + col, q + ((size_t)min(row, T - 1) * Hq + h) * DH + col, row < T);
+        cp_async16(qs + r * LDS + col, q + ((size_t)(min(row, T - 1) - own_base) * Hq + h) * DH + col, row < T);
     }
     const int kv_end = min(T, q0 + BM);
     const int ntiles = (kv_end + BN - 1) / BN;
@@ -119,8 +122,13 @@ __global__ void __launch_bounds__(FA_THREADS)
             const int r = c / CPR, col = (c % CPR) * 8, row = k0 + r;
             const bool ok = row < kv_end;
             const int rr = min(row, T - 1);
-            cp_async16(kd + r * LDS + col, k + ((size_t)rr * Hk + hk) * DH + col, ok);
-            cp_async16(vd + r * LDS + col, v + (size_t)rr * ldv + (size_t)hk * DH + col, ok);
+            if (rr < own_base) {
+                cp_async16(kd + r * LDS + col, kpre + ((size_t)rr * Hk + hk) * DH + col, ok);
+                cp_async16(vd + r * LDS + col, vpre + (size_t)rr * ldvpre + (size_t)hk * DH + col, ok);
+            } else {
+                cp_async16(kd + r * LDS + col, k + ((size_t)(rr - own_base) * Hk + hk) * DH + col, ok);
+                cp_async16(vd + r * LDS + col, v + (size_t)(rr - own_base) * ldv + (size_t)hk * DH + col, ok);
+            }
         }
     };
     load_kv(0, 0);
@@ -228,7 +236,7 @@ __global__ void __launch_bounds__(FA_THREADS)
     for (int r = 0; r < 2; r++) {
         const int row = row0 + g + r * 8;
         if (row >= T) continue;
-        const size_t base = ((size_t)row * Hq + h) * DH + 2 * t;
+        const size_t base = ((size_t)(row - own_base) * Hq + h) * DH + 2 * t;
 #pragma unroll
         for (int n = 0; n < DT; n++) {
             float a = o[n][2 * r] * inv[r], b = o[n][2 * r + 1] * inv[r];
@@ -245,7 +253,8 @@ __global__ void __launch_bounds__(FA_THREADS)
 
 template <int DH, int BN, bool GATED>
 int launch_flash(const bf16* q, const bf16* k, const bf16* v, int ldv, const bf16* gate, bf16* out, int T, int Hq,
-                 int Hk, float scale, int q_base, cudaStream_t st) {
+                 int Hk, float scale, int q_base, cudaStream_t st, const bf16* kpre = nullptr,
+                 const bf16* vpre = nullptr, int ldvpre = 0, int own_base = 0) {
     constexpr int BYTES = FaSmem<DH, BN>::BYTES;
     // Raise the dynamic shared memory limit once per device.
     static bool configured[64] = {};
@@ -261,7 +270,7 @@ int launch_flash(const bf16* q, const bf16* k, const bf16* v, int ldv, const bf1
     constexpr float LOG2E = 1.4426950408889634f;
     const dim3 grid((T - q_base + BM - 1) / BM, Hq);
     flash_kernel<DH, BN, GATED><<<grid, FA_THREADS, BYTES, st>>>(q, k, v, ldv, gate, out, T, Hq, Hk, scale * LOG2E,
-                                                                q_base);
+                                                                q_base, kpre, vpre, ldvpre, own_base);
     return cudaGetLastError();
 }
 
@@ -324,6 +333,36 @@ extern "C" int cs1_attention(const void* q, const void* k, const void* v, int ld
 extern "C" int cs1_attention_gated(const void* q, const void* k, const void* v, int ldv, const void* gate, void* out,
                                    int T, int Hq, int Hk, int Dh, float scale, void* stream) {
     return attention_entry<true>(q, k, v, ldv, gate, out, T, Hq, Hk, Dh, scale, 0, stream);
+}
+
+// Gated causal attention of a window that continues a shared prefix: positions
+// [prefix_len, prefix_len + rows). q, gate, out [rows, Hq, Dh], k [rows, Hk, Dh] and v (row
+// stride ldv) hold the window only; the prefix's post-prep keys [prefix_len, Hk, Dh] and values
+// (row stride ldv_prefix) are read where they lie, so several windows can share one copy. Same
+// tiles and arithmetic as cs1_attention_gated_prefix on the concatenated buffers (the
+// reference restores the prefix rows into the scratch first, model.rs:1516-1523).
+extern "C" int s1_attention_gated_shared_prefix(const void* q, const void* k, const void* v, int ldv, const void* gate,
+                                                void* out, const void* k_prefix, const void* v_prefix, int ldv_prefix,
+                                                int prefix_len, int rows, int Hq, int Hk, int Dh, float scale,
+                                                void* stream) {
+    if ((Dh != 128 && Dh != 256) || Hk <= 0 || Hq <= 0 || Hq % Hk != 0 || ldv % 8 != 0 || ldv < Hk * Dh ||
+        ldv_prefix % 8 != 0 || ldv_prefix < Hk * Dh || rows < 0 || prefix_len < 0 || prefix_len % BM)
+        return cudaErrorInvalidValue;
+    if (rows == 0) return cudaSuccess;
+    if (!q || !k || !v || !gate || !out || (prefix_len > 0 && (!k_prefix || !v_prefix))) return cudaErrorInvalidValue;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(k_prefix) || !aligned16(v_prefix) ||
+        (reinterpret_cast<uintptr_t>(out) & 3) || (reinterpret_cast<uintptr_t>(gate) & 3))
+        return cudaErrorInvalidValue;
+    const bf16 *qp = static_cast<const bf16*>(q), *kp = static_cast<const bf16*>(k), *vp = static_cast<const bf16*>(v);
+    const bf16 *kpre = static_cast<const bf16*>(k_prefix), *vpre = static_cast<const bf16*>(v_prefix);
+    const bf16* gp = static_cast<const bf16*>(gate);
+    bf16* op = static_cast<bf16*>(out);
+    const int T = prefix_len + rows;
+    if (Dh == 256)
+        return launch_flash<256, 32, true>(qp, kp, vp, ldv, gp, op, T, Hq, Hk, scale, prefix_len, as_stream(stream), kpre,
+                                           vpre, ldv_prefix, prefix_len);
+    return launch_flash<128, 64, true>(qp, kp, vp, ldv, gp, op, T, Hq, Hk, scale, prefix_len, as_stream(stream), kpre, vpre,
+                                       ldv_prefix, prefix_len);
 }
 
 extern "C" int cs1_attention_gated_prefix(const void* q, const void* k, const void* v, int ldv, const void* gate,

@@ -334,6 +334,37 @@ int gemm_rows(Model* m, size_t x, const Tensor& w, size_t y, const int* lengths,
     return 0;
 }
 
+// Second half of a layer (model.rs:1287-1336): residual add + post norm, SwiGLU MLP, residual
+// add + the next layer's input norm (the final norm after the last layer).
+int mlp_block(Model* m, size_t li, const int* lengths, int nseq, int t) {
+    const S1Config& c = m->cfg;
+    const Scratch& s = m->s;
+    void* st = m->stream;
+    const Layer& ly = m->layers[li];
+    const int h = c.hidden, I = c.intermediate;
+    const float eps = c.eps;
+    S1_OP(S1_FAMILY_NORM, 1,
+          cs1_add_rms_norm(s.at(s.res), s.at(s.delta), m->w(ly.post_norm), s.at(s.x), t, h, eps, st));
+    // gate/up projection and SiLU-multiply: one kernel where the tcgen05 engine takes it
+    // (same bits as the two operators), else the reference's sequence
+    int fused = CS1_ERR_UNSUPPORTED;
+    if (m->fuse_swiglu) {
+        S1_TRY(op(m, S1_FAMILY_GEMM, 0, [&] {
+            fused = s1_gemm_swiglu(m->gemm, s.at(s.x), m->w(ly.gate_up), s.at(s.act), t, I, h, I, st);
+            return fused == CS1_ERR_UNSUPPORTED ? 0 : fused;
+        }));
+        if (fused == 0) m->launches[S1_FAMILY_GEMM] += 1;
+    }
+    if (fused == CS1_ERR_UNSUPPORTED) {
+        S1_TRY(gemm(m, s.x, ly.gate_up, s.gate_up, t, 2 * I, h));
+        S1_OP(S1_FAMILY_SILU_MUL, 1, cs1_silu_mul(s.at(s.gate_up), 2 * I, s.at(s.act), t, I, st));
+    }
+    S1_TRY(gemm_rows(m, s.act, ly.down, s.delta, lengths, nseq, h, I));
+    const Tensor& next = li + 1 < m->layers.size() ? m->layers[li + 1].input_norm : m->final_norm;
+    S1_OP(S1_FAMILY_NORM, 1, cs1_add_rms_norm(s.at(s.res), s.at(s.delta), m->w(next), s.at(s.x), t, h, eps, st));
+    return 0;
+}
+
 // The layer loop (model.rs:1119-1338). Pointwise operators and the input / gate-up GEMMs run
 // once over the packed rows; conv, delta rule, attention prep and attention run per sequence.
 // dump (nullable, host) receives the residual stream after each layer.
@@ -344,7 +375,7 @@ int run(Model* m, const int* lengths, int nseq, char* dump) {
     int t = 0;
     for (int i = 0; i < nseq; i++) t += lengths[i];
     const int h = c.hidden, kd = m->key_dim(), vd = m->value_dim(), hv = c.lin_v_heads;
-    const int hq = c.heads, hk = c.kv_heads, hd = c.head_dim, I = c.intermediate;
+    const int hq = c.heads, hk = c.kv_heads, hd = c.head_dim;
     const int gdn_in = m->gdn_in_w(), attn_in = m->attn_in_w(), attn_q = m->attn_q_w(), conv = m->conv_w();
     const float eps = c.eps;
     S1_OP(S1_FAMILY_NORM, 1, cs1_rms_norm(s.at(s.res), m->w(m->layers[0].input_norm), s.at(s.x), t, h, eps, st));
@@ -402,26 +433,125 @@ int run(Model* m, const int* lengths, int nseq, char* dump) {
             }
             S1_TRY(gemm_rows(m, s.ao, ly.o, s.delta, lengths, nseq, h, hq * hd));
         }
-        S1_OP(S1_FAMILY_NORM, 1,
-              cs1_add_rms_norm(s.at(s.res), s.at(s.delta), m->w(ly.post_norm), s.at(s.x), t, h, eps, st));
-        // gate/up projection and SiLU-multiply: one kernel where the tcgen05 engine takes it
-        // (same bits as the two operators), else the reference's sequence
-        int fused = CS1_ERR_UNSUPPORTED;
-        if (m->fuse_swiglu) {
-            S1_TRY(op(m, S1_FAMILY_GEMM, 0, [&] {
-                fused = s1_gemm_swiglu(m->gemm, s.at(s.x), m->w(ly.gate_up), s.at(s.act), t, I, h, I, st);
-                return fused == CS1_ERR_UNSUPPORTED ? 0 : fused;
-            }));
-            if (fused == 0) m->launches[S1_FAMILY_GEMM] += 1;
-        }
-        if (fused == CS1_ERR_UNSUPPORTED) {
-            S1_TRY(gemm(m, s.x, ly.gate_up, s.gate_up, t, 2 * I, h));
-            S1_OP(S1_FAMILY_SILU_MUL, 1, cs1_silu_mul(s.at(s.gate_up), 2 * I, s.at(s.act), t, I, st));
-        }
-        S1_TRY(gemm_rows(m, s.act, ly.down, s.delta, lengths, nseq, h, I));
-        const Tensor& next = li + 1 < m->layers.size() ? m->layers[li + 1].input_norm : m->final_norm;
-        S1_OP(S1_FAMILY_NORM, 1, cs1_add_rms_norm(s.at(s.res), s.at(s.delta), m->w(next), s.at(s.x), t, h, eps, st));
+        S1_TRY(mlp_block(m, li, lengths, nseq, t));
         if (dump) S1_TRY(cs1_download(dump + li * (size_t)t * h * BF16, s.at(s.res), (size_t)t * h * BF16, st));
+    }
+    return 0;
+}
+
+// The device-side state of one token prefix, rows [0, len) of a prompt (PrefixState,
+// model.rs:557-576): per full-attention layer the post-prep keys and the raw values, per Gated
+// DeltaNet layer the float32 recurrent state and the last three pre-conv projection rows.
+struct Prefix {
+    Model* owner = nullptr;
+    bool ready = false;
+    int len = 0;
+    std::vector<void*> k, v;         // [len, Hk * Dh] bf16 each
+    std::vector<void*> state, tail;  // [H, 128, 128] float32; [3, gdn_in] bf16
+    size_t bytes = 0;
+};
+
+constexpr int TAIL_ROWS = 3;  // conv kernel 4: a row needs the three rows before it
+
+// The layer loop over a window that captures or continues a prefix (run_window,
+// model.rs:1340-1638), for a pack of windows instead of one.
+//   capture: one sequence, rows [0, len); the per-layer state is copied out as it is produced.
+//   prefix:  nseq continuations of the same prefix, each at positions [len, len + c_i). The
+//            reference runs one continuation per call; here the candidates of a request share
+//            every GEMM and pointwise launch, which is what keeps the weights' one pass over
+//            HBM amortised over all of them. A continuation owns lengths[i] = 3 + c_i packed
+//            rows: three lead rows that receive the prefix's conv tail in every Gated DeltaNet
+//            layer (so the convolution over the whole pack sees the right history; what the
+//            lead rows themselves compute is never read), then its c_i token rows.
+int run_window(Model* m, const int* lengths, int nseq, Prefix* capture, const Prefix* prefix) {
+    const S1Config& c = m->cfg;
+    const Scratch& s = m->s;
+    void* st = m->stream;
+    int t = 0;
+    for (int i = 0; i < nseq; i++) t += lengths[i];
+    const int lead = prefix ? TAIL_ROWS : 0, qb = prefix ? prefix->len : 0;
+    const int h = c.hidden, kd = m->key_dim(), vd = m->value_dim(), hv = c.lin_v_heads;
+    const int hq = c.heads, hk = c.kv_heads, hd = c.head_dim;
+    const int gdn_in = m->gdn_in_w(), attn_in = m->attn_in_w(), attn_q = m->attn_q_w(), conv = m->conv_w();
+    const size_t kv_row = (size_t)hk * hd * BF16, tail_bytes = (size_t)TAIL_ROWS * gdn_in * BF16;
+    const float eps = c.eps;
+    if (prefix) {
+        // the lead rows skip the per-sequence operators; give what those would have written a value
+        S1_TRY(s1_memset_async(s.at(s.lo), 0, (size_t)t * vd * BF16, st));
+        S1_TRY(s1_memset_async(s.at(s.ao), 0, (size_t)t * hq * hd * BF16, st));
+    }
+    S1_OP(S1_FAMILY_NORM, 1, cs1_rms_norm(s.at(s.res), m->w(m->layers[0].input_norm), s.at(s.x), t, h, eps, st));
+    size_t la = 0, fa = 0;
+    for (size_t li = 0; li < m->layers.size(); li++) {
+        const Layer& ly = m->layers[li];
+        if (!ly.full) {
+            S1_TRY(gemm(m, s.x, ly.in_proj, s.gdn_in, t, gdn_in, h));
+            const size_t z = s.gdn_in + (size_t)conv * BF16;
+            const size_t b = z + (size_t)vd * BF16;
+            const size_t a = b + (size_t)hv * BF16;
+            if (capture)
+                S1_TRY(cs1_copy_dd(capture->tail[la], s.at(s.gdn_in + (size_t)(t - TAIL_ROWS) * gdn_in * BF16), tail_bytes,
+                                   st));
+            size_t off = 0;
+            for (int q = 0; prefix && q < nseq; q++) {
+                S1_TRY(cs1_copy_dd(s.at(s.gdn_in + off * gdn_in * BF16), prefix->tail[la], tail_bytes, st));
+                off += lengths[q];
+            }
+            // one convolution over the pack: a continuation's first token row sees its lead rows
+            S1_OP(S1_FAMILY_CONV, 1,
+                  cs1_gdn_conv(s.at(s.gdn_in), gdn_in, m->w(ly.conv), s.at(s.lq), s.at(s.lk), s.at(s.lv), t, kd, vd, st));
+            S1_OP(S1_FAMILY_GATES, 1,
+                  cs1_gdn_gates(s.at(b), s.at(a), gdn_in, m->w(ly.a_log), m->w(ly.dt_bias), s.at(s.beta),
+                                reinterpret_cast<float*>(s.at(s.g)), t, hv, st));
+            off = 0;
+            for (int q = 0; q < nseq; q++) {
+                const size_t r = off + lead;
+                S1_OP(S1_FAMILY_GDN, 2,
+                      cs1_gdn_prefill_x(s.at(s.lq + r * kd * BF16), s.at(s.lk + r * kd * BF16), s.at(s.lv + r * vd * BF16),
+                                        reinterpret_cast<const float*>(s.at(s.g + r * hv * F32)),
+                                        s.at(s.beta + r * hv * BF16), s.at(s.lo + r * vd * BF16),
+                                        reinterpret_cast<float*>(s.at(s.workspace)), lengths[q] - lead, hv,
+                                        c.lin_k_heads, 1.0f / sqrtf(128.0f),
+                                        prefix ? static_cast<const float*>(prefix->state[la]) : nullptr,
+                                        capture ? static_cast<float*>(capture->state[la]) : nullptr, st));
+                off += lengths[q];
+            }
+            S1_OP(S1_FAMILY_GATED_NORM, 1,
+                  cs1_gated_rms_norm(s.at(s.lo), s.at(z), gdn_in, m->w(ly.norm), s.at(s.ln), t, hv, 128, eps, st));
+            S1_TRY(gemm_rows(m, s.ln, ly.out, s.delta, lengths, nseq, h, vd));
+            la++;
+        } else {
+            S1_TRY(gemm(m, s.x, ly.qkv, s.attn_in, t, attn_in, h));
+            const size_t k = s.attn_in + (size_t)attn_q * BF16;
+            const size_t v = k + kv_row;
+            size_t off = 0;
+            for (int q = 0; q < nseq; q++) {
+                const size_t r = off + lead;
+                const int rows = lengths[q] - lead;
+                // rotary tables from position qb on
+                S1_OP(S1_FAMILY_ATTN_PREP, 1,
+                      cs1_attn_prep(s.at(s.attn_in + r * attn_in * BF16), s.at(k + r * attn_in * BF16), attn_in,
+                                    m->w(ly.q_norm), m->w(ly.k_norm), s.at(s.cos + (size_t)qb * c.rotary_half * BF16),
+                                    s.at(s.sin + (size_t)qb * c.rotary_half * BF16), s.at(s.aq + r * hq * hd * BF16),
+                                    s.at(s.agate + r * hq * hd * BF16), s.at(s.ak + r * kv_row), rows, hq, hk, hd,
+                                    c.rotary_half, eps, st));
+                if (capture) {
+                    // keys after norm and rotary; values as projected
+                    S1_TRY(cs1_copy_dd(capture->k[fa], s.at(s.ak), (size_t)rows * kv_row, st));
+                    S1_TRY(cs1_copy2d(capture->v[fa], kv_row, s.at(v), (size_t)attn_in * BF16, kv_row, rows, st));
+                }
+                S1_OP(S1_FAMILY_ATTENTION, 1,
+                      s1_attention_gated_shared_prefix(
+                          s.at(s.aq + r * hq * hd * BF16), s.at(s.ak + r * kv_row), s.at(v + r * attn_in * BF16), attn_in,
+                          s.at(s.agate + r * hq * hd * BF16), s.at(s.ao + r * hq * hd * BF16),
+                          prefix ? prefix->k[fa] : nullptr, prefix ? prefix->v[fa] : nullptr, hk * hd, qb, rows, hq, hk,
+                          hd, 1.0f / sqrtf((float)hd), st));
+                off += lengths[q];
+            }
+            S1_TRY(gemm_rows(m, s.ao, ly.o, s.delta, lengths, nseq, h, hq * hd));
+            fa++;
+        }
+        S1_TRY(mlp_block(m, li, lengths, nseq, t));
     }
     return 0;
 }
@@ -674,6 +804,120 @@ int s1_model_forward_device(void* model, const int32_t* ids_device, const int* l
           s1::gather_rows(s.at(s.x), reinterpret_cast<const int*>(s.at(s.ends)), s.at(s.last), nseq, h,
                           static_cast<cudaStream_t>(m->stream)));
     if (last_rows) *last_rows = s.at(s.last);
+    return 0;
+}
+
+// ---- prefix capture / continuation (alloc_prefix, forward_multimodal_capture / _continue,
+// model.rs:954-1073, for text positions) ----
+
+void s1_prefix_destroy(void* prefix) {
+    Prefix* p = static_cast<Prefix*>(prefix);
+    if (!p) return;
+    if (p->owner) cs1_set_device(p->owner->device);
+    for (auto* list : {&p->k, &p->v, &p->state, &p->tail})
+        for (void* b : *list)
+            if (b) cs1_free(b);
+    delete p;
+}
+
+int s1_prefix_create(void* model, int len, void** out) {
+    Model* m = static_cast<Model*>(model);
+    if (!m || !out || len < 64 || len % 64 || len > m->cfg.max_positions) return S1_ERR_ARGUMENT;
+    S1_TRY(cs1_set_device(m->device));
+    Prefix* p = new Prefix();
+    p->owner = m;
+    p->len = len;
+    const size_t kv = (size_t)len * m->cfg.kv_heads * m->cfg.head_dim * BF16;
+    const size_t state = (size_t)m->cfg.lin_v_heads * 128 * 128 * F32, tail = (size_t)TAIL_ROWS * m->gdn_in_w() * BF16;
+    int rc = 0;
+    auto take = [&](std::vector<void*>& list, size_t bytes) {
+        void* b = nullptr;
+        if (rc == 0) rc = cs1_malloc(&b, bytes);
+        if (rc == 0) {
+            list.push_back(b);
+            p->bytes += bytes;
+        }
+    };
+    for (const Layer& ly : m->layers) {
+        if (ly.full) {
+            take(p->k, kv);
+            take(p->v, kv);
+        } else {
+            take(p->state, state);
+            take(p->tail, tail);
+        }
+    }
+    if (rc != 0) {
+        s1_prefix_destroy(p);
+        return rc;
+    }
+    *out = p;
+    return 0;
+}
+
+size_t s1_prefix_bytes(void* prefix) { return prefix ? static_cast<Prefix*>(prefix)->bytes : 0; }
+int s1_prefix_len(void* prefix) { return prefix ? static_cast<Prefix*>(prefix)->len : 0; }
+
+int s1_model_prefix_capture(void* model, const int32_t* ids, int len, void* prefix) {
+    Model* m = static_cast<Model*>(model);
+    Prefix* p = static_cast<Prefix*>(prefix);
+    if (!m || !ids || !p || p->owner != m || len != p->len) return S1_ERR_ARGUMENT;
+    for (int i = 0; i < len; i++)
+        if (ids[i] < 0 || ids[i] >= m->cfg.vocab) return S1_ERR_ARGUMENT;
+    p->ready = false;
+    S1_TRY(prepare_scratch(m, (size_t)len));
+    const Scratch& s = m->s;
+    S1_TRY(cs1_upload(s.at(s.ids), ids, (size_t)len * 4, m->stream));
+    S1_OP(S1_FAMILY_OTHER, 1,
+          cs1_embed(reinterpret_cast<const int32_t*>(s.at(s.ids)), m->w(m->embed), s.at(s.res), len, m->cfg.hidden,
+                    m->stream));
+    S1_TRY(run_window(m, &len, 1, p, nullptr));
+    S1_TRY(cs1_stream_sync(m->stream));
+    p->ready = true;
+    return 0;
+}
+
+int s1_model_forward_continue(void* model, const void* prefix, const int32_t* ids, const int* lengths, int nseq,
+                              float* last_hidden) {
+    Model* m = static_cast<Model*>(model);
+    const Prefix* p = static_cast<const Prefix*>(prefix);
+    if (!m || !p || p->owner != m || !p->ready || !ids || !last_hidden || nseq <= 0 || !lengths) return S1_ERR_ARGUMENT;
+    long tokens = 0, longest = 0;
+    for (int i = 0; i < nseq; i++) {
+        if (lengths[i] <= 0 || (long)p->len + lengths[i] > m->cfg.max_positions) return S1_ERR_ARGUMENT;
+        tokens += lengths[i];
+        longest = std::max<long>(longest, lengths[i]);
+    }
+    for (long i = 0; i < tokens; i++)
+        if (ids[i] < 0 || ids[i] >= m->cfg.vocab) return S1_ERR_ARGUMENT;
+    // packed rows: three lead rows in front of every continuation (see run_window)
+    const long rows = tokens + (long)TAIL_ROWS * nseq;
+    if (rows > 0x7fffffffL) return S1_ERR_ARGUMENT;
+    std::vector<int32_t> packed_ids;
+    std::vector<int> packed_len(nseq);
+    packed_ids.reserve(rows);
+    long at = 0;
+    for (int i = 0; i < nseq; i++) {
+        packed_ids.insert(packed_ids.end(), TAIL_ROWS, ids[at]);
+        packed_ids.insert(packed_ids.end(), ids + at, ids + at + lengths[i]);
+        packed_len[i] = lengths[i] + TAIL_ROWS;
+        at += lengths[i];
+    }
+    // the rotary tables are as long as the scratch: cover the last position too
+    S1_TRY(prepare_scratch(m, (size_t)std::max<long>(rows, p->len + longest)));
+    const Scratch& s = m->s;
+    const int h = m->cfg.hidden;
+    S1_TRY(cs1_upload(s.at(s.ids), packed_ids.data(), (size_t)rows * 4, m->stream));
+    S1_TRY(stage_ends(m, packed_len.data(), nseq));
+    S1_OP(S1_FAMILY_OTHER, 1,
+          cs1_embed(reinterpret_cast<const int32_t*>(s.at(s.ids)), m->w(m->embed), s.at(s.res), (int)rows, h, m->stream));
+    S1_TRY(run_window(m, packed_len.data(), nseq, nullptr, p));
+    S1_OP(S1_FAMILY_OTHER, 1,
+          s1::gather_rows(s.at(s.x), reinterpret_cast<const int*>(s.at(s.ends)), s.at(s.last), nseq, h,
+                          static_cast<cudaStream_t>(m->stream)));
+    std::vector<uint16_t> out((size_t)nseq * h);
+    S1_TRY(cs1_download(out.data(), s.at(s.last), out.size() * BF16, m->stream));
+    for (size_t i = 0; i < out.size(); i++) last_hidden[i] = bf2f(out[i]);
     return 0;
 }
 

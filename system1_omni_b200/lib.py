@@ -94,6 +94,13 @@ SIGNATURES = {
     "s1_gemm_swiglu": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "s1_model_set_exact_packing": (i32, [vp, i32]),
     "s1_model_set_fused_mlp": (i32, [vp, i32]),
+    "s1_attention_gated_shared_prefix": (i32, [vp, vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp]),
+    "s1_prefix_create": (i32, [vp, i32, vp]),
+    "s1_prefix_destroy": (None, [vp]),
+    "s1_prefix_bytes": (C.c_size_t, [vp]),
+    "s1_prefix_len": (i32, [vp]),
+    "s1_model_prefix_capture": (i32, [vp, vp, i32, vp]),
+    "s1_model_forward_continue": (i32, [vp, vp, vp, vp, i32, vp]),
     "s1_model_create": (i32, [C.POINTER(S1Config), i32, vpp]),
     "s1_model_destroy": (None, [vp]),
     "s1_model_set_tensor": (i32, [vp, C.c_char_p, vp, sz]),

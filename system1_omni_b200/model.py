@@ -140,6 +140,22 @@ def tensor_shapes(cfg):
     return out
 
 
+class Prefix:
+    """Device-side state of a captured prefix; owned by the model that captured it."""
+
+    def __init__(self, handle, length):
+        self.handle, self.length = handle, length
+
+    @property
+    def nbytes(self):
+        return int(L.load().s1_prefix_bytes(self.handle)) if self.handle else 0
+
+    def close(self):
+        if self.handle:
+            L.load().s1_prefix_destroy(self.handle)
+            self.handle = None
+
+
 class Model:
     """One decoder on one GPU: weights, scratch, stream, GEMM handle and graph cache."""
 
@@ -223,6 +239,41 @@ class Model:
             last.ctypes.data_as(C.c_void_p), None if layers is None else layers.ctypes.data_as(C.c_void_p))
         L.check(code, "forward_batch")
         return (last, layers) if want_layers else last
+
+    # ---- prefix capture / continuation (PrefixState, model.rs:557-588, 954-1073) ----
+    def capture_prefix(self, ids):
+        """Run a prefix (a positive multiple of 64 tokens) once and keep its per-layer state on
+        the device. Returns a Prefix to pass to forward_continue; release it with .close()."""
+        ids = np.ascontiguousarray(np.asarray(ids, np.int64))
+        if ids.size and (ids.min() < 0 or ids.max() >= 2 ** 31):
+            raise ValueError("token id outside the vocabulary")
+        ids = ids.astype(np.int32)
+        handle = C.c_void_p()
+        L.check(L.load().s1_prefix_create(self.handle, int(ids.size), C.byref(handle)), "prefix create")
+        prefix = Prefix(handle, int(ids.size))
+        try:
+            L.check(L.load().s1_model_prefix_capture(self.handle, ids.ctypes.data_as(C.c_void_p), int(ids.size), handle),
+                    "prefix capture")
+        except Exception:
+            prefix.close()
+            raise
+        return prefix
+
+    def forward_continue(self, prefix, candidates):
+        """candidates: token id sequences that each continue the captured prefix. Returns the
+        final-norm hidden state of every candidate's last token, float32 [n, hidden] - what
+        forward_batch returns for the prompts prefix + candidate."""
+        lengths = np.array([len(x) for x in candidates], np.int32)
+        ids = np.ascontiguousarray(np.concatenate([np.asarray(x, np.int64) for x in candidates]) if len(candidates)
+                                   else np.zeros(0, np.int64))
+        if ids.size and (ids.min() < 0 or ids.max() >= 2 ** 31):
+            raise ValueError("token id outside the vocabulary")
+        ids = ids.astype(np.int32)
+        last = np.zeros((len(candidates), self.cfg.hidden), np.float32)
+        L.check(L.load().s1_model_forward_continue(self.handle, prefix.handle, ids.ctypes.data_as(C.c_void_p),
+                                                   lengths.ctypes.data_as(C.c_void_p), len(candidates),
+                                                   last.ctypes.data_as(C.c_void_p)), "forward_continue")
+        return last
 
     def forward_flat(self, ids, lengths):
         """The same pass on an int32 array used in place (e.g. a view of pinned host memory)."""
