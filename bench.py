@@ -19,7 +19,7 @@ One JSON line on rank 0:
   cpu_baseline  the CPU oracle (a port of the reference's arithmetic, OpenMP) on a bounded
              sample of the same workload, N = 1 only
 --impl reference times that CPU oracle as the reference arm (the reference has no CPU
-forward pass of its own).
+forward pass of its own: its CPU code for this path is the float64 test oracles the port restates).
 """
 import argparse
 import ctypes as C
@@ -53,7 +53,7 @@ def cfg2(layers=32):
 
 
 def gemm_flops_per_token(cfg):
-    """2*N*K summed over the projections of every layer (the figure DESIGN.md derives)."""
+    """2*N*K summed over the projections of every layer: the GEMM FLOPs one token costs."""
     h, I, kd, vd, hv = cfg.hidden, cfg.intermediate, cfg.key_dim, cfg.value_dim, cfg.lin_v_heads
     gdn = (2 * kd + vd + vd + 2 * hv) * h + h * vd
     att = (cfg.heads * cfg.head_dim * 2 + 2 * cfg.kv_heads * cfg.head_dim) * h + h * cfg.heads * cfg.head_dim

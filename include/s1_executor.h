@@ -87,10 +87,12 @@ void* s1_model_stream(void* model);
  * CUA_S1_GRAPH=1 is in the environment at creation, as in the reference (model.rs:695). */
 int s1_model_enable_graphs(void* model, int on);
 /* Exact packing (off by default): a prompt's hidden states come out bit-identical whether it
- * runs alone or inside a pack. The projections back to the hidden size then run per sequence,
- * as the reference does (model.rs:723-739), and the packed GEMMs run without a K split. With
- * it off every GEMM runs once over the pack and may split K by the row count: faster, and
- * equal to single execution within rounding (the reference's gate is 0.01 on the logits). */
+ * runs alone, inside a pack, or as a continuation of a captured prefix. Every GEMM then runs on
+ * whole tiles (no K range shared between blocks), which makes a row's result independent of the
+ * call's row count; a shape this library's engine does not take (cuBLASLt) runs per sequence,
+ * as the reference does for its out/down projections (model.rs:723-739). With it off the
+ * planner may share K by the row count: faster on a few shapes, and equal to single execution
+ * within rounding (the reference's gate is 0.01 on the logits). */
 int s1_model_set_exact_packing(void* model, int on);
 /* The MLP's gate/up projection and SiLU-multiply as one kernel (s1_gemm_swiglu; on by default,
  * same bits as the two operators). Off: always the reference's two-operator sequence. */

@@ -305,30 +305,30 @@ int op(Model* m, int family, int kernels, F&& call) {
 }
 #define S1_OP(family, kernels, expr) S1_TRY(op(m, family, kernels, [&] { return (expr); }))
 
-int gemm(Model* m, size_t x, const Tensor& w, size_t y, int rows, int n, int k, bool packed = true) {
+int gemm(Model* m, size_t x, const Tensor& w, size_t y, int rows, int n, int k) {
     const bool own = s1_gemm_engine(m->gemm, m->s.at(x), m->w(w), rows, n, k) == 1;
     if (!own) m->library_launches++;
     return op(m, S1_FAMILY_GEMM, own ? 1 : 0, [&] {
-        // packed rows under exact packing: no K split, so a row's sum does not depend on the pack
-        if (m->exact_packing && packed)
+        // exact packing: whole tiles only, so a row's sum over K runs in one fixed order
+        // whatever the row count of the call (packed, alone, or continuing a prefix)
+        if (m->exact_packing)
             return s1_gemm_unsplit(m->gemm, m->s.at(x), m->w(w), m->s.at(y), rows, n, k, n, m->stream);
         return cs1_gemm(m->gemm, m->s.at(x), m->w(w), m->s.at(y), rows, n, k, n, m->stream);
     });
 }
 
-// The projections back to the hidden size (out / o / down). With exact packing they run per
-// sequence, as the reference does (gemm_sequences, model.rs:723-739), so that a prompt sees
-// the same GEMM shape - and the same K-split plan - packed or alone; otherwise once over
-// the whole pack, which is faster and equal within rounding.
+// The projections back to the hidden size (out / o / down). The reference runs them per
+// sequence (gemm_sequences, model.rs:723-739) so that a prompt sees the same GEMM shape, hence
+// the same library plan, packed or alone. Under exact packing this library's own engine needs
+// no such split (whole tiles make rows independent of the row count); only a shape that goes
+// to cuBLASLt is still run per sequence. Without exact packing: once over the pack.
 int gemm_rows(Model* m, size_t x, const Tensor& w, size_t y, const int* lengths, int nseq, int n, int k) {
-    if (!m->exact_packing) {
-        int t = 0;
-        for (int i = 0; i < nseq; i++) t += lengths[i];
-        return gemm(m, x, w, y, t, n, k);
-    }
+    int t = 0;
+    for (int i = 0; i < nseq; i++) t += lengths[i];
+    if (!m->exact_packing || s1_gemm_engine(m->gemm, m->s.at(x), m->w(w), t, n, k) == 1) return gemm(m, x, w, y, t, n, k);
     size_t off = 0;
     for (int i = 0; i < nseq; i++) {
-        S1_TRY(gemm(m, x + off * k * BF16, w, y + off * n * BF16, lengths[i], n, k, /*packed=*/false));
+        S1_TRY(gemm(m, x + off * k * BF16, w, y + off * n * BF16, lengths[i], n, k));
         off += lengths[i];
     }
     return 0;
@@ -448,6 +448,7 @@ struct Prefix {
     int len = 0;
     std::vector<void*> k, v;         // [len, Hk * Dh] bf16 each
     std::vector<void*> state, tail;  // [H, 128, 128] float32; [3, gdn_in] bf16
+    void* arena = nullptr;           // the one allocation they are carved from
     size_t bytes = 0;
 };
 
@@ -814,9 +815,7 @@ void s1_prefix_destroy(void* prefix) {
     Prefix* p = static_cast<Prefix*>(prefix);
     if (!p) return;
     if (p->owner) cs1_set_device(p->owner->device);
-    for (auto* list : {&p->k, &p->v, &p->state, &p->tail})
-        for (void* b : *list)
-            if (b) cs1_free(b);
+    if (p->arena) cs1_free(p->arena);
     delete p;
 }
 
@@ -829,14 +828,11 @@ int s1_prefix_create(void* model, int len, void** out) {
     p->len = len;
     const size_t kv = (size_t)len * m->cfg.kv_heads * m->cfg.head_dim * BF16;
     const size_t state = (size_t)m->cfg.lin_v_heads * 128 * 128 * F32, tail = (size_t)TAIL_ROWS * m->gdn_in_w() * BF16;
-    int rc = 0;
+    // one allocation, carved at 256-byte boundaries (the reference allocates each buffer, model.rs:968-989)
+    size_t at = 0;
     auto take = [&](std::vector<void*>& list, size_t bytes) {
-        void* b = nullptr;
-        if (rc == 0) rc = cs1_malloc(&b, bytes);
-        if (rc == 0) {
-            list.push_back(b);
-            p->bytes += bytes;
-        }
+        list.push_back(reinterpret_cast<void*>(at));
+        at += (bytes + ALIGN - 1) / ALIGN * ALIGN;
     };
     for (const Layer& ly : m->layers) {
         if (ly.full) {
@@ -847,10 +843,14 @@ int s1_prefix_create(void* model, int len, void** out) {
             take(p->tail, tail);
         }
     }
+    p->bytes = at;
+    const int rc = cs1_malloc(&p->arena, at);
     if (rc != 0) {
-        s1_prefix_destroy(p);
+        delete p;
         return rc;
     }
+    for (auto* list : {&p->k, &p->v, &p->state, &p->tail})
+        for (void*& b : *list) b = static_cast<char*>(p->arena) + reinterpret_cast<size_t>(b);
     *out = p;
     return 0;
 }

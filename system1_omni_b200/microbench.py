@@ -228,6 +228,71 @@ def layer(b, out):
         lay.close()
 
 
+def prefix(b, out):
+    """Shared prefix + candidates on a 9B-shaped decoder (hidden 4096, 32 layers 3:1, 16 qk / 32 v
+    GDN heads, 32 q / 8 kv attention heads of 128, MLP 12288): a 1536-token prefix and 8
+    candidates of 32..128 tokens. Times the one-shot packed pass over the 8 full prompts, the
+    capture + packed continuation pair, and the continuation alone (prefix already cached)."""
+    import time
+    from . import model as M
+    types = [("full_attention" if (i + 1) % 4 == 0 else "linear_attention") for i in range(32)]
+    cfg = M.Config(hidden=4096, intermediate=12288, layer_types=types, heads=32, kv_heads=8, head_dim=128,
+                   rotary_half=32, lin_k_heads=16, lin_v_heads=32, vocab=151936, eps=1e-6, rope_theta=1e7,
+                   max_positions=262144)
+    model = M.Model(cfg, device=0)
+    model.init_random(seed=0, std=0.02)
+    rng = np.random.default_rng(0)
+    pre = rng.integers(0, cfg.vocab, 1536).tolist()
+    cands = [rng.integers(0, cfg.vocab, int(n)).tolist() for n in rng.integers(32, 129, 8)]
+    logical = len(pre) + sum(len(c) for c in cands)
+    prompts = [pre + c for c in cands]
+    packs = M.ranges([len(p) for p in prompts])
+
+    def one_shot():
+        return np.concatenate([model.forward_batch([prompts[i] for i in pack]) for pack in packs])
+
+    def pair():
+        p = model.capture_prefix(pre)
+        try:
+            return model.forward_continue(p, cands)
+        finally:
+            p.close()
+
+    def wall(fn, warm=2, n=5):
+        for _ in range(warm):
+            r = fn()
+        model.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            r = fn()
+        model.synchronize()
+        return (time.perf_counter() - t0) / n * 1e3, r
+
+    ms_one, ref = wall(one_shot)
+    ms_pair, got = wall(pair)
+    cached = model.capture_prefix(pre)
+    ms_cont, got2 = wall(lambda: model.forward_continue(cached, cands))
+    cached.close()
+    # with every GEMM pinned to whole tiles the two ways must agree bit for bit
+    model.set_exact_packing(True)
+    exact_ref = np.concatenate([model.forward_batch([p]) for p in prompts[:2]])
+    cached = model.capture_prefix(pre)
+    exact_got = model.forward_continue(cached, cands[:2])
+    cached.close()
+    model.set_exact_packing(False)
+    scale = max(1.0, float(np.abs(ref).max()))
+    rel_l2 = float(np.linalg.norm(got - ref) / np.linalg.norm(ref))
+    out({"op": "shared_prefix_request", "model": "9B-shaped", "prefix": len(pre), "candidates": [len(c) for c in cands],
+         "logical_tokens": logical, "executed_tokens_one_shot": sum(len(p) for p in prompts), "packs_one_shot": len(packs),
+         "one_shot_ms": ms_one, "capture_plus_continue_ms": ms_pair, "continue_only_ms": ms_cont,
+         "one_shot_logical_tokens_per_s": logical / ms_one * 1e3,
+         "capture_plus_continue_logical_tokens_per_s": logical / ms_pair * 1e3,
+         "max_abs_diff_vs_one_shot": float(np.abs(got - ref).max()), "max_abs_diff_cached": float(np.abs(got2 - ref).max()),
+         "relative_l2_vs_one_shot": rel_l2, "hidden_scale": scale,
+         "bit_exact_with_whole_tile_gemms": bool(np.array_equal(exact_ref, exact_got)), "timing": "host wall clock around the public calls"})
+    model.close()
+
+
 def attention(b, out):
     lib, st = b.lib, b.stream.handle
     for dh, hq, hk in [(128, 16, 4), (128, 24, 4), (256, 16, 4), (256, 24, 4)]:
@@ -244,7 +309,7 @@ def attention(b, out):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", default="all", choices=["elementwise", "gemm", "gdn", "layer", "attention", "all"])
+    ap.add_argument("--what", default="all", choices=["elementwise", "gemm", "gdn", "layer", "attention", "prefix", "all"])
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--out", default=None)
@@ -268,6 +333,8 @@ def main():
                      ("attention", attention)):
         if args.what in (name, "all"):
             fn(b, out)
+    if args.what == "prefix":  # builds a 9B-shaped model (14 GB of weights): only on request
+        prefix(b, out)
     if sink:
         sink.close()
 

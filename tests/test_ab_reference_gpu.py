@@ -2,8 +2,9 @@
 kernels compiled for sm_100) on the operators of the Gated DeltaNet layer, at the shapes the
 reference published timings for (H = 48, HK = 16, T in {107, 936, 3399}) and the model
 shapes. Protocol after benchmarks/gdn/README.md:47-51 of the reference: warm-ups, then timed
-calls between events, arms alternated. Writes gpurun_out/ab_reference.json and asserts that
-this library is not slower where it claims a win. Skipped when oracle/_ref is absent."""
+calls between events, arms alternated. Writes ab_reference.json into $S1_RESULTS_DIR (when set)
+and asserts that this library is not slower where it claims a win. Skipped when oracle/_ref is
+absent."""
 import ctypes as C
 import json
 import os
@@ -96,9 +97,11 @@ def test_speed_against_the_reference_library(ref, cs1, stream):
                                                                 hk, dh, 0.0625, st) for lib in (ref, cs1)])
     rows.append({"op": "attention_gated", "T": T, "Hq": hq, "Dh": dh, "reference_us": r, "this_us": m, "speedup": r / m})
 
-    os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-    with open(os.path.join(ROOT, "gpurun_out", "ab_reference.json"), "w") as f:
-        json.dump(rows, f, indent=1)
+    results_dir = os.environ.get("S1_RESULTS_DIR")
+    if results_dir:
+        os.makedirs(results_dir, exist_ok=True)
+        with open(os.path.join(results_dir, "ab_reference.json"), "w") as f:
+            json.dump(rows, f, indent=1)
     for row in rows:
         print(json.dumps({k: (round(v, 2) if isinstance(v, float) else v) for k, v in row.items()}))
     by = {(r_["op"], r_.get("T")): r_ for r_ in rows}
