@@ -40,6 +40,10 @@ int s1_attention_gated_shared_prefix(const void* q, const void* k, const void* v
                                      const void* k_prefix, const void* v_prefix, int ldv_prefix, int prefix_len,
                                      int rows, int Hq, int Hk, int Dh, float scale, void* stream);
 
+/* The attention kernel's counterpart of s1_gemm_tc5_status: its device error word (0 = no bounded
+ * wait ever gave up), read after waiting for all queued work, then cleared. */
+int s1_attn_tc5_status(int* code);
+
 /* ---- GEMM engines behind cs1_gemm, pinned (benchmark arms and parity tests) ---- */
 int s1_gemm_cublaslt(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream);
 /* cs1_gemm with the K-split path switched off for this call. */

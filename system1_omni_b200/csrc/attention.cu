@@ -12,6 +12,7 @@
 // tests/qwen3_5/kernels.rs:273-474,852-929).
 #include <math.h>
 
+#include "attention_tc5.h"
 #include "common.cuh"
 #include "cs1_ops.h"
 #include "mma.cuh"
@@ -288,6 +289,10 @@ int attention_entry(const void* q, const void* k, const void* v, int ldv, const 
     const bf16 *qp = static_cast<const bf16*>(q), *kp = static_cast<const bf16*>(k), *vp = static_cast<const bf16*>(v);
     const bf16* gp = static_cast<const bf16*>(gate);
     bf16* op = static_cast<bf16*>(out);
+    // one kernel for every size, so that a window and the one-shot pass round alike
+    if (s1_attn_tc5_enabled())
+        return s1_attn_tc5(qp, kp, vp, ldv, GATED ? gp : nullptr, op, T, Hq, Hk, Dh, scale, q_base, nullptr, nullptr, 0, 0,
+                           as_stream(stream));
     if (Dh == 256) return launch_flash<256, 32, GATED>(qp, kp, vp, ldv, gp, op, T, Hq, Hk, scale, q_base, as_stream(stream));
     return launch_flash<128, 64, GATED>(qp, kp, vp, ldv, gp, op, T, Hq, Hk, scale, q_base, as_stream(stream));
 }
@@ -358,6 +363,9 @@ extern "C" int s1_attention_gated_shared_prefix(const void* q, const void* k, co
     const bf16* gp = static_cast<const bf16*>(gate);
     bf16* op = static_cast<bf16*>(out);
     const int T = prefix_len + rows;
+    if (s1_attn_tc5_enabled())
+        return s1_attn_tc5(qp, kp, vp, ldv, gp, op, T, Hq, Hk, Dh, scale, prefix_len, kpre, vpre, ldv_prefix, prefix_len,
+                           as_stream(stream));
     if (Dh == 256)
         return launch_flash<256, 32, true>(qp, kp, vp, ldv, gp, op, T, Hq, Hk, scale, prefix_len, as_stream(stream), kpre,
                                            vpre, ldv_prefix, prefix_len);

@@ -1,0 +1,448 @@
+// Causal GQA flash attention for sm_100a on tcgen05: one block per (128 query rows, query head).
+//
+//   warp 0    TMA producer: the Q tile once, then K and V tiles of BN keys through two stages
+//             each ([64 rows, 64 columns] boxes, 128-byte swizzle)
+//   warp 1    one thread issues the MMAs: S = Q K^T (128 x BN, K-major operands) into one of two
+//             score buffers in tensor memory, and O += P V (128 x Dh; V is read MN-major, as it
+//             lies in memory) into the output accumulator, also in tensor memory
+//   warps 2-5 one query row per thread: tcgen05.ld the scores, scale, causal mask, online
+//             softmax in base 2 (row statistics in registers, no shuffles), rescale O in tensor
+//             memory when a row maximum moved, write P (bf16) into shared memory in the
+//             operand layout, and at the end normalise, gate and store the row
+//
+// The score MMA of tile j + 1 is issued before the P V MMA of tile j, so it runs under tile
+// j's softmax. Same arithmetic contract as the mma.sync kernel in attention.cu (attention.cu:110-233
+// of the reference): P rounded to bf16 before P V, the row sum taken from the unrounded p, output
+// divided by the sum, then the gate. A row's result does not depend on where its 128-row block
+// starts, only on the key tiling (tiles of BN from position 0), so windows that start at a
+// multiple of 64 repeat the one-shot arithmetic. Every barrier wait is bounded.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "attention_tc5.h"
+#include "common.cuh"
+#include "cs1_ops.h"
+#include "tc5.cuh"
+#include "tmap.h"
+
+namespace s1 {
+namespace {
+
+constexpr int ABM = 128;       // query rows per block
+constexpr int ATHREADS = 192;  // producer warp, MMA warp, four softmax warps
+
+template <int DH>
+struct ACfg {
+    static constexpr int BN = DH == 128 ? 128 : 64;   // keys per tile
+    static constexpr int Q_BYTES = ABM * DH * 2;       // DH / 64 boxes of [128 rows, 64 columns]
+    static constexpr int KV_BYTES = BN * DH * 2;       // one K or V tile: DH / 64 column boxes of [BN rows, 64]
+    static constexpr int P_BYTES = ABM * BN * 2;       // BN / 64 boxes of [128 rows, 64 keys]
+    static constexpr int OFF_K = Q_BYTES;
+    static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;
+    static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
+    static constexpr int OFF_BAR = OFF_P + P_BYTES;
+    static constexpr int SMEM = OFF_BAR + 256 + 1024;  // 193 KB (Dh 128), 209 KB (Dh 256): one block per SM
+    static constexpr int O_COL = 2 * BN;               // tensor memory: two score buffers, then the output
+    static constexpr int TMEM_COLS = 512;
+};
+
+__device__ int g_attn_error = 0;
+
+struct AttnMaps {
+    CUtensorMap q, k, v, kpre, vpre;
+};
+
+// The four softmax warps: thread (warp & 3) * 32 + lane owns query row q0 + that index, which is
+// also its lane of tensor memory.
+template <int DH, bool GATED>
+__device__ __forceinline__ void softmax_rows(unsigned char* smem, uint64_t* bars, uint32_t tmem_base,
+                                             volatile int* abort_flag, const bf16* __restrict__ gate,
+                                             bf16* __restrict__ out, int T, int Hq, int h, int q0, int own_base, int ntiles,
+                                             float scale_log2, int vec_ok, int warp, int lane) {
+    using namespace tc5;
+    using G = ACfg<DH>;
+    constexpr int BN = G::BN;
+    uint64_t *s_full = bars + 9, *s_empty = bars + 11, *p_full = bars + 13, *o_done = bars + 14;
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int row = q0 + r;
+    const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    unsigned char* p_row = smem + G::OFF_P + r * 128;
+    const int sw = r & 7;
+    auto fail = [&](int code) {
+        atomicCAS(&g_attn_error, 0, code);
+        *abort_flag = 1;
+    };
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+#pragma unroll 1
+    for (int j = 0; j < ntiles; j++) {
+        const int b = j & 1;
+        if (!mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag)) {
+            fail(31);
+            ok = false;
+            break;
+        }
+        fence_after_sync();
+        uint32_t sv[BN];
+#pragma unroll
+        for (int cc = 0; cc < BN / 32; cc++)
+            tmem_ld_32x32(t_row + b * BN + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[cc * 32]));
+        tmem_ld_wait();
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_empty[b]);
+
+        const int k0 = j * BN;
+        float mx = -INFINITY;
+        if (k0 + BN - 1 > row) {
+#pragma unroll
+            for (int i = 0; i < BN; i++)
+                if (k0 + i > row) sv[i] = 0xff800000u;  // -inf
+        }
+#pragma unroll
+        for (int i = 0; i < BN; i++) mx = fmaxf(mx, __uint_as_float(sv[i]));
+        const float mn = fmaxf(m, mx * scale_log2);
+        const float alpha = exp2f(m - mn);
+        m = mn;
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < BN; i++) {
+            const float p = exp2f(__uint_as_float(sv[i]) * scale_log2 - mn);
+            sv[i] = __float_as_uint(p);
+            sum += p;
+        }
+        l = l * alpha + sum;
+
+        if (j > 0) {
+            // P V of the previous tile is complete: the accumulator may be rescaled and P overwritten
+            if (!mbar_wait(o_done, (j - 1) & 1, abort_flag)) {
+                fail(32);
+                ok = false;
+                break;
+            }
+            fence_after_sync();
+            if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+                for (int cc = 0; cc < DH / 32; cc++) {
+                    uint32_t o[32];
+                    tmem_ld_32x32(t_row + G::O_COL + cc * 32, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st_32x32(t_row + G::O_COL + cc * 32, o);
+                }
+                tmem_st_wait();
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < BN / 64; c++) {
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) {
+                const uint32_t* v = &sv[c * 64 + ch * 8];
+                uint4 w;
+                w.x = pack2(__uint_as_float(v[0]), __uint_as_float(v[1]));
+                w.y = pack2(__uint_as_float(v[2]), __uint_as_float(v[3]));
+                w.z = pack2(__uint_as_float(v[4]), __uint_as_float(v[5]));
+                w.w = pack2(__uint_as_float(v[6]), __uint_as_float(v[7]));
+                *reinterpret_cast<uint4*>(p_row + c * (ABM * 128) + ((ch ^ sw) * 16)) = w;
+            }
+        }
+        fence_proxy_async();
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full);
+    }
+    if (!ok || ntiles == 0) return;
+    if (!mbar_wait(o_done, (ntiles - 1) & 1, abort_flag)) {
+        fail(33);
+        return;
+    }
+    fence_after_sync();
+    const float inv = 1.f / l;
+    const size_t base = ((size_t)(row - own_base) * Hq + h) * DH;
+#pragma unroll 1
+    for (int cc = 0; cc < DH / 32; cc++) {
+        uint32_t o[32];
+        tmem_ld_32x32(t_row + G::O_COL + cc * 32, o);
+        tmem_ld_wait();
+        if (row >= T) continue;
+        float y[32];
+#pragma unroll
+        for (int i = 0; i < 32; i++) y[i] = __uint_as_float(o[i]) * inv;
+        if constexpr (GATED) {
+            // attention -> bf16 store -> bf16 sigmoid -> multiply, without the store
+            const uint32_t* gp = reinterpret_cast<const uint32_t*>(gate + base + cc * 32);
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const uint32_t gw = gp[i];
+                y[2 * i] = rbf(y[2 * i]) * rbf(sigmoid(__uint_as_float(gw << 16)));
+                y[2 * i + 1] = rbf(y[2 * i + 1]) * rbf(sigmoid(__uint_as_float(gw & 0xffff0000u)));
+            }
+        }
+        bf16* dst = out + base + cc * 32;
+        if (vec_ok) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                uint4 w;
+                w.x = pack2(y[8 * q + 0], y[8 * q + 1]);
+                w.y = pack2(y[8 * q + 2], y[8 * q + 3]);
+                w.z = pack2(y[8 * q + 4], y[8 * q + 5]);
+                w.w = pack2(y[8 * q + 6], y[8 * q + 7]);
+                *reinterpret_cast<uint4*>(dst + 8 * q) = w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; i++) *reinterpret_cast<uint32_t*>(dst + 2 * i) = pack2(y[2 * i], y[2 * i + 1]);
+        }
+    }
+}
+
+template <int DH, bool GATED>
+__global__ void __launch_bounds__(ATHREADS, 1)
+    attn_tc5_kernel(const __grid_constant__ AttnMaps maps, const bf16* __restrict__ gate, bf16* __restrict__ out, int T,
+                    int Hq, int Hk, float scale_log2, int q_base, int own_base, int vec_ok) {
+    using namespace tc5;
+    using G = ACfg<DH>;
+    constexpr int BN = G::BN;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);
+    uint64_t* q_full = bars;          // 1
+    uint64_t* k_full = bars + 1;      // 2
+    uint64_t* v_full = bars + 3;      // 2
+    uint64_t* k_empty = bars + 5;     // 2
+    uint64_t* v_empty = bars + 7;     // 2
+    uint64_t* s_full = bars + 9;      // 2
+    uint64_t* s_empty = bars + 11;    // 2
+    uint64_t* p_full = bars + 13;     // 1
+    uint64_t* o_done = bars + 14;     // 1
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int h = blockIdx.y, hk = h / (Hq / Hk);
+    const int q0 = q_base + (gridDim.x - 1 - blockIdx.x) * ABM;  // longest blocks first
+    const int kv_end = min(T, q0 + ABM);
+    const int ntiles = (kv_end + BN - 1) / BN;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&v_full[i], 1);
+            mbar_init(&k_empty[i], 1);
+            mbar_init(&v_empty[i], 1);
+            mbar_init(&s_full[i], 1);
+            mbar_init(&s_empty[i], 4);
+        }
+        mbar_init(p_full, 4);
+        mbar_init(o_done, 1);
+        *abort_flag = 0;
+        mbar_init_fence();
+        prefetch_tmap(&maps.q);
+        prefetch_tmap(&maps.k);
+        prefetch_tmap(&maps.v);
+    }
+    if (warp == 2) {
+        tmem_alloc(tmem_slot, G::TMEM_COLS);
+        tmem_relinquish();
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    auto fail = [&](int code) {
+        atomicCAS(&g_attn_error, 0, code);
+        *abort_flag = 1;
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(q_full, G::Q_BYTES);
+            for (int c = 0; c < DH / 64; c++)
+                tma_load_2d(smem + c * (ABM * 128), &maps.q, h * DH + c * 64, q0 - own_base, q_full);
+            for (int j = 0; j < ntiles; j++) {
+                const int stage = j & 1;
+                const uint32_t parity = ((j >> 1) & 1) ^ 1;
+                // a tile is BN / 64 groups of 64 keys; a group lies wholly in the prefix or in the window
+                if (!mbar_wait(&k_empty[stage], parity, abort_flag)) {
+                    fail(21);
+                    break;
+                }
+                mbar_expect_tx(&k_full[stage], G::KV_BYTES);
+                for (int c = 0; c < DH / 64; c++)
+                    for (int g = 0; g < BN / 64; g++) {
+                        const int r0 = j * BN + g * 64;
+                        unsigned char* dst = smem + G::OFF_K + stage * G::KV_BYTES + c * (BN * 128) + g * (64 * 128);
+                        if (r0 < own_base)
+                            tma_load_2d(dst, &maps.kpre, hk * DH + c * 64, r0, &k_full[stage]);
+                        else
+                            tma_load_2d(dst, &maps.k, hk * DH + c * 64, r0 - own_base, &k_full[stage]);
+                    }
+                if (!mbar_wait(&v_empty[stage], parity, abort_flag)) {
+                    fail(22);
+                    break;
+                }
+                mbar_expect_tx(&v_full[stage], G::KV_BYTES);
+                for (int c = 0; c < DH / 64; c++)
+                    for (int g = 0; g < BN / 64; g++) {
+                        const int r0 = j * BN + g * 64;
+                        unsigned char* dst = smem + G::OFF_V + stage * G::KV_BYTES + c * (BN * 128) + g * (64 * 128);
+                        if (r0 < own_base)
+                            tma_load_2d(dst, &maps.vpre, hk * DH + c * 64, r0, &v_full[stage]);
+                        else
+                            tma_load_2d(dst, &maps.v, hk * DH + c * 64, r0 - own_base, &v_full[stage]);
+                    }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = instr_desc(1, ABM, BN);
+            constexpr uint32_t idesc_o = instr_desc_b_mn(1, ABM, DH);
+            const uint32_t q_addr = smem_addr(smem), p_addr = smem_addr(smem + G::OFF_P);
+            bool ok = mbar_wait(q_full, 0, abort_flag);
+            if (!ok) fail(23);
+            // P V of tile t: A = P (K-major over keys), B = V tile read MN-major
+            auto issue_pv = [&](int t) {
+                const int stage = t & 1;
+                if (!mbar_wait(p_full, t & 1, abort_flag)) {
+                    fail(26);
+                    return false;
+                }
+                if (!mbar_wait(&v_full[stage], (t >> 1) & 1, abort_flag)) {
+                    fail(27);
+                    return false;
+                }
+                fence_after_sync();
+                const uint32_t v_addr = smem_addr(smem + G::OFF_V + stage * G::KV_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; kk++) {
+                    const uint64_t a = smem_desc_sw128(p_addr + (kk / 4) * (ABM * 128) + (kk % 4) * 32);
+                    const uint64_t b = smem_desc_mn_sw128(v_addr + kk * 2048, BN * 128, 1024);
+                    mma_bf16_ss(tmem_base + G::O_COL, a, b, idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
+                }
+                mma_commit(&v_empty[stage]);
+                mma_commit(o_done);
+                return true;
+            };
+            for (int j = 0; ok && j < ntiles; j++) {
+                const int stage = j & 1;
+                const uint32_t use = (j >> 1) & 1;
+                if (!mbar_wait(&k_full[stage], use, abort_flag)) {
+                    fail(24);
+                    ok = false;
+                    break;
+                }
+                if (!mbar_wait(&s_empty[stage], use ^ 1, abort_flag)) {
+                    fail(25);
+                    ok = false;
+                    break;
+                }
+                fence_after_sync();
+                const uint32_t k_addr = smem_addr(smem + G::OFF_K + stage * G::KV_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < DH / 16; kk++) {
+                    const uint64_t a = smem_desc_sw128(q_addr + (kk / 4) * (ABM * 128) + (kk % 4) * 32);
+                    const uint64_t b = smem_desc_sw128(k_addr + (kk / 4) * (BN * 128) + (kk % 4) * 32);
+                    mma_bf16_ss(tmem_base + stage * BN, a, b, idesc_s, kk > 0 ? 1u : 0u);
+                }
+                mma_commit(&k_empty[stage]);
+                mma_commit(&s_full[stage]);
+                if (j > 0) ok = issue_pv(j - 1);
+            }
+            if (ok && ntiles > 0) issue_pv(ntiles - 1);
+        }
+        __syncwarp();
+    } else {
+        softmax_rows<DH, GATED>(smem, bars, tmem_base, abort_flag, gate, out, T, Hq, h, q0, own_base, ntiles, scale_log2,
+                                vec_ok, warp, lane);
+    }
+
+    // wind down: after an abort give copies and MMAs in flight time to land before the
+    // shared memory and tensor memory are released
+    if (*abort_flag) __nanosleep(1000000);
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 2) tmem_dealloc(tmem_base, G::TMEM_COLS);
+}
+
+template <int DH, bool GATED>
+int launch_attn(const AttnMaps& maps, const bf16* gate, bf16* out, int T, int Hq, int Hk, float scale, int q_base,
+                int own_base, cudaStream_t st) {
+    using G = ACfg<DH>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 64) return cudaErrorInvalidDevice;
+    if (!configured[dev]) {
+        e = cudaFuncSetAttribute(attn_tc5_kernel<DH, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    constexpr float LOG2E = 1.4426950408889634f;
+    const dim3 grid((T - q_base + ABM - 1) / ABM, Hq);
+    const int vec_ok = aligned16(out) && (!GATED || aligned16(gate));
+    attn_tc5_kernel<DH, GATED><<<grid, ATHREADS, G::SMEM, st>>>(maps, gate, out, T, Hq, Hk, scale * LOG2E, q_base, own_base,
+                                                               vec_ok);
+    return cudaGetLastError();
+}
+
+}  // namespace
+}  // namespace s1
+
+using namespace s1;
+
+bool s1_attn_tc5_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("S1_ATTN");
+        return !(v && strcmp(v, "mma") == 0);
+    }();
+    return on;
+}
+
+int s1_attn_tc5(const bf16* q, const bf16* k, const bf16* v, int ldv, const bf16* gate, bf16* out, int T, int Hq, int Hk,
+                int Dh, float scale, int q_base, const bf16* kpre, const bf16* vpre, int ldvpre, int own_base,
+                cudaStream_t st) {
+    const uint64_t own_rows = (uint64_t)(T - own_base);
+    AttnMaps maps;
+    if (!tensor_map_2d(q, own_rows, (uint64_t)Hq * Dh, (uint64_t)Hq * Dh, ABM, &maps.q) ||
+        !tensor_map_2d(k, own_rows, (uint64_t)Hk * Dh, (uint64_t)Hk * Dh, 64, &maps.k) ||
+        !tensor_map_2d(v, own_rows, (uint64_t)Hk * Dh, (uint64_t)ldv, 64, &maps.v))
+        return CS1_ERR_TENSOR_MAP;
+    if (own_base > 0) {
+        if (!tensor_map_2d(kpre, (uint64_t)own_base, (uint64_t)Hk * Dh, (uint64_t)Hk * Dh, 64, &maps.kpre) ||
+            !tensor_map_2d(vpre, (uint64_t)own_base, (uint64_t)Hk * Dh, (uint64_t)ldvpre, 64, &maps.vpre))
+            return CS1_ERR_TENSOR_MAP;
+    } else {
+        maps.kpre = maps.k;
+        maps.vpre = maps.v;
+    }
+    if (Dh == 256)
+        return gate ? launch_attn<256, true>(maps, gate, out, T, Hq, Hk, scale, q_base, own_base, st)
+                    : launch_attn<256, false>(maps, gate, out, T, Hq, Hk, scale, q_base, own_base, st);
+    return gate ? launch_attn<128, true>(maps, gate, out, T, Hq, Hk, scale, q_base, own_base, st)
+                : launch_attn<128, false>(maps, gate, out, T, Hq, Hk, scale, q_base, own_base, st);
+}
+
+// The device error word of the attention kernel on the current device (0 = no bounded wait ever
+// gave up) after waiting for all queued work; cleared by the call.
+extern "C" int s1_attn_tc5_status(int* code) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return e;
+    int v = 0;
+    e = cudaMemcpyFromSymbol(&v, g_attn_error, sizeof(int));
+    if (e != cudaSuccess) return e;
+    if (v != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(g_attn_error, &zero, sizeof(int));
+    }
+    *code = v;
+    return e;
+}

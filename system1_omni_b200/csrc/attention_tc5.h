@@ -1,0 +1,14 @@
+// Internal interface of the tcgen05 attention kernel (attention_tc5.cu), used by attention.cu.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+// False when S1_ATTN=mma is in the environment (the mma.sync kernel then serves every call).
+bool s1_attn_tc5_enabled();
+// Causal GQA attention of positions [q_base, T) over keys [0, T). q, gate, out, k and v hold the
+// positions from own_base on (indexed from zero); keys and values of positions below own_base are
+// read from kpre / vpre (row stride ldvpre). gate null = ungated. Dh 128 or 256; q, k, v, kpre, vpre
+// 16-byte aligned, ldv and ldvpre multiples of 8. Returns 0, a cudaError_t or CS1_ERR_TENSOR_MAP.
+int s1_attn_tc5(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v, int ldv,
+                const __nv_bfloat16* gate, __nv_bfloat16* out, int T, int Hq, int Hk, int Dh, float scale, int q_base,
+                const __nv_bfloat16* kpre, const __nv_bfloat16* vpre, int ldvpre, int own_base, cudaStream_t stream);

@@ -117,6 +117,25 @@ __host__ __device__ constexpr uint32_t instr_desc(int fmt, int M, int N) {
            ((uint32_t)(M >> 4) << 24);
 }
 
+// Descriptor of an MN-major bf16 operand (the contraction index runs over rows): rows of 128
+// bytes = 64 consecutive MN elements of one k, rows of 8 consecutive k packed in 1024-byte
+// groups (stride byte offset), the next 64 MN elements lbo_bytes further on (leading byte
+// offset). This is what TMA writes for [k rows, 64 columns] boxes with the 128-byte swizzle,
+// one box per 64 columns. Advancing K by one MMA step (16 rows) adds 2048 bytes.
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes = 1024) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3ffff) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// instr_desc with the B operand MN-major (bit 16) and A K-major.
+__host__ __device__ constexpr uint32_t instr_desc_b_mn(int fmt, int M, int N) {
+    return instr_desc(fmt, M, N) | (1u << 16);
+}
+
 // D[tmem] (+)= A[smem] * B[smem]^T, issued by one thread.
 __device__ __forceinline__ void mma_bf16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                             uint32_t accumulate) {
@@ -149,6 +168,22 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
         : "r"(taddr)
         : "memory");
 }
+// The reverse of tmem_ld_32x32: lane i writes v[j] to row (lane base + i), column (col base + j).
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+        "%30,%31,%32};" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+        "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]),
+        "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]),
+        "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// Orders this thread's ordinary shared-memory writes before later reads by the asynchronous
+// units (TMA, tcgen05.mma): needed when threads, not TMA, fill an MMA operand.
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ---- CTA pairs (cta_group::2): two blocks of a cluster share one MMA of 256 rows ----

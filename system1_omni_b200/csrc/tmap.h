@@ -1,0 +1,13 @@
+// Host-side TMA tensor maps for row-major bf16 matrices (shared by the tcgen05 kernels).
+#pragma once
+#include <cuda.h>
+#include <stdint.h>
+
+namespace s1 {
+// Tensor map of a row-major bf16 matrix [rows, cols] whose rows are row_stride elements apart
+// (a multiple of 8), read in boxes of [box_rows, 64 columns] with the 128-byte swizzle. Rows and
+// columns outside the matrix read as zero. Maps are cached by their arguments. False when the
+// driver entry point is missing or refuses the arguments (base not 16-byte aligned, ...).
+bool tensor_map_2d(const void* ptr, uint64_t rows, uint64_t cols, uint64_t row_stride, uint32_t box_rows,
+                   CUtensorMap* out);
+}  // namespace s1

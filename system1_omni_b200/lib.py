@@ -91,6 +91,7 @@ SIGNATURES = {
     "s1_gemm_tcgen05": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "s1_gemm_tc5_status": (i32, [ip]),
     "s1_gemm_unsplit": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+    "s1_attn_tc5_status": (i32, [ip]),
     "s1_gemm_swiglu": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "s1_model_set_exact_packing": (i32, [vp, i32]),
     "s1_model_set_fused_mlp": (i32, [vp, i32]),
@@ -247,6 +248,12 @@ def from_device(buf, shape, dtype, stream, offset_bytes=0):
 def gemm_status():
     code = C.c_int(0)
     check(load().s1_gemm_tc5_status(C.byref(code)), "gemm status")
+    return code.value
+
+
+def attn_status():
+    code = C.c_int(0)
+    check(load().s1_attn_tc5_status(C.byref(code)), "attention status")
     return code.value
 
 
