@@ -147,6 +147,24 @@ enum {
     S1_FAMILY_NORM = 5, S1_FAMILY_GATED_NORM = 6, S1_FAMILY_SILU_MUL = 7, S1_FAMILY_ATTN_PREP = 8,
     S1_FAMILY_OTHER = 9, S1_FAMILIES = 10
 };
+/* ---- Safetensors checkpoints (Weights::load, model.rs:239-315) ----
+ * dir holds model.safetensors, or model.safetensors.index.json and the files it names. The
+ * language model's tensors are those under the first of the prefixes "model.language_model.",
+ * "model.", "" that has embed_tokens.weight. */
+/* Host only (no GPU needed): the prefix, the number of language-model tensors and, for
+ * index >= 0, that tensor's name without the prefix, dtype string, rank, shape (up to 8 extents)
+ * and byte size. Every out pointer is nullable. */
+int s1_checkpoint_inspect(const char* dir, char* prefix_out, size_t prefix_cap, int* n_tensors, int index,
+                          char* name_out, size_t name_cap, char* dtype_out, size_t dtype_cap, int* rank,
+                          uint64_t* shape8, uint64_t* bytes);
+/* Upload every tensor of the decoder from the checkpoint into the model's arena (tensors the
+ * decoder has no place for - lm_head, vision tower, MTP - are skipped). All must be bfloat16 and
+ * of the planned byte size; all planned tensors must be present. offender (nullable) receives the
+ * name of the tensor an error is about. */
+int s1_model_load_checkpoint(void* model, const char* dir, char* offender, size_t offender_cap);
+/* Number of planned tensors not yet given a value; the first one's name in name_out (nullable). */
+int s1_model_unfilled(void* model, char* name_out, size_t cap);
+
 /* Profile mode brackets every operator of eager passes with events on the model's stream. */
 int s1_model_profile(void* model, int on);
 /* Waits for the stream, then returns and resets: device milliseconds per family since the
@@ -176,6 +194,10 @@ int s1_assign_requests(const int* lengths, int n, int n_ranks, double a, double 
 #define S1_ERR_NONFINITE 3001
 #define S1_ERR_UNKNOWN_TENSOR 3002
 #define S1_ERR_TENSOR_SIZE 3003
+#define S1_ERR_CHECKPOINT_IO 3004      /* a checkpoint file cannot be opened or mapped */
+#define S1_ERR_CHECKPOINT_FORMAT 3005  /* not a safetensors file / index */
+#define S1_ERR_CHECKPOINT_DTYPE 3006   /* a language-model tensor is not bfloat16 (model.rs:291-295) */
+#define S1_ERR_CHECKPOINT_MISSING 3007 /* no embed_tokens.weight, or a tensor of the decoder is absent */
 
 #ifdef __cplusplus
 }

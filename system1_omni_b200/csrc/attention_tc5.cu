@@ -5,10 +5,13 @@
 //   warp 1    one thread issues the MMAs: S = Q K^T (128 x BN, K-major operands) into one of two
 //             score buffers in tensor memory, and O += P V (128 x Dh; V is read MN-major, as it
 //             lies in memory) into the output accumulator, also in tensor memory
-//   warps 2-5 one query row per thread: tcgen05.ld the scores, scale, causal mask, online
-//             softmax in base 2 (row statistics in registers, no shuffles), rescale O in tensor
-//             memory when a row maximum moved, write P (bf16) into shared memory in the
-//             operand layout, and at the end normalise, gate and store the row
+//   warps 2-9 two threads per query row (warps w and w + 4 share the rows of one quarter of
+//             tensor memory, each takes half of the columns): tcgen05.ld the scores, scale,
+//             causal mask, online softmax in base 2 (the two halves exchange only their row
+//             maximum, through shared memory), rescale O in tensor memory when a row maximum
+//             moved, write P (bf16) into shared memory in the operand layout, and at the end
+//             normalise, gate and store. Two warps per scheduler hide the dependent latencies
+//             of the exponentials that one warp per scheduler leaves exposed.
 //
 // The score MMA of tile j + 1 is issued before the P V MMA of tile j, so it runs under tile
 // j's softmax. Same arithmetic contract as the mma.sync kernel in attention.cu (attention.cu:110-233
@@ -33,7 +36,7 @@ namespace s1 {
 namespace {
 
 constexpr int ABM = 128;       // query rows per block
-constexpr int ATHREADS = 192;  // producer warp, MMA warp, four softmax warps
+constexpr int ATHREADS = 320;  // producer warp, MMA warp, eight softmax warps
 
 template <int DH>
 struct ACfg {
@@ -45,7 +48,8 @@ struct ACfg {
     static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;
     static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
     static constexpr int OFF_BAR = OFF_P + P_BYTES;
-    static constexpr int SMEM = OFF_BAR + 256 + 1024;  // 193 KB (Dh 128), 209 KB (Dh 256): one block per SM
+    static constexpr int OFF_X = OFF_BAR + 256;        // float [2][2][128]: row maxima (and sums) of the two halves
+    static constexpr int SMEM = OFF_X + 2048 + 1024;   // 195 KB (Dh 128), 211 KB (Dh 256): one block per SM
     static constexpr int O_COL = 2 * BN;               // tensor memory: two score buffers, then the output
     static constexpr int TMEM_COLS = 512;
 };
@@ -56,8 +60,16 @@ struct AttnMaps {
     CUtensorMap q, k, v, kpre, vpre;
 };
 
-// The four softmax warps: thread (warp & 3) * 32 + lane owns query row q0 + that index, which is
-// also its lane of tensor memory.
+// ex2.approx: the exponentials of the softmax (2 ulp; the row sum and P carry the same value).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// The eight softmax warps. Warp 2 + i and warp 6 + i (i = 0..3) own the 32 query rows of tensor
+// memory lanes [32 ((2 + i) & 3), +32); the first takes the lower half of the score and output
+// columns, the second the upper half.
 template <int DH, bool GATED>
 __device__ __forceinline__ void softmax_rows(unsigned char* smem, uint64_t* bars, uint32_t tmem_base,
                                              volatile int* abort_flag, const bf16* __restrict__ gate,
@@ -66,12 +78,17 @@ __device__ __forceinline__ void softmax_rows(unsigned char* smem, uint64_t* bars
     using namespace tc5;
     using G = ACfg<DH>;
     constexpr int BN = G::BN;
+    constexpr int HN = BN / 2;   // score columns per thread
+    constexpr int HD = DH / 2;   // output columns per thread
     uint64_t *s_full = bars + 9, *s_empty = bars + 11, *p_full = bars + 13, *o_done = bars + 14;
-    const int quarter = warp & 3;
+    float* xchg = reinterpret_cast<float*>(smem + G::OFF_X);  // [2][2][128]
+    const int quarter = warp & 3, hf = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     const int row = q0 + r;
     const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    unsigned char* p_row = smem + G::OFF_P + r * 128;
+    // P: boxes of 64 keys, 128 bytes per row, 16-byte chunks swizzled by the row
+    unsigned char* p_row = smem + G::OFF_P + r * 128 + (BN == 128 ? hf * (ABM * 128) : 0);
+    const int chunk0 = BN == 128 ? 0 : hf * 4;
     const int sw = r & 7;
     auto fail = [&](int code) {
         atomicCAS(&g_attn_error, 0, code);
@@ -79,40 +96,47 @@ __device__ __forceinline__ void softmax_rows(unsigned char* smem, uint64_t* bars
     };
     float m = -INFINITY, l = 0.f;
     bool ok = true;
+    // Every one of the 256 threads runs every iteration and meets the others at the named
+    // barrier, also after a wait has given up (ok = false): nobody is left waiting there.
 #pragma unroll 1
     for (int j = 0; j < ntiles; j++) {
         const int b = j & 1;
-        if (!mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag)) {
+        if (ok && !mbar_wait(&s_full[b], (j >> 1) & 1, abort_flag)) {
             fail(31);
             ok = false;
-            break;
         }
-        fence_after_sync();
-        uint32_t sv[BN];
-#pragma unroll
-        for (int cc = 0; cc < BN / 32; cc++)
-            tmem_ld_32x32(t_row + b * BN + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[cc * 32]));
-        tmem_ld_wait();
-        fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&s_empty[b]);
-
-        const int k0 = j * BN;
+        uint32_t sv[HN];
         float mx = -INFINITY;
-        if (k0 + BN - 1 > row) {
+        if (ok) {
+            fence_after_sync();
 #pragma unroll
-            for (int i = 0; i < BN; i++)
-                if (k0 + i > row) sv[i] = 0xff800000u;  // -inf
+            for (int cc = 0; cc < HN / 32; cc++)
+                tmem_ld_32x32(t_row + b * BN + hf * HN + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[cc * 32]));
+            tmem_ld_wait();
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[b]);
+            const int k0 = j * BN + hf * HN;
+            if (k0 + HN - 1 > row) {
+#pragma unroll
+                for (int i = 0; i < HN; i++)
+                    if (k0 + i > row) sv[i] = 0xff800000u;  // -inf
+            }
+#pragma unroll
+            for (int i = 0; i < HN; i++) mx = fmaxf(mx, __uint_as_float(sv[i]));
         }
-#pragma unroll
-        for (int i = 0; i < BN; i++) mx = fmaxf(mx, __uint_as_float(sv[i]));
+        // the row maximum over both halves; the buffers alternate, so one barrier per tile is enough
+        xchg[(b * 2 + hf) * ABM + r] = mx;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (!ok) continue;
+        mx = fmaxf(mx, xchg[(b * 2 + (hf ^ 1)) * ABM + r]);
         const float mn = fmaxf(m, mx * scale_log2);
-        const float alpha = exp2f(m - mn);
+        const float alpha = fast_exp2(m - mn);
         m = mn;
         float sum = 0.f;
 #pragma unroll
-        for (int i = 0; i < BN; i++) {
-            const float p = exp2f(__uint_as_float(sv[i]) * scale_log2 - mn);
+        for (int i = 0; i < HN; i++) {
+            const float p = fast_exp2(__uint_as_float(sv[i]) * scale_log2 - mn);
             sv[i] = __float_as_uint(p);
             sum += p;
         }
@@ -123,52 +147,53 @@ __device__ __forceinline__ void softmax_rows(unsigned char* smem, uint64_t* bars
             if (!mbar_wait(o_done, (j - 1) & 1, abort_flag)) {
                 fail(32);
                 ok = false;
-                break;
+                continue;
             }
             fence_after_sync();
-            if (__any_sync(0xffffffffu, alpha != 1.f)) {
+            if (__any_sync(__activemask(), alpha != 1.f)) {
 #pragma unroll 1
-                for (int cc = 0; cc < DH / 32; cc++) {
+                for (int cc = 0; cc < HD / 32; cc++) {
                     uint32_t o[32];
-                    tmem_ld_32x32(t_row + G::O_COL + cc * 32, o);
+                    tmem_ld_32x32(t_row + G::O_COL + hf * HD + cc * 32, o);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tmem_st_32x32(t_row + G::O_COL + cc * 32, o);
+                    tmem_st_32x32(t_row + G::O_COL + hf * HD + cc * 32, o);
                 }
                 tmem_st_wait();
             }
         }
 #pragma unroll
-        for (int c = 0; c < BN / 64; c++) {
-#pragma unroll
-            for (int ch = 0; ch < 8; ch++) {
-                const uint32_t* v = &sv[c * 64 + ch * 8];
-                uint4 w;
-                w.x = pack2(__uint_as_float(v[0]), __uint_as_float(v[1]));
-                w.y = pack2(__uint_as_float(v[2]), __uint_as_float(v[3]));
-                w.z = pack2(__uint_as_float(v[4]), __uint_as_float(v[5]));
-                w.w = pack2(__uint_as_float(v[6]), __uint_as_float(v[7]));
-                *reinterpret_cast<uint4*>(p_row + c * (ABM * 128) + ((ch ^ sw) * 16)) = w;
-            }
+        for (int ch = 0; ch < HN / 8; ch++) {
+            const uint32_t* v = &sv[ch * 8];
+            uint4 w;
+            w.x = pack2(__uint_as_float(v[0]), __uint_as_float(v[1]));
+            w.y = pack2(__uint_as_float(v[2]), __uint_as_float(v[3]));
+            w.z = pack2(__uint_as_float(v[4]), __uint_as_float(v[5]));
+            w.w = pack2(__uint_as_float(v[6]), __uint_as_float(v[7]));
+            *reinterpret_cast<uint4*>(p_row + (((chunk0 + ch) ^ sw) * 16)) = w;
         }
         fence_proxy_async();
         fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(p_full);
     }
+    // The row sum is the lower half's plus the upper half's, in that order for both threads. Every
+    // thread comes here, also after a failed wait (the barrier counts all 256).
+    xchg[hf * ABM + r] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
     if (!ok || ntiles == 0) return;
     if (!mbar_wait(o_done, (ntiles - 1) & 1, abort_flag)) {
         fail(33);
         return;
     }
     fence_after_sync();
-    const float inv = 1.f / l;
-    const size_t base = ((size_t)(row - own_base) * Hq + h) * DH;
+    const float inv = 1.f / (xchg[r] + xchg[ABM + r]);
+    const size_t base = ((size_t)(row - own_base) * Hq + h) * DH + hf * HD;
 #pragma unroll 1
-    for (int cc = 0; cc < DH / 32; cc++) {
+    for (int cc = 0; cc < HD / 32; cc++) {
         uint32_t o[32];
-        tmem_ld_32x32(t_row + G::O_COL + cc * 32, o);
+        tmem_ld_32x32(t_row + G::O_COL + hf * HD + cc * 32, o);
         tmem_ld_wait();
         if (row >= T) continue;
         float y[32];
@@ -238,9 +263,9 @@ __global__ void __launch_bounds__(ATHREADS, 1)
             mbar_init(&k_empty[i], 1);
             mbar_init(&v_empty[i], 1);
             mbar_init(&s_full[i], 1);
-            mbar_init(&s_empty[i], 4);
+            mbar_init(&s_empty[i], 8);
         }
-        mbar_init(p_full, 4);
+        mbar_init(p_full, 8);
         mbar_init(o_done, 1);
         *abort_flag = 0;
         mbar_init_fence();

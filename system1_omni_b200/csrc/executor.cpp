@@ -687,6 +687,21 @@ int s1_model_tensor(void* model, const char* name, void** device_ptr, size_t* by
     return 0;
 }
 
+int s1_model_unfilled(void* model, char* name_out, size_t cap) {
+    Model* m = static_cast<Model*>(model);
+    if (!m) return -1;
+    int n = 0;
+    for (const auto& entry : m->order) {
+        if (m->named[entry.first].filled) continue;
+        if (n++ == 0 && name_out && cap) {
+            const size_t len = std::min(cap - 1, entry.first.size());
+            memcpy(name_out, entry.first.data(), len);
+            name_out[len] = 0;
+        }
+    }
+    return n;
+}
+
 int s1_model_init_random(void* model, uint64_t seed, float std) {
     Model* m = static_cast<Model*>(model);
     if (!m) return S1_ERR_ARGUMENT;

@@ -92,6 +92,10 @@ SIGNATURES = {
     "s1_gemm_tc5_status": (i32, [ip]),
     "s1_gemm_unsplit": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "s1_attn_tc5_status": (i32, [ip]),
+    "s1_checkpoint_inspect": (i32, [C.c_char_p, C.c_char_p, C.c_size_t, ip, i32, C.c_char_p, C.c_size_t, C.c_char_p,
+                                    C.c_size_t, ip, vp, vp]),
+    "s1_model_load_checkpoint": (i32, [vp, C.c_char_p, C.c_char_p, C.c_size_t]),
+    "s1_model_unfilled": (i32, [vp, C.c_char_p, C.c_size_t]),
     "s1_gemm_swiglu": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "s1_model_set_exact_packing": (i32, [vp, i32]),
     "s1_model_set_fused_mlp": (i32, [vp, i32]),

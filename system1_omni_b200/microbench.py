@@ -293,6 +293,48 @@ def prefix(b, out):
     model.close()
 
 
+def requests(b, out):
+    """One GPU's share of the ragged request set on a 27B-shaped decoder (hidden 5120, 64 layers
+    3:1, 16 qk / 48 v GDN heads, 24 q / 4 kv attention heads of 128, MLP 17408; 47 GB of bf16
+    weights): 64 requests with lengths log-uniform on [512, 16384] (seed 0), assigned to 8 ranks
+    longest-first on cost T + T^2 / 65536, rank 0's share run here pack by pack. Every rank holds
+    a full replica and talks to nobody during the pass, so this is what each of 8 GPUs does."""
+    import time
+    from . import model as M
+    types = [("full_attention" if (i + 1) % 4 == 0 else "linear_attention") for i in range(64)]
+    cfg = M.Config(hidden=5120, intermediate=17408, layer_types=types, heads=24, kv_heads=4, head_dim=128,
+                   rotary_half=32, lin_k_heads=16, lin_v_heads=48, vocab=151936, eps=1e-6, rope_theta=1e7,
+                   max_positions=262144)
+    rng = np.random.default_rng(0)
+    lengths = np.exp(rng.uniform(np.log(512), np.log(16384), 64)).astype(np.int64)
+    rank_of = M.assign_requests(lengths, 8, 1.0, 1.0 / 65536)
+    cost = lengths + lengths.astype(np.float64) ** 2 / 65536
+    shares = [float(cost[rank_of == r].sum()) for r in range(8)]
+    tokens_by_rank = [int(lengths[rank_of == r].sum()) for r in range(8)]
+    mine = [int(n) for n in lengths[rank_of == 0]]
+    model = M.Model(cfg, device=0)
+    model.init_random(seed=0, std=0.02)
+    prompts = [rng.integers(0, cfg.vocab, n).tolist() for n in mine]
+    packs = M.ranges(mine)
+
+    def run():
+        return [model.forward_batch([prompts[i] for i in pack]) for pack in packs]
+
+    run()
+    model.synchronize()
+    t0 = time.perf_counter()
+    last = run()
+    model.synchronize()
+    sec = time.perf_counter() - t0
+    out({"op": "ragged_requests_share", "model": "27B-shaped", "requests_total": 64, "tokens_total": int(lengths.sum()),
+         "rank0_requests": mine, "rank0_tokens": int(sum(mine)), "packs": len(packs), "seconds": sec,
+         "tokens_per_s_this_gpu": sum(mine) / sec, "tokens_by_rank": tokens_by_rank,
+         "cost_imbalance_max_over_mean": max(shares) / (sum(shares) / 8),
+         "finite": bool(all(np.all(np.isfinite(x)) for x in last)), "weights_GB": model.weight_bytes / 1e9,
+         "timing": "host wall clock around the public calls, second pass"})
+    model.close()
+
+
 def attention(b, out):
     lib, st = b.lib, b.stream.handle
     for dh, hq, hk in [(128, 16, 4), (128, 24, 4), (256, 16, 4), (256, 24, 4)]:
@@ -309,7 +351,7 @@ def attention(b, out):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", default="all", choices=["elementwise", "gemm", "gdn", "layer", "attention", "prefix", "all"])
+    ap.add_argument("--what", default="all", choices=["elementwise", "gemm", "gdn", "layer", "attention", "prefix", "requests", "all"])
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--out", default=None)
@@ -335,6 +377,8 @@ def main():
             fn(b, out)
     if args.what == "prefix":  # builds a 9B-shaped model (14 GB of weights): only on request
         prefix(b, out)
+    if args.what == "requests":  # builds a 27B-shaped model (47 GB of weights): only on request
+        requests(b, out)
     if sink:
         sink.close()
 

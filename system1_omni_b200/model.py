@@ -188,6 +188,17 @@ class Model:
     def weight_bytes(self):
         return L.load().s1_model_weight_bytes(self.handle)
 
+    @classmethod
+    def from_checkpoint(cls, directory, device=0):
+        """Model::load (model.rs:622-705): config.json + safetensors files of a checkpoint directory."""
+        model = cls(Config.load(directory), device=device)
+        offender = C.create_string_buffer(256)
+        code = L.load().s1_model_load_checkpoint(model.handle, os.fsencode(directory), offender, 256)
+        if code != 0:
+            model.close()
+            raise L.CudaError(code, f"load checkpoint ({offender.value.decode() or directory})")
+        return model
+
     def init_random(self, seed=0, std=0.02):
         L.check(L.load().s1_model_init_random(self.handle, seed, std), "init random")
 
