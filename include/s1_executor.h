@@ -44,6 +44,9 @@ int s1_attention_gated_shared_prefix(const void* q, const void* k, const void* v
  * wait ever gave up), read after waiting for all queued work, then cleared. */
 int s1_attn_tc5_status(int* code);
 
+/* The same for the delta-rule kernels (a bounded wait for a TMA or bulk copy gave up). */
+int s1_gdn_status(int* code);
+
 /* ---- GEMM engines behind cs1_gemm, pinned (benchmark arms and parity tests) ---- */
 int s1_gemm_cublaslt(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream);
 /* cs1_gemm with the K-split path switched off for this call. */

@@ -13,16 +13,25 @@
 //             v_new = u - w S, o = qd S + P v_new (written straight to the output) and
 //             S = decay S + kd^T v_new. Neither S nor v_new ever goes to global memory.
 //
+// Data movement is by the copy engine: gdn_prep takes its v and k rows as two TMA tiles, and
+// leaves every workspace tile in the padded row layout its consumer wants in shared memory, so
+// gdn_scan fetches a chunk's five tiles with five bulk copies issued by one thread (per-thread
+// 16-byte asynchronous copies held up every later shared-memory access of the block).
+//
 // Arithmetic and rounding points are those of the reference implementation
 // (src/backends/cuda/qwen3_5/gdn_prefill.cu:110-544): float32 cumsum, norms, pair products
 // (TF32 operands), inverse and state; bf16 qd, kd, P, T*beta, k*exp(cum), u, w, v_new and
 // the chunk-entry state. The state is float32 across calls (s_in / s_out), so a window that
 // starts on a multiple of 64 tokens continues a previous one bit for bit.
+#include <cuda.h>
+
 #include <mutex>
 
 #include "common.cuh"
 #include "cs1_ops.h"
 #include "mma.cuh"
+#include "tc5.cuh"
+#include "tmap.h"
 
 namespace s1 {
 namespace {
@@ -34,30 +43,38 @@ constexpr int LDA = C + 4;   // float row stride of A
 constexpr int LDH = D + 8;   // bf16 row stride of [64][128] tiles
 constexpr int LDT = C + 8;   // bf16 row stride of [64][64] tiles
 
+// Width of the value-column slice one scan block owns: narrow slices when there are few heads,
+// so that the scan still covers the SMs.
+inline int slice_width(int H) { return H * (D / 32) >= 96 ? 32 : 16; }
+
+// Workspace: per (head, chunk) tiles in the padded row layouts of the scan's shared memory, each
+// tile contiguous so that one bulk copy brings it in.
 struct Work {
-    bf16* u;       // [H, NCC, 128]
-    bf16* w;       // [H, NCC, 128]
-    bf16* qd;      // [H, NCC, 128]
-    bf16* kd;      // [H, NCC, 128]
-    bf16* p;       // [H, NC, 64, 64]
+    bf16* u;       // [H, NC, 128 / VS, 64, VS + 8]  one tile per slice of value columns
+    bf16* w;       // [H, NC, 64, LDH]
+    bf16* qd;      // [H, NC, 64, LDH]
+    bf16* kd;      // [H, NC, 64, LDH]
+    bf16* p;       // [H, NC, 64, LDT]
     float* decay;  // [H, NC]
+    int vs;        // VS
 };
 
 struct Layout {
     size_t u, w, qd, kd, p, decay, total;
     Layout(int T, int H) {
-        const size_t NC = ((size_t)T + C - 1) / C, NCC = NC * C;
+        const size_t NC = ((size_t)T + C - 1) / C;
+        const size_t vs = (size_t)slice_width(H);
         size_t at = 0;
         auto take = [&](size_t bytes) {
             const size_t off = at;
             at = (at + bytes + 255) / 256 * 256;
             return off;
         };
-        u = take((size_t)H * NCC * D * 2);
-        w = take((size_t)H * NCC * D * 2);
-        qd = take((size_t)H * NCC * D * 2);
-        kd = take((size_t)H * NCC * D * 2);
-        p = take((size_t)H * NC * C * C * 2);
+        u = take((size_t)H * NC * (D / vs) * C * (vs + 8) * 2);
+        w = take((size_t)H * NC * C * LDH * 2);
+        qd = take((size_t)H * NC * C * LDH * 2);
+        kd = take((size_t)H * NC * C * LDH * 2);
+        p = take((size_t)H * NC * C * LDT * 2);
         decay = take((size_t)H * NC * 4);
         total = at;
     }
@@ -73,8 +90,11 @@ Work split(float* workspace, int T, int H) {
     ws.kd = reinterpret_cast<bf16*>(b + l.kd);
     ws.p = reinterpret_cast<bf16*>(b + l.p);
     ws.decay = reinterpret_cast<float*>(b + l.decay);
+    ws.vs = slice_width(H);
     return ws;
 }
+
+__device__ int g_gdn_error = 0;  // a bounded wait for a copy gave up (read with s1_gdn_status)
 
 // ---------------------------------------------------------------------------------------
 // gdn_prep
@@ -86,17 +106,22 @@ constexpr int P_QF = P_KF + C * LDF * 4;         // float [64][LDF]  q normalize
 constexpr int P_A = P_QF + C * LDF * 4;          // float [64][LDA]  A
 constexpr int P_TB = P_A + C * LDA * 4;          // bf16  [64][LDT]  T * beta
 constexpr int P_SM = P_TB + C * LDT * 2;         // float [6][64]    g/cum, beta, ecum, erem, kinv, spare
-constexpr int PREP_SMEM = P_SM + 6 * C * 4;
+constexpr int LDX = 36;                          // float row stride of the 32 x 32 temporary of the inverse
+constexpr int P_X = P_SM + 6 * C * 4;            // float [32][LDX]
+constexpr int PREP_SMEM = P_X + 32 * LDX * 4;
 // after the pair products the operand tiles are dead: v and k*exp(cum) reuse them
 constexpr int P_VS = P_KF;                       // bf16 [64][LDH]
+constexpr int P_VR = P_KF + C * LDH * 2;         // bf16 [64][128] raw v rows as the TMA tile leaves them
 constexpr int P_KE = P_QF + C * D * 2;           // bf16 [64][LDH], after the unpadded raw k rows
-static_assert(C * LDH * 2 <= C * LDF * 4, "bf16 tile fits over a float tile");
+static_assert(C * LDH * 2 + C * D * 2 <= C * LDF * 4, "padded and raw v tiles fit over the k operand tile");
+static_assert(P_VR % 128 == 0 && P_QF % 128 == 0, "TMA destinations are 128-byte aligned");
 static_assert(C * D * 2 + C * LDH * 2 <= C * LDF * 4, "raw k rows and k*exp(cum) fit over the q tile");
 
 __global__ void __launch_bounds__(PREP_THREADS, 2)
-    gdn_prep(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
-             const float* __restrict__ g, const bf16* __restrict__ beta, Work ws, int T, int H, int HK, float scale) {
-    extern __shared__ __align__(16) unsigned char smem[];
+    gdn_prep(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+             const bf16* __restrict__ q, const bf16* __restrict__ k, const float* __restrict__ g,
+             const bf16* __restrict__ beta, Work ws, int T, int H, int HK, float scale) {
+    extern __shared__ __align__(128) unsigned char smem[];
     float* kf = reinterpret_cast<float*>(smem + P_KF);
     float* qf = reinterpret_cast<float*>(smem + P_QF);
     float* A = reinterpret_cast<float*>(smem + P_A);
@@ -106,13 +131,19 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
     float* ecum = bt + C;
     float* erem = ecum + C;
     float* kinv = erem + C;
+    uint64_t* tile_bar = reinterpret_cast<uint64_t*>(kinv + C);  // the spare row of the scalar block
     bf16* vs = reinterpret_cast<bf16*>(smem + P_VS);
     bf16* ke = reinterpret_cast<bf16*>(smem + P_KE);
 
     const int c = blockIdx.x, h = blockIdx.y, hk = h / (H / HK);
-    const int NC = gridDim.x, NCC = NC * C;
+    const int NC = gridDim.x;
     const int r0 = c * C, n = min(C, T - r0);
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    if (tid == 0) {
+        tc5::mbar_init(tile_bar, 1);
+        tc5::mbar_init_fence();
+    }
+    const size_t tile = (size_t)h * NC + c;  // this block's (head, chunk) tile in every workspace array
 
     // The q and k rows of the norm phase are requested first of all, so that their latency
     // hides behind the decay phase.
@@ -166,8 +197,8 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
         // 16 lanes per row, 16 rows per pass; a lane owns dims [4 sub, 4 sub + 4) and
         // [64 + 4 sub, 64 + 4 sub + 4), so that the float4 stores of a quarter warp fall in one
         // contiguous 128-byte run of shared memory. All 16 loads are requested up front.
-        bf16* qd_out = ws.qd + ((size_t)h * NCC + r0) * D;
-        bf16* kd_out = ws.kd + ((size_t)h * NCC + r0) * D;
+        bf16* qd_out = ws.qd + tile * (C * LDH);
+        bf16* kd_out = ws.kd + tile * (C * LDH);
 #pragma unroll
         for (int pass = 0; pass < 8; pass++) {
             const bool is_k = pass < 4;
@@ -192,7 +223,7 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
             }
             const float mult = is_k ? erem[i] : ecum[i];
             float* tile = (is_k ? kf : qf) + i * LDF;
-            bf16* dout = (is_k ? kd_out : qd_out) + (size_t)i * D;
+            bf16* dout = (is_k ? kd_out : qd_out) + i * LDH;
 #pragma unroll
             for (int half = 0; half < 2; half++) {
                 float4 t;
@@ -238,7 +269,7 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
                 }
             }
         }
-        bf16* p_out = ws.p + ((size_t)h * NC + c) * C * C;
+        bf16* p_out = ws.p + tile * (C * LDT);
 #pragma unroll
         for (int nt = 0; nt < 8; nt++) {
 #pragma unroll
@@ -261,54 +292,111 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
                     A[i * LDA + j] = v0;
                     A[i * LDA + j + 1] = v1;
                 } else {
-                    *reinterpret_cast<uint32_t*>(p_out + i * C + j) = pack2(v0, v1);
+                    *reinterpret_cast<uint32_t*>(p_out + i * LDT + j) = pack2(v0, v1);
                 }
             }
         }
     }
     __syncthreads();
 
-    // ---- v and the raw k rows come in by asynchronous copies over the dead operand tiles
-    //      (every thread requests four 16-byte pieces of each and later converts only the k
-    //      pieces it requested itself, so no barrier is needed in between) ----
+    // ---- v and the raw k rows come in as two TMA tiles over the dead operand tiles (rows past the
+    //      end of the sequence read as zero) ----
     bf16* kraw = reinterpret_cast<bf16*>(smem + P_QF);  // [64][128], no padding
-#pragma unroll
-    for (int piece = 0; piece < 4; piece++) {
-        const int cidx = tid + piece * PREP_THREADS;
-        const int i = cidx / (D / 8), d0 = (cidx % (D / 8)) * 8;
-        const int row = r0 + min(i, n - 1);
-        cp_async16(vs + i * LDH + d0, v + ((size_t)row * H + h) * D + d0, i < n);
-        cp_async16(kraw + i * D + d0, k + ((size_t)row * HK + hk) * D + d0, i < n);
+    bf16* vraw = reinterpret_cast<bf16*>(smem + P_VR);  // [64][128], no padding
+    if (tid == 0) {
+        tc5::mbar_expect_tx(tile_bar, 2 * C * D * 2);
+        tc5::tma_load_2d(kraw, &map_k, hk * D, r0, tile_bar);
+        tc5::tma_load_2d(vraw, &map_v, h * D, r0, tile_bar);
     }
-    cp_async_commit();
 
-    // ---- warps 0-1: T = (I + A)^-1 by forward substitution, one column per thread held in
-    //      registers, while the copies land ----
-    if (warp < 2) {
-        const int j = tid;
-        float col[C];
+    // ---- T = (I + A)^-1 (unit lower triangular, float32), in place over A, while the copies land:
+    //      the four 16 x 16 diagonal blocks by forward substitution (one column per thread), then the
+    //      blocks below them from T21 = -T22 (A21 T11), first 16 -> 32, then 32 -> 64, as plain
+    //      float32 products spread over all 256 threads. A is zero on and above its diagonal. ----
+    {
+        float* X = reinterpret_cast<float*>(smem + P_X);  // [32][LDX]
+        float col[16];
+        if (tid < 64) {
+            const float* blk = A + (16 * (tid >> 4)) * (LDA + 1);
+            const int j = tid & 15;
 #pragma unroll
-        for (int i = 0; i < C; i++) {
-            // four independent partial sums (m mod 4) keep the dependent chain a quarter as long
-            float a0 = i == j ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-            const float* arow = A + i * LDA;
+            for (int i = 0; i < 16; i++) {
+                float acc = i == j ? 1.f : 0.f;
 #pragma unroll
-            for (int m4 = 0; m4 < (i + 3) / 4; m4++) {
-                const float4 a4 = *reinterpret_cast<const float4*>(arow + m4 * 4);
-                if (m4 * 4 + 0 < i) a0 -= a4.x * col[m4 * 4 + 0];
-                if (m4 * 4 + 1 < i) a1 -= a4.y * col[m4 * 4 + 1];
-                if (m4 * 4 + 2 < i) a2 -= a4.z * col[m4 * 4 + 2];
-                if (m4 * 4 + 3 < i) a3 -= a4.w * col[m4 * 4 + 3];
+                for (int m = 0; m < i; m++) acc -= blk[i * LDA + m] * col[m];  // col[m] is 0 above the diagonal
+                col[i] = acc;
             }
-            col[i] = (a0 + a1) + (a2 + a3);
         }
-        const float bj = bt[j];
+        __syncthreads();  // every column of a block is computed before any is written over A
+        if (tid < 64) {
+            float* blk = A + (16 * (tid >> 4)) * (LDA + 1);
+            const int j = tid & 15;
 #pragma unroll
-        for (int i = 0; i < C; i++) Tb[i * LDT + j] = to_bf16(col[i] * bj);
+            for (int i = 0; i < 16; i++) blk[i * LDA + j] = col[i];
+        }
+        __syncthreads();
+        {   // 16 -> 32: two independent pairs of diagonal blocks; 2 x 256 outputs, two per thread
+            const int p = tid >> 7, idx = tid & 127, i = idx >> 3, j0 = (idx & 7) * 2;
+            float* t11 = A + (32 * p) * (LDA + 1);
+            float* a21 = t11 + 16 * LDA;
+            const float* t22 = a21 + 16;
+            float x0 = 0.f, x1 = 0.f;
+#pragma unroll
+            for (int m = 0; m < 16; m++) {
+                const float a = a21[i * LDA + m];
+                const float2 t = *reinterpret_cast<const float2*>(t11 + m * LDA + j0);
+                x0 += a * t.x;
+                x1 += a * t.y;
+            }
+            *reinterpret_cast<float2*>(X + (16 * p + i) * LDX + j0) = make_float2(x0, x1);
+            __syncthreads();
+            float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+            for (int m = 0; m < 16; m++) {
+                const float a = t22[i * LDA + m];
+                const float2 t = *reinterpret_cast<const float2*>(X + (16 * p + m) * LDX + j0);
+                y0 -= a * t.x;
+                y1 -= a * t.y;
+            }
+            *reinterpret_cast<float2*>(a21 + i * LDA + j0) = make_float2(y0, y1);
+            __syncthreads();
+        }
+        {   // 32 -> 64: 32 x 32 outputs, four per thread
+            const int i = tid >> 3, j0 = (tid & 7) * 4;
+            float* a21 = A + 32 * LDA;
+            const float* t22 = a21 + 32;
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+            for (int m = 0; m < 32; m++) {
+                const float a = a21[i * LDA + m];
+                const float4 t = *reinterpret_cast<const float4*>(A + m * LDA + j0);
+                x.x += a * t.x, x.y += a * t.y, x.z += a * t.z, x.w += a * t.w;
+            }
+            *reinterpret_cast<float4*>(X + i * LDX + j0) = x;
+            __syncthreads();
+            float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+            for (int m = 0; m < 32; m++) {
+                const float a = t22[i * LDA + m];
+                const float4 t = *reinterpret_cast<const float4*>(X + m * LDX + j0);
+                y.x -= a * t.x, y.y -= a * t.y, y.z -= a * t.z, y.w -= a * t.w;
+            }
+            *reinterpret_cast<float4*>(a21 + i * LDA + j0) = y;
+            __syncthreads();
+        }
+        // T beta as the bf16 operand of the two products below
+#pragma unroll
+        for (int e = 0; e < C * C / PREP_THREADS; e++) {
+            const int idx = tid + e * PREP_THREADS, i = idx >> 6, j = idx & 63;
+            Tb[i * LDT + j] = to_bf16(A[i * LDA + j] * bt[j]);
+        }
     }
-    cp_async_wait<0>();
+    {
+        volatile int never = 0;
+        if (!tc5::mbar_wait(tile_bar, 0, &never)) atomicCAS(&g_gdn_error, 0, 41);  // carries on with what is there
+    }
 #pragma unroll
-    for (int piece = 0; piece < 4; piece++) {  // k * exp(cum) in bf16 from this thread's own pieces
+    for (int piece = 0; piece < 4; piece++) {  // k * exp(cum) in bf16, and v into its padded tile
         const int cidx = tid + piece * PREP_THREADS;
         const int i = cidx / (D / 8), d0 = (cidx % (D / 8)) * 8;
         float x[8], y[8];
@@ -317,6 +405,7 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
 #pragma unroll
         for (int e = 0; e < 8; e++) y[e] = (x[e] * inv) * ec;
         st16(ke + i * LDH + d0, pack8(y));
+        st16(vs + i * LDH + d0, ld16(vraw + i * D + d0));
     }
     __syncthreads();
 
@@ -340,13 +429,17 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
                 mma_bf16(acc[2 * np + 1], a, b[2], b[3]);
             }
         }
-        bf16* dst = (is_u ? ws.u : ws.w) + ((size_t)h * NCC + r0) * D;
+        // w: one [64][LDH] tile; u: one [64][VS + 8] tile per slice of VS value columns
+        const int vs_w = ws.vs, ldu = vs_w + 8;
+        bf16* dst = is_u ? ws.u + tile * (size_t)(D / vs_w) * (C * ldu) : ws.w + tile * (C * LDH);
         const int gq = lane / 4, tq = lane % 4;
 #pragma unroll
         for (int nt = 0; nt < 16; nt++) {
             const int col = nt * 8 + 2 * tq;
-            *reinterpret_cast<uint32_t*>(dst + (size_t)(mt * 16 + gq) * D + col) = pack2(acc[nt][0], acc[nt][1]);
-            *reinterpret_cast<uint32_t*>(dst + (size_t)(mt * 16 + gq + 8) * D + col) = pack2(acc[nt][2], acc[nt][3]);
+            bf16* at = is_u ? dst + (col / vs_w) * (C * ldu) + (col % vs_w) : dst + col;
+            const int ld = is_u ? ldu : LDH;
+            *reinterpret_cast<uint32_t*>(at + (mt * 16 + gq) * ld) = pack2(acc[nt][0], acc[nt][1]);
+            *reinterpret_cast<uint32_t*>(at + (mt * 16 + gq + 8) * ld) = pack2(acc[nt][2], acc[nt][3]);
         }
     }
 }
@@ -365,7 +458,8 @@ struct ScanSmem {
     static constexpr int P = KD + C * LDH * 2;                 // [64][LDT]
     static constexpr int SB = P + C * LDT * 2;                 // [128][LDV]
     static constexpr int VN = SB + D * LDV * 2;                // [64][LDV]
-    static constexpr int BYTES = VN + C * LDV * 2;
+    static constexpr int BAR = VN + C * LDV * 2;               // three mbarriers and a flag
+    static constexpr int BYTES = BAR + 32;
 };
 
 // WARPS is 4 or 8. The 64 chunk rows split into four 16-row tiles (rt); with 8 warps the
@@ -382,7 +476,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2)
     constexpr int MT = 8 / WARPS;            // 16-row tiles of the state per warp
     constexpr int NTL = NT / (WARPS / 4);    // column tiles per warp in the row products
     static_assert(NTL >= 2 && NTL % 2 == 0, "column tiles are loaded in pairs");
-    extern __shared__ __align__(16) unsigned char smem[];
+    extern __shared__ __align__(128) unsigned char smem[];
     bf16* Wb = reinterpret_cast<bf16*>(smem + L::W);
     bf16* Ub = reinterpret_cast<bf16*>(smem + L::U);
     bf16* QDb = reinterpret_cast<bf16*>(smem + L::QD);
@@ -390,53 +484,58 @@ __global__ void __launch_bounds__(WARPS * 32, 2)
     bf16* Pb = reinterpret_cast<bf16*>(smem + L::P);
     bf16* Sb = reinterpret_cast<bf16*>(smem + L::SB);
     bf16* VNb = reinterpret_cast<bf16*>(smem + L::VN);
+    uint64_t* wu_bar = reinterpret_cast<uint64_t*>(smem + L::BAR);  // [2], one per buffer of w and u
+    uint64_t* qpk_bar = wu_bar + 2;
+    volatile int* gave_up = reinterpret_cast<volatile int*>(qpk_bar + 1);
 
     const int h = blockIdx.x, v0 = blockIdx.y * VS;
-    const int NCC = NC * C;
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const int gq = lane / 4, tq = lane % 4;
     const int rt = warp & 3, cb = (warp >> 2) * NTL * 8;
 
-    const bf16* w_g = ws.w + (size_t)h * NCC * D;
-    const bf16* u_g = ws.u + (size_t)h * NCC * D + v0;
-    const bf16* qd_g = ws.qd + (size_t)h * NCC * D;
-    const bf16* kd_g = ws.kd + (size_t)h * NCC * D;
-    const bf16* p_g = ws.p + (size_t)h * NC * C * C;
+    // this head's tiles; every tile is contiguous and already in the shared-memory row layout
+    constexpr uint32_t W_BYTES = C * LDH * 2, U_BYTES = C * LDV * 2, P_BYTES = C * LDT * 2;
+    const bf16* w_g = ws.w + (size_t)h * NC * (C * LDH);
+    const bf16* u_g = ws.u + ((size_t)h * NC * (D / VS) + blockIdx.y) * (C * LDV);
+    const bf16* qd_g = ws.qd + (size_t)h * NC * (C * LDH);
+    const bf16* kd_g = ws.kd + (size_t)h * NC * (C * LDH);
+    const bf16* p_g = ws.p + (size_t)h * NC * (C * LDT);
     const float* decay_g = ws.decay + (size_t)h * NC;
 
+    if (tid == 0) {
+        tc5::mbar_init(&wu_bar[0], 1);
+        tc5::mbar_init(&wu_bar[1], 1);
+        tc5::mbar_init(qpk_bar, 1);
+        *gave_up = 0;
+        tc5::mbar_init_fence();
+    }
+    __syncthreads();
+    // Issued by one thread: two bulk copies (w, u) into buffer c & 1, three (qd, kd, P) into the
+    // single buffer of the second half of a chunk step.
     auto load_wu = [&](int c) {
-        bf16* wd = Wb + (c & 1) * C * LDH;
-        bf16* ud = Ub + (c & 1) * C * LDV;
-        const bf16* wsrc = w_g + (size_t)c * C * D;
-        const bf16* usrc = u_g + (size_t)c * C * D;
-        for (int i = tid; i < C * (D / 8); i += THREADS) {
-            const int r = i / (D / 8), col = (i % (D / 8)) * 8;
-            cp_async16(wd + r * LDH + col, wsrc + (size_t)r * D + col);
-        }
-        for (int i = tid; i < C * (VS / 8); i += THREADS) {
-            const int r = i / (VS / 8), col = (i % (VS / 8)) * 8;
-            cp_async16(ud + r * LDV + col, usrc + (size_t)r * D + col);
-        }
+        uint64_t* bar = &wu_bar[c & 1];
+        tc5::mbar_expect_tx(bar, W_BYTES + U_BYTES);
+        tc5::bulk_load(Wb + (c & 1) * C * LDH, w_g + (size_t)c * (C * LDH), W_BYTES, bar);
+        tc5::bulk_load(Ub + (c & 1) * C * LDV, u_g + (size_t)c * (D / VS) * (C * LDV), U_BYTES, bar);
     };
     auto load_qpk = [&](int c) {
-        const bf16* qsrc = qd_g + (size_t)c * C * D;
-        const bf16* ksrc = kd_g + (size_t)c * C * D;
-        const bf16* psrc = p_g + (size_t)c * C * C;
-        for (int i = tid; i < C * (D / 8); i += THREADS) {
-            const int r = i / (D / 8), col = (i % (D / 8)) * 8;
-            cp_async16(QDb + r * LDH + col, qsrc + (size_t)r * D + col);
-            cp_async16(KDb + r * LDH + col, ksrc + (size_t)r * D + col);
-        }
-        for (int i = tid; i < C * (C / 8); i += THREADS) {
-            const int r = i / (C / 8), col = (i % (C / 8)) * 8;
-            cp_async16(Pb + r * LDT + col, psrc + (size_t)r * C + col);
+        tc5::mbar_expect_tx(qpk_bar, 2 * W_BYTES + P_BYTES);
+        tc5::bulk_load(QDb, qd_g + (size_t)c * (C * LDH), W_BYTES, qpk_bar);
+        tc5::bulk_load(KDb, kd_g + (size_t)c * (C * LDH), W_BYTES, qpk_bar);
+        tc5::bulk_load(Pb, p_g + (size_t)c * (C * LDT), P_BYTES, qpk_bar);
+    };
+    // A wait that runs out records it and lets the block finish its steps (on whatever is there).
+    auto wait_for = [&](uint64_t* bar, uint32_t parity) {
+        if (!tc5::mbar_wait(bar, parity, gave_up)) {
+            atomicCAS(&g_gdn_error, 0, 42);
+            *gave_up = 1;
         }
     };
 
-    load_wu(0);
-    cp_async_commit();
-    load_qpk(0);
-    cp_async_commit();
+    if (tid == 0) {
+        load_wu(0);
+        load_qpk(0);
+    }
 
     // state rows [32 warp, 32 warp + 32) x VS columns, float32, in mma accumulator layout
     float S[MT][NT][4];
@@ -461,10 +560,9 @@ __global__ void __launch_bounds__(WARPS * 32, 2)
                 *reinterpret_cast<uint32_t*>(Sb + kr * LDV + vc) = pack2(S[mt][nt][0], S[mt][nt][1]);
                 *reinterpret_cast<uint32_t*>(Sb + (kr + 8) * LDV + vc) = pack2(S[mt][nt][2], S[mt][nt][3]);
             }
-        cp_async_wait<1>();  // w, u of this chunk have landed
-        __syncthreads();
-        if (c + 1 < NC) load_wu(c + 1);
-        cp_async_commit();
+        wait_for(&wu_bar[c & 1], (c >> 1) & 1);  // w, u of this chunk have landed
+        __syncthreads();                          // and nobody still reads the other buffer
+        if (tid == 0 && c + 1 < NC) load_wu(c + 1);
 
         const bf16* Wc = Wb + (c & 1) * C * LDH;
         const bf16* Uc = Ub + (c & 1) * C * LDV;
@@ -498,7 +596,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2)
                     pack2(__uint_as_float(u1 << 16) - acc[nt][2], __uint_as_float(u1 & 0xffff0000u) - acc[nt][3]);
             }
         }
-        cp_async_wait<1>();  // qd, kd, P of this chunk have landed
+        wait_for(qpk_bar, c & 1);  // qd, kd, P of this chunk have landed
         __syncthreads();
 
         // (3) o = qd S + P v_new
@@ -566,10 +664,8 @@ __global__ void __launch_bounds__(WARPS * 32, 2)
             }
         }
         __syncthreads();  // all reads of this chunk's tiles are done
-        if (c + 1 < NC) load_qpk(c + 1);
-        cp_async_commit();
+        if (tid == 0 && c + 1 < NC) load_qpk(c + 1);
     }
-    cp_async_wait<0>();
 
     if (s_out) {
 #pragma unroll
@@ -618,13 +714,17 @@ int gdn_run(const void* q, const void* k, const void* v, const float* g, const v
     if (e != cudaSuccess) return e;
     const int NC = (T + C - 1) / C;
     const Work ws = split(workspace, T, H);
-    gdn_prep<<<dim3(NC, H), PREP_THREADS, PREP_SMEM, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(k),
-                                                          static_cast<const bf16*>(v), g,
+    // v and k rows of a chunk as [64 rows, 128 columns] tiles of the caller's [T, heads, 128] arrays
+    CUtensorMap map_k, map_v;
+    if (!tensor_map_2d_plain(k, (uint64_t)T, (uint64_t)HK * D, (uint64_t)HK * D, C, D, &map_k) ||
+        !tensor_map_2d_plain(v, (uint64_t)T, (uint64_t)H * D, (uint64_t)H * D, C, D, &map_v))
+        return CS1_ERR_TENSOR_MAP;
+    gdn_prep<<<dim3(NC, H), PREP_THREADS, PREP_SMEM, st>>>(map_k, map_v, static_cast<const bf16*>(q),
+                                                          static_cast<const bf16*>(k), g,
                                                           static_cast<const bf16*>(beta), ws, T, H, HK, scale);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    // Narrow slices when there are few heads, so that the scan still covers the SMs.
-    if (H * (D / 32) >= 96) {
+    if (ws.vs == 32) {
         e = set_smem_once(gdn_scan<32, 8>, ScanSmem<32>::BYTES, scan32_done);
         if (e != cudaSuccess) return e;
         gdn_scan<32, 8><<<dim3(H, D / 32), 256, ScanSmem<32>::BYTES, st>>>(ws, static_cast<bf16*>(o), T, H, NC, si, so);
@@ -640,6 +740,22 @@ int gdn_run(const void* q, const void* k, const void* v, const float* g, const v
 }  // namespace s1
 
 using namespace s1;
+
+// The device error word of the delta-rule kernels on the current device (0 = no bounded wait for
+// a copy ever gave up) after waiting for all queued work; cleared by the call.
+extern "C" int s1_gdn_status(int* code) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return e;
+    int v = 0;
+    e = cudaMemcpyFromSymbol(&v, s1::g_gdn_error, sizeof(int));
+    if (e != cudaSuccess) return e;
+    if (v != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(s1::g_gdn_error, &zero, sizeof(int));
+    }
+    *code = v;
+    return e;
+}
 
 extern "C" size_t cs1_gdn_workspace_floats(int T, int H) {
     if (T < 0 || H < 0) return 0;
@@ -670,7 +786,7 @@ extern "C" int cs1_gdn_prefill_x(const void* q, const void* k, const void* v, co
 //
 // Limits and rules, all consequences of the array being one fixed, shared block:
 //   * the window must fit: cs1_gdn_workspace_floats(T, H) * 4 <= CS1_GDN_STATIC_SCRATCH_BYTES
-//     (64 MiB: for example 1792 tokens at 32 value heads, 1152 at 48, 3584 at 16); anything
+//     (64 MiB: for example 1600 tokens at 32 value heads, 1088 at 48, 3072 at 16); anything
 //     larger is refused with CS1_ERR_STATIC_SCRATCH before any launch;
 //   * every call on a GPU uses the same bytes, so two calls that may run at the same time
 //     on one GPU (different streams, or different threads) race on it; calls on one stream

@@ -80,6 +80,15 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         : "memory");
 }
 
+// One contiguous run of global memory into shared memory by the copy engine; `bytes` (a multiple
+// of 16, both addresses 16-byte aligned) are counted on `bar` as they land.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_addr(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+
 // ---- tensor memory ----
 // One whole warp allocates `cols` columns (power of two, 32..512); the base address lands in *dst (shared).
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst, uint32_t cols) {

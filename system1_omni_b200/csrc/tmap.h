@@ -10,4 +10,8 @@ namespace s1 {
 // driver entry point is missing or refuses the arguments (base not 16-byte aligned, ...).
 bool tensor_map_2d(const void* ptr, uint64_t rows, uint64_t cols, uint64_t row_stride, uint32_t box_rows,
                    CUtensorMap* out);
+// The same without swizzle: boxes of [box_rows, box_cols] (box_cols * 2 bytes a multiple of 16, at
+// most 256 columns) land densely packed, row after row.
+bool tensor_map_2d_plain(const void* ptr, uint64_t rows, uint64_t cols, uint64_t row_stride, uint32_t box_rows,
+                         uint32_t box_cols, CUtensorMap* out);
 }  // namespace s1

@@ -92,6 +92,7 @@ SIGNATURES = {
     "s1_gemm_tc5_status": (i32, [ip]),
     "s1_gemm_unsplit": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "s1_attn_tc5_status": (i32, [ip]),
+    "s1_gdn_status": (i32, [ip]),
     "s1_checkpoint_inspect": (i32, [C.c_char_p, C.c_char_p, C.c_size_t, ip, i32, C.c_char_p, C.c_size_t, C.c_char_p,
                                     C.c_size_t, ip, vp, vp]),
     "s1_model_load_checkpoint": (i32, [vp, C.c_char_p, C.c_char_p, C.c_size_t]),
@@ -258,6 +259,12 @@ def gemm_status():
 def attn_status():
     code = C.c_int(0)
     check(load().s1_attn_tc5_status(C.byref(code)), "attention status")
+    return code.value
+
+
+def gdn_status():
+    code = C.c_int(0)
+    check(load().s1_gdn_status(C.byref(code)), "delta-rule status")
     return code.value
 
 
