@@ -47,6 +47,7 @@ class Bench:
         self.e0, self.e1 = L.Event(), L.Event()
         self.rng = np.random.default_rng(0)
         self.gemm_shape = None
+        self.attn_shape = None
 
     def bf16(self, n, scale=1.0):
         """n bf16 values ~ N(0, scale) as a device buffer (bit patterns made on the host)."""
@@ -337,8 +338,12 @@ def requests(b, out):
 
 def attention(b, out):
     lib, st = b.lib, b.stream.handle
-    for dh, hq, hk in [(128, 16, 4), (128, 24, 4), (256, 16, 4), (256, 24, 4)]:
-        for T in (1024, 4096, 16384):
+    cases = [(dh, hq, hk, T) for dh, hq, hk in [(128, 16, 4), (128, 24, 4), (256, 16, 4), (256, 24, 4)]
+             for T in (1024, 4096, 16384)]
+    if b.attn_shape:
+        cases = [tuple(b.attn_shape)]
+    for dh, hq, hk, T in cases:
+        if True:
             q, k, v = b.bf16(T * hq * dh), b.bf16(T * hk * dh), b.bf16(T * hk * dh)
             gate = b.bf16(T * hq * dh)
             o = L.DeviceBuffer(T * hq * dh * 2)
@@ -357,12 +362,15 @@ def main():
     ap.add_argument("--out", default=None)
     ap.add_argument("--gemm-shape", type=int, nargs=3, metavar=("M", "N", "K"), default=None,
                     help="time this one GEMM problem only (for a profiler capture)")
+    ap.add_argument("--attn-shape", type=int, nargs=4, metavar=("Dh", "Hq", "Hk", "T"), default=None,
+                    help="time this one attention problem only (for a profiler capture)")
     ap.add_argument("--gdn-shape", type=int, nargs=3, metavar=("H", "HK", "T"), default=None,
                     help="time this one delta-rule problem only (for a profiler capture)")
     args = ap.parse_args()
     b = Bench(args.warmup, args.iters)
     b.gemm_shape = args.gemm_shape
     b.gdn_shape = args.gdn_shape
+    b.attn_shape = args.attn_shape
     sink = open(args.out, "w") if args.out else None
 
     def out(row):
