@@ -24,6 +24,8 @@
 // the chunk-entry state. The state is float32 across calls (s_in / s_out), so a window that
 // starts on a multiple of 64 tokens continues a previous one bit for bit.
 #include <cuda.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include <mutex>
 
@@ -445,6 +447,414 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
 }
 
 // ---------------------------------------------------------------------------------------
+// gdn_prep_tc5: the same work with the dense products on tcgen05, two chunks (128 rows) of one
+// value head per block. The pair products k.k and q.k are two 128 x 128 x 128 TF32 MMAs whose
+// operands the norm phase writes straight into the swizzled K-major layout (only the two 64 x 64
+// diagonal blocks of each result are used); u and w are one 128 x 256 x 128 bf16 MMA of the
+// block-diagonal T beta with [v | k exp(cum)], v arriving as a TMA tile and read MN-major. The
+// results come back through tensor memory, one row per thread. Everything between - decays,
+// norms, masks, the triangular inverse - is the float32 code of gdn_prep on twice the rows.
+// ---------------------------------------------------------------------------------------
+constexpr int R2 = 2 * C;                        // rows per block
+constexpr int BOX = R2 * 128;                    // bytes of one [128 rows x 128 bytes] swizzled box
+constexpr int T_KF = 0;                          // float, 4 boxes of 32 columns: k normalised (TF32 bits)
+constexpr int T_QF = T_KF + 4 * BOX;             // float, 4 boxes: q normalised * scale (TF32 bits)
+constexpr int T_KE = T_QF + 4 * BOX;             // bf16, 2 boxes of 64 columns: k exp(cum)
+constexpr int T_A = T_KE + 2 * BOX;              // float [128][LDA]: A, then T, block by chunk
+constexpr int T_X = T_A + R2 * LDA * 4;          // float [2][32][LDX]: temporaries of the two inverses
+constexpr int T_SM = T_X + 2 * 32 * LDX * 4;     // float [4][128]: cum, beta, exp(cum), exp(cum_last - cum)
+constexpr int T_BAR = T_SM + 4 * R2 * 4;         // three mbarriers, the tensor-memory address, a flag
+constexpr int PREP2_SMEM = T_BAR + 64 + 1024;    // + slack to align the base to 1024
+// once the pair products are done, over their operands:
+constexpr int T_TB = T_KF;                       // bf16, 2 boxes of 64 k-columns: T beta (block diagonal)
+constexpr int T_VB = T_QF + 2 * BOX;             // bf16, 2 boxes of 64 columns: v, as TMA leaves it; T_KE follows
+static_assert(T_VB + 2 * BOX == T_KE, "v and k exp(cum) form one MN-major operand of four boxes");
+constexpr int PREP2_THREADS = 512;  // 16 warps: the float32 phases between the MMAs need the threads
+
+__global__ void __launch_bounds__(PREP2_THREADS, 1)
+    gdn_prep_tc5(const __grid_constant__ CUtensorMap map_v, const bf16* __restrict__ q, const bf16* __restrict__ k,
+                 const float* __restrict__ g, const bf16* __restrict__ beta, Work ws, int T, int H, int HK, int NC,
+                 float scale) {
+    using namespace tc5;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
+    float* A = reinterpret_cast<float*>(smem + T_A);
+    float* cum = reinterpret_cast<float*>(smem + T_SM);
+    float* bt = cum + R2;
+    float* ecum = bt + R2;
+    float* erem = ecum + R2;
+    uint64_t* bar_s = reinterpret_cast<uint64_t*>(smem + T_BAR);  // pair products done
+    uint64_t* bar_v = bar_s + 1;                                  // v has landed
+    uint64_t* bar_uw = bar_s + 2;                                 // u, w product done
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_s + 3);
+    volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int c0 = 2 * blockIdx.x, h = blockIdx.y, hk = h / (H / HK);
+    const int r0 = c0 * C;
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const size_t tile0 = (size_t)h * NC + c0;   // (head, chunk) tile of rows [0, 64); rows [64, 128) are tile0 + 1
+    const bool second = c0 + 1 < NC;            // the second chunk exists
+    if (tid == 0) {
+        mbar_init(bar_s, 1);
+        mbar_init(bar_v, 1);
+        mbar_init(bar_uw, 1);
+        *gave_up = 0;
+        mbar_init_fence();
+        prefetch_tmap(&map_v);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    auto wait_for = [&](uint64_t* bar) {
+        if (!mbar_wait(bar, 0, gave_up)) {
+            atomicCAS(&g_gdn_error, 0, 43);
+            *gave_up = 1;
+        }
+    };
+
+    // ---- log-decays per chunk: sequential float32 prefix sums, rows past the end have g = beta = 0 ----
+    if (tid < R2) {
+        const int row = r0 + tid;
+        cum[tid] = row < T ? g[(size_t)row * H + h] : 0.f;
+        bt[tid] = row < T ? f32(beta[(size_t)row * H + h]) : 0.f;
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    if (lane == 0 && warp < 2) {  // one thread per chunk
+        float* cc = cum + warp * C;
+        float run = 0.f;
+#pragma unroll 8
+        for (int i = 0; i < C; i++) cc[i] = (run += cc[i]);
+    }
+    __syncthreads();
+    if (tid < R2) {
+        const float last = cum[(tid & ~(C - 1)) + C - 1];
+        ecum[tid] = expf(cum[tid]);
+        erem[tid] = expf(last - cum[tid]);
+        if ((tid & (C - 1)) == 0 && (tid == 0 || second)) ws.decay[tile0 + (tid >> 6)] = expf(last);
+    }
+    __syncthreads();
+
+    // ---- L2 norms; TF32 operand tiles in the swizzled K-major layout; k exp(cum) in the swizzled
+    //      MN-major layout; qd and kd to the workspace. 16 lanes per row, 32 rows per pass; a lane
+    //      owns dims [4 sub, 4 sub + 4) and [64 + 4 sub, 64 + 4 sub + 4). ----
+    {
+        const int sub = tid & 15, rsel = tid >> 4, d0 = sub * 4;
+        // all rows of k and q are requested before the first is used
+        uint2 raws[2][4][2];
+#pragma unroll
+        for (int which = 0; which < 2; which++) {
+            const bf16* src0 = which == 0 ? k : q;
+#pragma unroll
+            for (int pass = 0; pass < 4; pass++) {
+                const int r = pass * 32 + rsel;
+                raws[which][pass][0] = raws[which][pass][1] = make_uint2(0, 0);
+                if (r0 + r < T) {
+                    const bf16* src = src0 + ((size_t)(r0 + r) * HK + hk) * D + d0;
+                    raws[which][pass][0] = *reinterpret_cast<const uint2*>(src);
+                    raws[which][pass][1] = *reinterpret_cast<const uint2*>(src + 64);
+                }
+            }
+        }
+#pragma unroll
+        for (int which = 0; which < 2; which++) {  // 0: k, 1: q
+            const bool is_k = which == 0;
+            const uint2 (&raw)[4][2] = raws[which];
+            unsigned char* tile = smem + (is_k ? T_KF : T_QF);
+#pragma unroll
+            for (int pass = 0; pass < 4; pass++) {
+                const int r = pass * 32 + rsel, ch = r >> 6, i = r & (C - 1);
+                float x[8];
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    x[4 * half + 0] = __uint_as_float(raw[pass][half].x << 16);
+                    x[4 * half + 1] = __uint_as_float(raw[pass][half].x & 0xffff0000u);
+                    x[4 * half + 2] = __uint_as_float(raw[pass][half].y << 16);
+                    x[4 * half + 3] = __uint_as_float(raw[pass][half].y & 0xffff0000u);
+                }
+                float ss = 0.f;
+#pragma unroll
+                for (int e = 0; e < 8; e++) ss += x[e] * x[e];
+                ss = warp_sum<16>(ss);
+                float inv = rsqrtf(ss + 1e-6f);
+                if (!is_k) inv *= scale;
+                const float mult = is_k ? erem[r] : ecum[r];
+                const float ec = ecum[r];
+                bf16* dout = (is_k ? ws.kd : ws.qd) + (tile0 + ch) * (C * LDH) + i * LDH;
+                const bool exists = ch == 0 || second;
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    float nrm[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) nrm[e] = x[4 * half + e] * inv;
+                    float4 t;
+                    t.x = __uint_as_float(to_tf32(nrm[0]));
+                    t.y = __uint_as_float(to_tf32(nrm[1]));
+                    t.z = __uint_as_float(to_tf32(nrm[2]));
+                    t.w = __uint_as_float(to_tf32(nrm[3]));
+                    // column 64 half + 4 sub of a float row: box (2 half + sub / 8), 16-byte chunk sub % 8
+                    *reinterpret_cast<float4*>(tile + (2 * half + (sub >> 3)) * BOX + r * 128 +
+                                               (((sub & 7) ^ (r & 7)) * 16)) = t;
+                    if (exists) {
+                        uint2 o;
+                        o.x = pack2(nrm[0] * mult, nrm[1] * mult);
+                        o.y = pack2(nrm[2] * mult, nrm[3] * mult);
+                        *reinterpret_cast<uint2*>(dout + 64 * half + d0) = o;
+                    }
+                    if (is_k) {
+                        // k exp(cum), bf16: box `half` of 64 columns, chunk (4 sub) / 8, 8 bytes at (sub & 1) * 8
+                        uint2 e2;
+                        e2.x = pack2(nrm[0] * ec, nrm[1] * ec);
+                        e2.y = pack2(nrm[2] * ec, nrm[3] * ec);
+                        *reinterpret_cast<uint2*>(smem + T_KE + half * BOX + r * 128 + (((sub >> 1) ^ (r & 7)) * 16) +
+                                                  (sub & 1) * 8) = e2;
+                    }
+                }
+            }
+        }
+    }
+    fence_proxy_async();  // the operand tiles were written by threads, the MMAs read them
+    __syncthreads();
+
+    // ---- pair products: S_kk = k k^T into tensor-memory columns [0, 128), S_qk = q k^T into [128, 256) ----
+    if (tid == 0) {
+        fence_after_sync();
+        constexpr uint32_t idesc = instr_desc(2, R2, R2);
+        const uint32_t kf = smem_addr(smem + T_KF), qf = smem_addr(smem + T_QF);
+#pragma unroll
+        for (int ks = 0; ks < D / 8; ks++) {  // 8 float columns per step; four steps per 32-column box
+            const uint64_t bk = smem_desc_sw128(kf + (ks / 4) * BOX + (ks % 4) * 32);
+            mma_tf32_ss(tmem_base, bk, bk, idesc, ks > 0 ? 1u : 0u);
+            mma_tf32_ss(tmem_base + R2, smem_desc_sw128(qf + (ks / 4) * BOX + (ks % 4) * 32), bk, idesc,
+                        ks > 0 ? 1u : 0u);
+        }
+        mma_commit(bar_s);
+    }
+    wait_for(bar_s);
+    fence_after_sync();
+    // the q operand is dead: v comes in over its second half, four [64 rows, 64 columns] boxes
+    if (tid == 0) {
+        mbar_expect_tx(bar_v, 2 * BOX);
+        for (int cb = 0; cb < 2; cb++)
+            for (int rh = 0; rh < 2; rh++)
+                tma_load_2d(smem + T_VB + cb * BOX + rh * (C * 128), &map_v, h * D + cb * 64, r0 + rh * C, bar_v);
+    }
+
+    // ---- decay masks: warps 0-7 read S_kk -> A (float32, shared), warps 8-15 S_qk -> P (bf16, workspace);
+    //      a thread takes one row, and of its chunk's 64 columns the 32 of its warp group ----
+    {
+        const int quarter = warp & 3, r = quarter * 32 + lane, ch = r >> 6, i = r & (C - 1);
+        const bool is_kk = warp < 8;
+        const int cc = (warp >> 2) & 1;
+        const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (is_kk ? 0 : R2) + ch * C;
+        const float ci = cum[r], bi = bt[r];
+        const float* cj = cum + ch * C;
+        float* a_row = A + r * LDA;
+        bf16* p_row = ws.p + (tile0 + ch) * (C * LDT) + i * LDT;
+        const bool exists = ch == 0 || second;
+        {
+            uint32_t v[32];
+            tmem_ld_32x32(t_row + cc * 32, v);
+            tmem_ld_wait();
+            float y[32];
+#pragma unroll
+            for (int e = 0; e < 32; e++) {
+                const int j = cc * 32 + e;
+                const float w = __uint_as_float(v[e]) * expf(ci - cj[j]);
+                y[e] = is_kk ? (j < i ? bi * w : 0.f) : (j <= i ? w : 0.f);
+            }
+            if (is_kk) {
+#pragma unroll
+                for (int e = 0; e < 8; e++)
+                    *reinterpret_cast<float4*>(a_row + cc * 32 + 4 * e) =
+                        make_float4(y[4 * e], y[4 * e + 1], y[4 * e + 2], y[4 * e + 3]);
+            } else if (exists) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    uint4 o;
+                    o.x = pack2(y[8 * e + 0], y[8 * e + 1]);
+                    o.y = pack2(y[8 * e + 2], y[8 * e + 3]);
+                    o.z = pack2(y[8 * e + 4], y[8 * e + 5]);
+                    o.w = pack2(y[8 * e + 6], y[8 * e + 7]);
+                    *reinterpret_cast<uint4*>(p_row + cc * 32 + 8 * e) = o;
+                }
+            }
+        }
+    }
+    fence_before_sync();
+    __syncthreads();
+
+    // ---- T = (I + A)^-1 for both chunks at once: threads [0, 256) the first, [256, 512) the second ----
+    {
+        const int g2 = tid >> 8, t = tid & 255;
+        float* Ab = A + g2 * C * LDA;
+        float* X = reinterpret_cast<float*>(smem + T_X) + g2 * 32 * LDX;
+        float col[16];
+        if (t < 64) {
+            const float* blk = Ab + (16 * (t >> 4)) * (LDA + 1);
+            const int j = t & 15;
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                float acc = i == j ? 1.f : 0.f;
+#pragma unroll
+                for (int m = 0; m < i; m++) acc -= blk[i * LDA + m] * col[m];
+                col[i] = acc;
+            }
+        }
+        __syncthreads();
+        if (t < 64) {
+            float* blk = Ab + (16 * (t >> 4)) * (LDA + 1);
+            const int j = t & 15;
+#pragma unroll
+            for (int i = 0; i < 16; i++) blk[i * LDA + j] = col[i];
+        }
+        __syncthreads();
+        {   // 16 -> 32: two pairs of diagonal blocks, 2 x 256 outputs, two per thread
+            const int p = t >> 7, idx = t & 127, i = idx >> 3, j0 = (idx & 7) * 2;
+            float* t11 = Ab + (32 * p) * (LDA + 1);
+            float* a21 = t11 + 16 * LDA;
+            const float* t22 = a21 + 16;
+            float x0 = 0.f, x1 = 0.f;
+#pragma unroll
+            for (int m = 0; m < 16; m++) {
+                const float a = a21[i * LDA + m];
+                const float2 tt = *reinterpret_cast<const float2*>(t11 + m * LDA + j0);
+                x0 += a * tt.x;
+                x1 += a * tt.y;
+            }
+            *reinterpret_cast<float2*>(X + (16 * p + i) * LDX + j0) = make_float2(x0, x1);
+            __syncthreads();
+            float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+            for (int m = 0; m < 16; m++) {
+                const float a = t22[i * LDA + m];
+                const float2 tt = *reinterpret_cast<const float2*>(X + (16 * p + m) * LDX + j0);
+                y0 -= a * tt.x;
+                y1 -= a * tt.y;
+            }
+            *reinterpret_cast<float2*>(a21 + i * LDA + j0) = make_float2(y0, y1);
+            __syncthreads();
+        }
+        {   // 32 -> 64: 32 x 32 outputs as 4 x 4 register tiles on 64 threads (a quarter of the
+            // shared-memory traffic of one row per thread, which bounded this step)
+            const int ib = (t >> 3) * 4, j0 = (t & 7) * 4;
+            float* a21 = Ab + 32 * LDA;
+            const float* t22 = a21 + 32;
+            float acc[4][4];
+            if (t < 64) {
+#pragma unroll
+                for (int rr = 0; rr < 4; rr++) acc[rr][0] = acc[rr][1] = acc[rr][2] = acc[rr][3] = 0.f;
+#pragma unroll 4
+                for (int m = 0; m < 32; m++) {
+                    const float4 tt = *reinterpret_cast<const float4*>(Ab + m * LDA + j0);
+#pragma unroll
+                    for (int rr = 0; rr < 4; rr++) {
+                        const float a = a21[(ib + rr) * LDA + m];
+                        acc[rr][0] += a * tt.x, acc[rr][1] += a * tt.y, acc[rr][2] += a * tt.z, acc[rr][3] += a * tt.w;
+                    }
+                }
+#pragma unroll
+                for (int rr = 0; rr < 4; rr++)
+                    *reinterpret_cast<float4*>(X + (ib + rr) * LDX + j0) =
+                        make_float4(acc[rr][0], acc[rr][1], acc[rr][2], acc[rr][3]);
+            }
+            __syncthreads();
+            if (t < 64) {
+#pragma unroll
+                for (int rr = 0; rr < 4; rr++) acc[rr][0] = acc[rr][1] = acc[rr][2] = acc[rr][3] = 0.f;
+#pragma unroll 4
+                for (int m = 0; m < 32; m++) {
+                    const float4 tt = *reinterpret_cast<const float4*>(X + m * LDX + j0);
+#pragma unroll
+                    for (int rr = 0; rr < 4; rr++) {
+                        const float a = t22[(ib + rr) * LDA + m];
+                        acc[rr][0] -= a * tt.x, acc[rr][1] -= a * tt.y, acc[rr][2] -= a * tt.z, acc[rr][3] -= a * tt.w;
+                    }
+                }
+#pragma unroll
+                for (int rr = 0; rr < 4; rr++)
+                    *reinterpret_cast<float4*>(a21 + (ib + rr) * LDA + j0) =
+                        make_float4(acc[rr][0], acc[rr][1], acc[rr][2], acc[rr][3]);
+            }
+            __syncthreads();
+        }
+    }
+    // ---- T beta as the bf16 K-major operand [128 rows][128 k], block diagonal: a thread writes 32
+    //      k-columns of one box of one row - its chunk's values, or zeros off the diagonal ----
+    {
+        const int r = tid >> 2, box = (tid >> 1) & 1, part = tid & 1, ch = r >> 6;
+        unsigned char* dst = smem + T_TB + box * BOX + r * 128;
+        const float* t_row = A + r * LDA;
+        const float* bj = bt + ch * C;
+#pragma unroll
+        for (int c4 = 0; c4 < 4; c4++) {
+            const int cj = 4 * part + c4;
+            uint4 o = make_uint4(0, 0, 0, 0);
+            if (box == ch) {
+                const float4 a0 = *reinterpret_cast<const float4*>(t_row + 8 * cj);
+                const float4 a1 = *reinterpret_cast<const float4*>(t_row + 8 * cj + 4);
+                o.x = pack2(a0.x * bj[8 * cj + 0], a0.y * bj[8 * cj + 1]);
+                o.y = pack2(a0.z * bj[8 * cj + 2], a0.w * bj[8 * cj + 3]);
+                o.z = pack2(a1.x * bj[8 * cj + 4], a1.y * bj[8 * cj + 5]);
+                o.w = pack2(a1.z * bj[8 * cj + 6], a1.w * bj[8 * cj + 7]);
+            }
+            *reinterpret_cast<uint4*>(dst + ((cj ^ (r & 7)) * 16)) = o;
+        }
+    }
+    fence_proxy_async();
+    wait_for(bar_v);
+    __syncthreads();
+
+    // ---- [u | w] = (T beta) [v | k exp(cum)]: one 128 x 256 x 128 product into columns [256, 512) ----
+    if (tid == 0) {
+        fence_after_sync();
+        constexpr uint32_t idesc = instr_desc_b_mn(1, R2, 2 * D);
+        const uint32_t tb = smem_addr(smem + T_TB), vb = smem_addr(smem + T_VB);
+#pragma unroll
+        for (int kk = 0; kk < R2 / 16; kk++)
+            mma_bf16_ss(tmem_base + 2 * R2, smem_desc_sw128(tb + (kk / 4) * BOX + (kk % 4) * 32),
+                        smem_desc_mn_sw128(vb + kk * 2048, BOX, 1024), idesc, kk > 0 ? 1u : 0u);
+        mma_commit(bar_uw);
+    }
+    wait_for(bar_uw);
+    fence_after_sync();
+    {   // warps 0-7 store u, warps 8-15 w; a thread takes one row and the 64 columns of its warp group
+        const int quarter = warp & 3, r = quarter * 32 + lane, ch = r >> 6, i = r & (C - 1);
+        const bool is_u = warp < 8;
+        const int cc0 = ((warp >> 2) & 1) * 2;
+        const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + 2 * R2 + (is_u ? 0 : D);
+        const int vs_w = ws.vs, ldu = vs_w + 8;
+        bf16* u_tile = ws.u + (tile0 + ch) * (size_t)(D / vs_w) * (C * ldu);
+        bf16* w_row = ws.w + (tile0 + ch) * (C * LDH) + i * LDH;
+        const bool exists = ch == 0 || second;
+#pragma unroll 1
+        for (int cc = cc0; cc < cc0 + 2; cc++) {
+            uint32_t v[32];
+            tmem_ld_32x32(t_row + cc * 32, v);
+            tmem_ld_wait();
+            if (!exists) continue;
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                uint4 o;
+                o.x = pack2(__uint_as_float(v[8 * e + 0]), __uint_as_float(v[8 * e + 1]));
+                o.y = pack2(__uint_as_float(v[8 * e + 2]), __uint_as_float(v[8 * e + 3]));
+                o.z = pack2(__uint_as_float(v[8 * e + 4]), __uint_as_float(v[8 * e + 5]));
+                o.w = pack2(__uint_as_float(v[8 * e + 6]), __uint_as_float(v[8 * e + 7]));
+                const int col = cc * 32 + 8 * e;
+                bf16* at = is_u ? u_tile + (col / vs_w) * (C * ldu) + i * ldu + (col % vs_w) : w_row + col;
+                *reinterpret_cast<uint4*>(at) = o;
+            }
+        }
+    }
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// ---------------------------------------------------------------------------------------
 // gdn_scan
 // ---------------------------------------------------------------------------------------
 
@@ -714,14 +1124,29 @@ int gdn_run(const void* q, const void* k, const void* v, const float* g, const v
     if (e != cudaSuccess) return e;
     const int NC = (T + C - 1) / C;
     const Work ws = split(workspace, T, H);
-    // v and k rows of a chunk as [64 rows, 128 columns] tiles of the caller's [T, heads, 128] arrays
-    CUtensorMap map_k, map_v;
-    if (!tensor_map_2d_plain(k, (uint64_t)T, (uint64_t)HK * D, (uint64_t)HK * D, C, D, &map_k) ||
-        !tensor_map_2d_plain(v, (uint64_t)T, (uint64_t)H * D, (uint64_t)H * D, C, D, &map_v))
-        return CS1_ERR_TENSOR_MAP;
-    gdn_prep<<<dim3(NC, H), PREP_THREADS, PREP_SMEM, st>>>(map_k, map_v, static_cast<const bf16*>(q),
-                                                          static_cast<const bf16*>(k), g,
-                                                          static_cast<const bf16*>(beta), ws, T, H, HK, scale);
+    static const bool prep_on_tc5 = [] {
+        const char* v = getenv("S1_GDN_PREP");
+        return !(v && strcmp(v, "mma") == 0);  // S1_GDN_PREP=mma keeps the mma.sync kernel, for A/B runs
+    }();
+    if (prep_on_tc5) {
+        static bool prep2_done[64] = {};
+        e = set_smem_once(gdn_prep_tc5, PREP2_SMEM, prep2_done);
+        if (e != cudaSuccess) return e;
+        CUtensorMap map_v;  // [64 rows, 64 columns] boxes, 128-byte swizzle
+        if (!tensor_map_2d(v, (uint64_t)T, (uint64_t)H * D, (uint64_t)H * D, C, &map_v)) return CS1_ERR_TENSOR_MAP;
+        gdn_prep_tc5<<<dim3((NC + 1) / 2, H), PREP2_THREADS, PREP2_SMEM, st>>>(
+            map_v, static_cast<const bf16*>(q), static_cast<const bf16*>(k), g, static_cast<const bf16*>(beta), ws, T, H,
+            HK, NC, scale);
+    } else {
+        // v and k rows of a chunk as [64 rows, 128 columns] tiles of the caller's [T, heads, 128] arrays
+        CUtensorMap map_k, map_v;
+        if (!tensor_map_2d_plain(k, (uint64_t)T, (uint64_t)HK * D, (uint64_t)HK * D, C, D, &map_k) ||
+            !tensor_map_2d_plain(v, (uint64_t)T, (uint64_t)H * D, (uint64_t)H * D, C, D, &map_v))
+            return CS1_ERR_TENSOR_MAP;
+        gdn_prep<<<dim3(NC, H), PREP_THREADS, PREP_SMEM, st>>>(map_k, map_v, static_cast<const bf16*>(q),
+                                                              static_cast<const bf16*>(k), g,
+                                                              static_cast<const bf16*>(beta), ws, T, H, HK, scale);
+    }
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     if (ws.vs == 32) {
