@@ -40,6 +40,11 @@ int s1_attention_gated_shared_prefix(const void* q, const void* k, const void* v
                                      const void* k_prefix, const void* v_prefix, int ldv_prefix, int prefix_len,
                                      int rows, int Hq, int Hk, int Dh, float scale, void* stream);
 
+/* Per-head L2 norm as an operator of its own (inside cs1_gdn_prefill it is part of the chunk kernel,
+ * gdn_prefill.cu:170-203): out = bf16(x * rsqrt(sum x^2 + 1e-6) * scale) over `rows` rows of 128 bf16;
+ * for the elementwise benchmark sweep and for checks. x and out 16-byte aligned. */
+int s1_l2norm_heads(const void* x, void* out, long long rows, float scale, void* stream);
+
 /* The attention kernel's counterpart of s1_gemm_tc5_status: its device error word (0 = no bounded
  * wait ever gave up), read after waiting for all queued work, then cleared. */
 int s1_attn_tc5_status(int* code);

@@ -202,3 +202,49 @@ extern "C" int cs1_gated_rms_norm(const void* x, const void* z, int ldz, const v
     }
     return cudaGetLastError();
 }
+
+// ---- per-head L2 norm, head dim 128 (the q / k normalisation of the delta rule as an operator of
+// its own: inside cs1_gdn_prefill it is part of the chunk kernel, gdn_prefill.cu:170-203 of the
+// reference; here it exists for the elementwise benchmark sweep and for checks) ----
+namespace s1 {
+namespace {
+__global__ void __launch_bounds__(GN_GROUPS * 16)
+    l2norm_heads_kernel(const bf16* __restrict__ x, bf16* __restrict__ out, int rows, float scale) {
+    constexpr int D = 128;
+    const int group = threadIdx.x / 16, sub = threadIdx.x & 15;
+    uint4 xv[GN_ROWS_PER_GROUP];
+    size_t base[GN_ROWS_PER_GROUP];
+    bool live[GN_ROWS_PER_GROUP];
+#pragma unroll
+    for (int r = 0; r < GN_ROWS_PER_GROUP; r++) {
+        const int row = blockIdx.x * GN_ROWS_PER_BLOCK + r * GN_GROUPS + group;
+        live[r] = row < rows;
+        base[r] = (size_t)(live[r] ? row : rows - 1) * D + sub * 8;
+        xv[r] = ld16_stream(x + base[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < GN_ROWS_PER_GROUP; r++) {
+        float v[8];
+        unpack8(xv[r], v);
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; e++) ss += v[e] * v[e];
+        const float inv = rsqrtf(warp_sum<16>(ss) + 1e-6f) * scale;
+#pragma unroll
+        for (int e = 0; e < 8; e++) v[e] *= inv;
+        if (live[r]) st16(out + base[r], pack8(v));
+    }
+}
+}  // namespace
+}  // namespace s1
+
+// out = bf16(x * rsqrt(sum x^2 + 1e-6) * scale) over rows of 128; x and out 16-byte aligned.
+extern "C" int s1_l2norm_heads(const void* x, void* out, long long rows, float scale, void* stream) {
+    if (rows < 0 || rows > 0x7fffffffLL) return cudaErrorInvalidValue;
+    if (rows == 0) return cudaSuccess;
+    if (!x || !out || !s1::aligned16(x) || !s1::aligned16(out)) return cudaErrorInvalidValue;
+    s1::l2norm_heads_kernel<<<(unsigned)((rows + s1::GN_ROWS_PER_BLOCK - 1) / s1::GN_ROWS_PER_BLOCK), s1::GN_GROUPS * 16, 0,
+                              s1::as_stream(stream)>>>(static_cast<const s1::bf16*>(x), static_cast<s1::bf16*>(out), (int)rows,
+                                                       scale);
+    return cudaGetLastError();
+}

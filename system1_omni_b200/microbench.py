@@ -119,6 +119,9 @@ def elementwise(b, out):
                 res[i].at(), dl[i].at(), nw.at(), no[i].at(), tokens, ch, 1e-6, st)))
             cases.append(("rms_norm", 4 * tokens * ch, na, lambda i: lib.cs1_rms_norm(
                 res[i].at(), nw.at(), no[i].at(), tokens, ch, 1e-6, st)))
+            # per-head L2 norm over rows of 128: ch / 128 heads per token
+            cases.append(("l2norm_heads", 4 * tokens * ch, na, lambda i: lib.s1_l2norm_heads(
+                res[i].at(), no[i].at(), tokens * (ch // 128), 1.0, st)))
             # SiLU * up: intermediate = ch
             sb = 6 * tokens * ch
             ns = b.copies(sb)

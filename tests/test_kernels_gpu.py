@@ -593,3 +593,22 @@ def test_gemm_argument_checks(cs1, stream):
     assert cs1.cs1_gemm(None, None, None, None, 1, 8, 8, 8, stream.handle) != 0
     cs1.cs1_gemm_destroy(handle)
     assert cs1.cs1_vision_gelu(None, 0, 0, stream.handle) == 2000      # present for the loader, not built
+
+
+def test_l2norm_heads_matches_float64(cs1, stream):
+    """The q / k normalisation of the delta rule as an operator of its own (gdn_prefill.cu:170-203:
+    x * rsqrt(sum x^2 + 1e-6), q also times the scale), against float64 rounded to bf16."""
+    rows = 1000 * 3 + 1
+    x = O.random_bf16(rows * 128, 77, 2.0).reshape(rows, 128)
+    x[5] = 0                                               # an all-zero row stays zero
+    xd = dev(x, stream)
+    out = L.DeviceBuffer(rows * 128 * 2)
+    L.check(cs1.s1_l2norm_heads(xd.at(), out.at(), rows, 128 ** -0.5, stream.handle), "l2norm")
+    got = host(out, (rows, 128), stream)
+    xf = f32(x).astype(np.float64)
+    want = bf((xf / np.sqrt((xf * xf).sum(-1, keepdims=True) + 1e-6) * 128 ** -0.5).astype(np.float32))
+    assert (ulp_diff(got, want) <= 1).all()
+    assert (ulp_diff(got, want) == 0).mean() > 0.98
+    assert not got[5].any()
+    assert cs1.s1_l2norm_heads(xd.at(2), out.at(), rows - 1, 1.0, stream.handle) != 0      # not 16-byte aligned
+    assert cs1.s1_l2norm_heads(None, None, 0, 1.0, stream.handle) == 0
