@@ -22,7 +22,7 @@
 
 /* Library-defined error codes (>= 1000, as src/backends/cuda/contract.md:145-148 reserves). */
 #define CS1_ERR_GEMM_BASE 1000      /* 1000 + cublasStatus_t, as the reference (gemm.cu:34) */
-#define CS1_ERR_UNSUPPORTED 2000    /* entry point present for the loader, operation not built */
+#define CS1_ERR_UNSUPPORTED 2000    /* this engine does not take the problem (see s1_gemm_swiglu, s1_gemm_tcgen05) */
 #define CS1_ERR_DEVICE_CHECK 2001   /* a device-side bounded wait gave up */
 #define CS1_ERR_TENSOR_MAP 2002     /* a TMA tensor map could not be encoded */
 #define CS1_ERR_STATIC_SCRATCH 2003 /* the window does not fit the fixed scratch of cs1_gdn_prefill_static */
@@ -131,8 +131,13 @@ void* cs1_gemm_create(size_t workspace_bytes);
 void cs1_gemm_destroy(void* gemm);
 int cs1_gemm(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream);
 
-/* ---- vision tower entry points: ops.h:127-142. The loader needs the symbols; the
- * operations are outside this build and return CS1_ERR_UNSUPPORTED. ---- */
+/* ---- vision tower (single image, hidden 1024, 16 heads of 64): ops.h:125-138, vision.cu, gemm.cu:137-163.
+ * linear: y = bf16(x w^T + bias), the bias joining the float32 sum (cuBLASLt, as in the reference);
+ * gemm_f32: float32 throughout; norm: LayerNorm eps 1e-6; position: x += bf16(sum of four table rows times
+ * their weights), separate float32 multiplies and adds; rope: q, k out of the fused [n, 3072] projection, cos / sin
+ * [n, 32] float32, both products rounded before the add; attention: every query over all n keys, v a slice of
+ * the projection with rows 3072 apart (tcgen05 kernel); bias / gelu / add / lora_add: in place, one bf16
+ * rounding; to_float: widening copy. ---- */
 int cs1_vision_linear(void* gemm, const void* x, const void* w, const void* bias, void* y, int M, int N, int K,
                       void* stream);
 int cs1_gemm_f32(void* gemm, const float* x, const float* w, float* y, int M, int N, int K, void* stream);

@@ -11,7 +11,7 @@ OUT = os.path.join(PKG, "libqwen3_5_cuda.so")
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 
-FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-Xcompiler", "-fPIC",
+FLAGS = ["-O3", "-std=c++17", "--extended-lambda", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-Xcompiler", "-fPIC",
          "-Xcompiler", "-Wall", "-I" + os.path.join(ROOT, "include"), "-I" + CSRC]
 
 

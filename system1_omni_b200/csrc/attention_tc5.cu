@@ -40,7 +40,7 @@ constexpr int ATHREADS = 320;  // producer warp, MMA warp, eight softmax warps
 
 template <int DH>
 struct ACfg {
-    static constexpr int BN = DH == 128 ? 128 : 64;   // keys per tile
+    static constexpr int BN = DH == 256 ? 64 : 128;   // keys per tile
     static constexpr int Q_BYTES = ABM * DH * 2;       // DH / 64 boxes of [128 rows, 64 columns]
     static constexpr int KV_BYTES = BN * DH * 2;       // one K or V tile: DH / 64 column boxes of [BN rows, 64]
     static constexpr int P_BYTES = ABM * BN * 2;       // BN / 64 boxes of [128 rows, 64 keys]
@@ -49,7 +49,9 @@ struct ACfg {
     static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
     static constexpr int OFF_BAR = OFF_P + P_BYTES;
     static constexpr int OFF_X = OFF_BAR + 256;        // float [2][2][128]: row maxima (and sums) of the two halves
-    static constexpr int SMEM = OFF_X + 2048 + 1024;   // 195 KB (Dh 128), 211 KB (Dh 256): one block per SM
+    // 195 KB (Dh 128), 211 KB (Dh 256); Dh 64 needs 116 KB and asks for 120 so that two blocks never share
+    // an SM (each allocates all 512 tensor-memory columns)
+    static constexpr int SMEM = (OFF_X + 2048 + 1024) > 120 * 1024 ? (OFF_X + 2048 + 1024) : 120 * 1024;
     static constexpr int O_COL = 2 * BN;               // tensor memory: two score buffers, then the output
     static constexpr int TMEM_COLS = 512;
 };
@@ -70,7 +72,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // The eight softmax warps. Warp 2 + i and warp 6 + i (i = 0..3) own the 32 query rows of tensor
 // memory lanes [32 ((2 + i) & 3), +32); the first takes the lower half of the score and output
 // columns, the second the upper half.
-template <int DH, bool GATED>
+template <int DH, bool GATED, bool CAUSAL>
 __device__ __forceinline__ void softmax_rows(unsigned char* smem, uint64_t* bars, uint32_t tmem_base,
                                              volatile int* abort_flag, const bf16* __restrict__ gate,
                                              bf16* __restrict__ out, int T, int Hq, int h, int q0, int own_base, int ntiles,
@@ -117,10 +119,10 @@ __device__ __forceinline__ void softmax_rows(unsigned char* smem, uint64_t* bars
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_empty[b]);
             const int k0 = j * BN + hf * HN;
-            if (k0 + HN - 1 > row) {
+            if (CAUSAL ? k0 + HN - 1 > row : k0 + HN > T) {  // causal: keys after the row; else: keys past the end
 #pragma unroll
                 for (int i = 0; i < HN; i++)
-                    if (k0 + i > row) sv[i] = 0xff800000u;  // -inf
+                    if (CAUSAL ? k0 + i > row : k0 + i >= T) sv[i] = 0xff800000u;  // -inf
             }
 #pragma unroll
             for (int i = 0; i < HN; i++) mx = fmaxf(mx, __uint_as_float(sv[i]));
@@ -227,7 +229,7 @@ __device__ __forceinline__ void softmax_rows(unsigned char* smem, uint64_t* bars
     }
 }
 
-template <int DH, bool GATED>
+template <int DH, bool GATED, bool CAUSAL>
 __global__ void __launch_bounds__(ATHREADS, 1)
     attn_tc5_kernel(const __grid_constant__ AttnMaps maps, const bf16* __restrict__ gate, bf16* __restrict__ out, int T,
                     int Hq, int Hk, float scale_log2, int q_base, int own_base, int vec_ok) {
@@ -252,7 +254,7 @@ __global__ void __launch_bounds__(ATHREADS, 1)
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int h = blockIdx.y, hk = h / (Hq / Hk);
     const int q0 = q_base + (gridDim.x - 1 - blockIdx.x) * ABM;  // longest blocks first
-    const int kv_end = min(T, q0 + ABM);
+    const int kv_end = CAUSAL ? min(T, q0 + ABM) : T;
     const int ntiles = (kv_end + BN - 1) / BN;
 
     if (threadIdx.x == 0) {
@@ -385,7 +387,7 @@ __global__ void __launch_bounds__(ATHREADS, 1)
         }
         __syncwarp();
     } else {
-        softmax_rows<DH, GATED>(smem, bars, tmem_base, abort_flag, gate, out, T, Hq, h, q0, own_base, ntiles, scale_log2,
+        softmax_rows<DH, GATED, CAUSAL>(smem, bars, tmem_base, abort_flag, gate, out, T, Hq, h, q0, own_base, ntiles, scale_log2,
                                 vec_ok, warp, lane);
     }
 
@@ -397,7 +399,7 @@ __global__ void __launch_bounds__(ATHREADS, 1)
     if (warp == 2) tmem_dealloc(tmem_base, G::TMEM_COLS);
 }
 
-template <int DH, bool GATED>
+template <int DH, bool GATED, bool CAUSAL = true>
 int launch_attn(const AttnMaps& maps, const bf16* gate, bf16* out, int T, int Hq, int Hk, float scale, int q_base,
                 int own_base, cudaStream_t st) {
     using G = ACfg<DH>;
@@ -407,14 +409,14 @@ int launch_attn(const AttnMaps& maps, const bf16* gate, bf16* out, int T, int Hq
     if (e != cudaSuccess) return e;
     if (dev >= 64) return cudaErrorInvalidDevice;
     if (!configured[dev]) {
-        e = cudaFuncSetAttribute(attn_tc5_kernel<DH, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM);
+        e = cudaFuncSetAttribute(attn_tc5_kernel<DH, GATED, CAUSAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
     constexpr float LOG2E = 1.4426950408889634f;
     const dim3 grid((T - q_base + ABM - 1) / ABM, Hq);
     const int vec_ok = aligned16(out) && (!GATED || aligned16(gate));
-    attn_tc5_kernel<DH, GATED><<<grid, ATHREADS, G::SMEM, st>>>(maps, gate, out, T, Hq, Hk, scale * LOG2E, q_base, own_base,
+    attn_tc5_kernel<DH, GATED, CAUSAL><<<grid, ATHREADS, G::SMEM, st>>>(maps, gate, out, T, Hq, Hk, scale * LOG2E, q_base, own_base,
                                                                vec_ok);
     return cudaGetLastError();
 }
@@ -454,6 +456,20 @@ int s1_attn_tc5(const bf16* q, const bf16* k, const bf16* v, int ldv, const bf16
                     : launch_attn<256, false>(maps, gate, out, T, Hq, Hk, scale, q_base, own_base, st);
     return gate ? launch_attn<128, true>(maps, gate, out, T, Hq, Hk, scale, q_base, own_base, st)
                 : launch_attn<128, false>(maps, gate, out, T, Hq, Hk, scale, q_base, own_base, st);
+}
+
+// Non-causal attention over all n positions, head dim 64, as many key-value heads as query heads
+// (the vision tower's: 16 heads, cs1_vision_attention). v rows are ldv elements apart.
+int s1_attn_tc5_full64(const bf16* q, const bf16* k, const bf16* v, int ldv, bf16* out, int n, int heads, float scale,
+                       cudaStream_t st) {
+    AttnMaps maps;
+    if (!tensor_map_2d(q, (uint64_t)n, (uint64_t)heads * 64, (uint64_t)heads * 64, ABM, &maps.q) ||
+        !tensor_map_2d(k, (uint64_t)n, (uint64_t)heads * 64, (uint64_t)heads * 64, 64, &maps.k) ||
+        !tensor_map_2d(v, (uint64_t)n, (uint64_t)heads * 64, (uint64_t)ldv, 64, &maps.v))
+        return CS1_ERR_TENSOR_MAP;
+    maps.kpre = maps.k;
+    maps.vpre = maps.v;
+    return launch_attn<64, false, false>(maps, nullptr, out, n, heads, heads, scale, 0, 0, st);
 }
 
 // The device error word of the attention kernel on the current device (0 = no bounded wait ever

@@ -12,3 +12,7 @@ bool s1_attn_tc5_enabled();
 int s1_attn_tc5(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v, int ldv,
                 const __nv_bfloat16* gate, __nv_bfloat16* out, int T, int Hq, int Hk, int Dh, float scale, int q_base,
                 const __nv_bfloat16* kpre, const __nv_bfloat16* vpre, int ldvpre, int own_base, cudaStream_t stream);
+// Non-causal attention over all n positions with head dim 64 and heads == key-value heads (the
+// vision tower): q, k, out [n, heads, 64], v rows ldv elements apart. Same return codes.
+int s1_attn_tc5_full64(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v, int ldv,
+                       __nv_bfloat16* out, int n, int heads, float scale, cudaStream_t stream);

@@ -29,7 +29,7 @@ struct Plan {
     cublasLtMatmulAlgo_t algo{};
 };
 
-using Key = std::tuple<int, int, int, int>;  // M, N, K, ldy
+using Key = std::tuple<int, int, int, int, int>;  // M, N, K, ldy, kind (0 bf16, 1 bf16 + bias epilogue, 2 float32)
 constexpr int COUNTER_SLOTS = 16384;
 constexpr size_t PARTIAL_BYTES = (size_t)48 << 20;
 
@@ -56,15 +56,22 @@ void destroy(Plan& p) {
 }
 
 // Row-major y = x w^T is the column-major product y^T [N, M] = (w as [K, N])^T (x as [K, M]).
-int make_plan(Gemm& g, int M, int N, int K, int ldy, Plan& p) {
+int make_plan(Gemm& g, int M, int N, int K, int ldy, Plan& p, int kind = 0) {
+    const cudaDataType_t dt = kind == 2 ? CUDA_R_32F : CUDA_R_16BF;
     cublasStatus_t s = cublasLtMatmulDescCreate(&p.op, CUBLAS_COMPUTE_32F, CUDA_R_32F);
     if (s != CUBLAS_STATUS_SUCCESS) return status(s);
     const cublasOperation_t ta = CUBLAS_OP_T, tb = CUBLAS_OP_N;
     cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_TRANSA, &ta, sizeof(ta));
     cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_TRANSB, &tb, sizeof(tb));
-    if ((s = cublasLtMatrixLayoutCreate(&p.a, CUDA_R_16BF, K, N, K)) != CUBLAS_STATUS_SUCCESS) return status(s);
-    if ((s = cublasLtMatrixLayoutCreate(&p.b, CUDA_R_16BF, K, M, K)) != CUBLAS_STATUS_SUCCESS) return status(s);
-    if ((s = cublasLtMatrixLayoutCreate(&p.c, CUDA_R_16BF, N, M, ldy)) != CUBLAS_STATUS_SUCCESS) return status(s);
+    if (kind == 1) {  // bias added to the float32 sum before the one bf16 rounding (gemm.cu:137-151 of the reference)
+        const cublasLtEpilogue_t ep = CUBLASLT_EPILOGUE_BIAS;
+        const cudaDataType_t bias_type = CUDA_R_16BF;
+        cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_EPILOGUE, &ep, sizeof(ep));
+        cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_BIAS_DATA_TYPE, &bias_type, sizeof(bias_type));
+    }
+    if ((s = cublasLtMatrixLayoutCreate(&p.a, dt, K, N, K)) != CUBLAS_STATUS_SUCCESS) return status(s);
+    if ((s = cublasLtMatrixLayoutCreate(&p.b, dt, K, M, K)) != CUBLAS_STATUS_SUCCESS) return status(s);
+    if ((s = cublasLtMatrixLayoutCreate(&p.c, dt, N, M, ldy)) != CUBLAS_STATUS_SUCCESS) return status(s);
     cublasLtMatmulPreference_t pref;
     if ((s = cublasLtMatmulPreferenceCreate(&pref)) != CUBLAS_STATUS_SUCCESS) return status(s);
     cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &g.workspace_bytes,
@@ -81,15 +88,16 @@ int make_plan(Gemm& g, int M, int N, int K, int ldy, Plan& p) {
     return 0;
 }
 
-int lt_gemm(Gemm& g, const void* x, const void* w, void* y, int M, int N, int K, int ldy, cudaStream_t st) {
+int lt_gemm(Gemm& g, const void* x, const void* w, void* y, int M, int N, int K, int ldy, cudaStream_t st, int kind = 0,
+            const void* bias = nullptr) {
     Plan* p = nullptr;
     {
         std::lock_guard<std::mutex> hold(g.lock);
-        const Key key{M, N, K, ldy};
+        const Key key{M, N, K, ldy, kind};
         auto it = g.plans.find(key);
         if (it == g.plans.end()) {
             Plan fresh;
-            const int rc = make_plan(g, M, N, K, ldy, fresh);
+            const int rc = make_plan(g, M, N, K, ldy, fresh, kind);
             if (rc != 0) {
                 destroy(fresh);
                 return rc;
@@ -99,6 +107,14 @@ int lt_gemm(Gemm& g, const void* x, const void* w, void* y, int M, int N, int K,
         p = &it->second;
     }
     const float alpha = 1.f, beta = 0.f;
+    if (kind == 1) {
+        // the pointer lives in the shared descriptor: one stream per handle, as for everything else here
+        std::lock_guard<std::mutex> hold(g.lock);
+        const cublasStatus_t s = cublasLtMatmulDescSetAttribute(p->op, CUBLASLT_MATMUL_DESC_BIAS_POINTER, &bias, sizeof(bias));
+        if (s != CUBLAS_STATUS_SUCCESS) return status(s);
+        return status(cublasLtMatmul(g.handle, p->op, &alpha, w, p->a, x, p->b, &beta, y, p->c, y, p->c, &p->algo,
+                                     g.workspace, g.workspace_bytes, st));
+    }
     return status(cublasLtMatmul(g.handle, p->op, &alpha, w, p->a, x, p->b, &beta, y, p->c, y, p->c, &p->algo,
                                  g.workspace, g.workspace_bytes, st));
 }
@@ -211,4 +227,20 @@ extern "C" int s1_gemm_tcgen05(void* gemm, const void* x, const void* w, void* y
     if (!g) return s1_gemm_tc5(x, w, y, M, N, K, ldy, nullptr, static_cast<cudaStream_t>(stream));
     const S1GemmScratch scratch = scratch_of(g);
     return s1_gemm_tc5(x, w, y, M, N, K, ldy, &scratch, static_cast<cudaStream_t>(stream));
+}
+
+// ---- the vision tower's two library GEMMs (gemm.cu:137-163 of the reference), on cuBLASLt as there ----
+// y [M, N] = bf16(x w^T + bias): the bias joins the float32 sum before the rounding.
+extern "C" int cs1_vision_linear(void* gemm, const void* x, const void* w, const void* bias, void* y, int M, int N, int K,
+                                 void* stream) {
+    Gemm* g = static_cast<Gemm*>(gemm);
+    if (!g || !bias || !x || !w || !y || M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
+    return lt_gemm(*g, x, w, y, M, N, K, N, static_cast<cudaStream_t>(stream), 1, bias);
+}
+
+// float32 in, float32 out, float32 arithmetic (unmerged LoRA factors; no TF32).
+extern "C" int cs1_gemm_f32(void* gemm, const float* x, const float* w, float* y, int M, int N, int K, void* stream) {
+    Gemm* g = static_cast<Gemm*>(gemm);
+    if (!g || !x || !w || !y || M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
+    return lt_gemm(*g, x, w, y, M, N, K, N, static_cast<cudaStream_t>(stream), 2);
 }

@@ -592,7 +592,6 @@ def test_gemm_argument_checks(cs1, stream):
     assert cs1.cs1_gemm(handle, None, None, None, 1, 8, 8, 4, stream.handle) != 0      # ldy < N
     assert cs1.cs1_gemm(None, None, None, None, 1, 8, 8, 8, stream.handle) != 0
     cs1.cs1_gemm_destroy(handle)
-    assert cs1.cs1_vision_gelu(None, 0, 0, stream.handle) == 2000      # present for the loader, not built
 
 
 def test_l2norm_heads_matches_float64(cs1, stream):
