@@ -40,6 +40,11 @@ TOKENS = 1024
 N_CLASSES = 16
 WORKLOAD = ("cfg2: 4B-shaped hybrid decoder (32 layers 3:1 GDN/attention, hidden 2560, MLP 9728, vocab 151936, "
             "16-class head), 1 request x 1024 uniform-random ids per GPU")
+# DRAM bytes of one launch of the pair kernel (ncu, dram__bytes_read.sum + dram__bytes_write.sum) on the
+# widest projection of this workload; the capture and its command are under profiles/.
+GEMM_TRAFFIC = {"bytes": 72.9e6,
+                "of": "one launch, y[1024,12352] = x[1024,2560] w^T (GDN in_proj): algorithmic 93.7e6 bytes "
+                      "(x 5.2e6 + w 63.2e6 + y 25.3e6, most of y still in L2 when the launch ends)"}
 FAMILIES = ["gemm", "gdn_prefill", "attention", "gdn_conv", "gdn_gates", "rms_norm", "gated_rms_norm", "silu_mul",
             "attn_prep", "other"]
 
@@ -339,7 +344,8 @@ def main():
                           "graph_replays": stats["replays"], "own_kernels_per_eager_step": own_per_step,
                           "library_launches_per_eager_step": int(fam_lib.value) // prof_steps},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
-                     "frac": achieved / pk["tflops"], "traffic": None, "kernel": f"bf16 GEMM, {engine}",
+                     "frac": achieved / pk["tflops"], "traffic": GEMM_TRAFFIC["bytes"] if fam_launch[0] > 0 else None,
+                     "traffic_of": GEMM_TRAFFIC["of"], "kernel": f"bf16 GEMM, {engine}",
                      "launches_per_step": gemm_launches, "flops_per_step": flops, "ms_per_step": gemm_ms,
                      "peak_source": pk["source"] + " (sustained cuBLAS bf16)"},
         "per_family": per_family,
