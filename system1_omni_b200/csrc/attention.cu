@@ -29,6 +29,8 @@ __global__ void __launch_bounds__(256)
                      const bf16* __restrict__ kw, const bf16* __restrict__ cos_t, const bf16* __restrict__ sin_t,
                      bf16* __restrict__ q, bf16* __restrict__ gate, bf16* __restrict__ k, long long total, int Hq,
                      int Hk, int half, float eps) {
+    grid_dep_trigger();
+    grid_dep_sync();
     constexpr int LANES = DH / 8;
     const int sub = threadIdx.x % LANES;
     long long unit = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LANES;
@@ -320,11 +322,11 @@ extern "C" int cs1_attn_prep(const void* qg, const void* kr, int ld, const void*
     const bf16 *a0 = static_cast<const bf16*>(qg), *a1 = static_cast<const bf16*>(kr), *a2 = static_cast<const bf16*>(qw),
                *a3 = static_cast<const bf16*>(kw), *a4 = static_cast<const bf16*>(cos), *a5 = static_cast<const bf16*>(sin);
     if (Dh == 256)
-        attn_prep_kernel<256><<<grid, 256, 0, as_stream(stream)>>>(a0, a1, ld, a2, a3, a4, a5, static_cast<bf16*>(q),
+        launch_dep(attn_prep_kernel<256>, grid, 256, 0, as_stream(stream), a0, a1, ld, a2, a3, a4, a5, static_cast<bf16*>(q),
                                                                    static_cast<bf16*>(gate), static_cast<bf16*>(k),
                                                                    total, Hq, Hk, half, eps);
     else
-        attn_prep_kernel<128><<<grid, 256, 0, as_stream(stream)>>>(a0, a1, ld, a2, a3, a4, a5, static_cast<bf16*>(q),
+        launch_dep(attn_prep_kernel<128>, grid, 256, 0, as_stream(stream), a0, a1, ld, a2, a3, a4, a5, static_cast<bf16*>(q),
                                                                    static_cast<bf16*>(gate), static_cast<bf16*>(k),
                                                                    total, Hq, Hk, half, eps);
     return cudaGetLastError();

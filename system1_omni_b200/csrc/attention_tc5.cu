@@ -279,10 +279,12 @@ __global__ void __launch_bounds__(ATHREADS, 1)
         tmem_alloc(tmem_slot, G::TMEM_COLS);
         tmem_relinquish();
     }
+    grid_dep_trigger();
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    grid_dep_sync();
     auto fail = [&](int code) {
         atomicCAS(&g_attn_error, 0, code);
         *abort_flag = 1;

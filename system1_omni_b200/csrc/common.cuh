@@ -1,6 +1,7 @@
 // Device helpers shared by the sm_100a kernels: bf16 conversion, 128-bit packs, warp and
 // block reductions, and the launch-argument checks every entry point performs.
 #pragma once
+#include <stdlib.h>
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -85,5 +86,38 @@ __device__ __forceinline__ float block_sum(float x, float* scratch) {
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
+
+// ---- programmatic dependent launch ----
+// A kernel launched with launch_dep may become resident while the kernel before it on the stream
+// is still running; it must call grid_dep_sync() before it touches anything that kernel wrote (or
+// still reads). Every kernel on the hot path calls it first thing, so the order of all memory
+// effects is that of ordinary stream order; what overlaps is launch latency, block scheduling and
+// the prologue up to that call. grid_dep_trigger() lets the next kernel start arriving as soon as all
+// blocks of this one are running. Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void grid_dep_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_sync() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+inline bool dep_launch_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("S1_PDL");
+        return v && v[0] == '1';  // off unless asked for
+    }();
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dep_launch_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 }  // namespace s1

@@ -35,6 +35,8 @@ constexpr int CONV_THREADS = 128;
 __global__ void __launch_bounds__(CONV_THREADS)
     gdn_conv_packed_kernel(const bf16* __restrict__ qkv, int ld, const bf16* __restrict__ w, bf16* __restrict__ q,
                            bf16* __restrict__ k, bf16* __restrict__ v, int T, int key_dim, int value_dim) {
+    grid_dep_trigger();
+    grid_dep_sync();
     const int packs = (2 * key_dim + value_dim) / 8;
     const int p = blockIdx.y * CONV_THREADS + threadIdx.x;
     if (p >= packs) return;
@@ -126,6 +128,8 @@ __global__ void gdn_conv_scalar_kernel(const bf16* __restrict__ qkv, int ld, con
 __global__ void gdn_gates_kernel(const bf16* __restrict__ b, const bf16* __restrict__ a, int ld,
                                  const bf16* __restrict__ A_log, const bf16* __restrict__ dt_bias,
                                  bf16* __restrict__ beta, float* __restrict__ g, int n, int H) {
+    grid_dep_trigger();
+    grid_dep_sync();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int h = i % H;
@@ -216,9 +220,9 @@ extern "C" int cs1_gdn_conv(const void* qkv, int ld, const void* w, void* q, voi
                         aligned16(q) && aligned16(k) && aligned16(v);
     if (packed) {
         const dim3 grid((T + CONV_TT - 1) / CONV_TT, (channels / 8 + CONV_THREADS - 1) / CONV_THREADS);
-        gdn_conv_packed_kernel<<<grid, CONV_THREADS, 0, as_stream(stream)>>>(
-            static_cast<const bf16*>(qkv), ld, static_cast<const bf16*>(w), static_cast<bf16*>(q),
-            static_cast<bf16*>(k), static_cast<bf16*>(v), T, key_dim, value_dim);
+        launch_dep(gdn_conv_packed_kernel, grid, CONV_THREADS, 0, as_stream(stream), static_cast<const bf16*>(qkv), ld,
+                   static_cast<const bf16*>(w), static_cast<bf16*>(q), static_cast<bf16*>(k), static_cast<bf16*>(v), T,
+                   key_dim, value_dim);
     } else {
         gdn_conv_scalar_kernel<<<blocks_for(n), THREADS, 0, as_stream(stream)>>>(
             static_cast<const bf16*>(qkv), ld, static_cast<const bf16*>(w), static_cast<bf16*>(q),
@@ -233,9 +237,9 @@ extern "C" int cs1_gdn_gates(const void* b, const void* a, int ld, const void* A
     const long long n = (long long)T * H;
     if (n == 0) return cudaSuccess;
     if (n > 0x7fffffffLL) return cudaErrorInvalidValue;
-    gdn_gates_kernel<<<blocks_for((size_t)n), THREADS, 0, as_stream(stream)>>>(
-        static_cast<const bf16*>(b), static_cast<const bf16*>(a), ld, static_cast<const bf16*>(A_log),
-        static_cast<const bf16*>(dt_bias), static_cast<bf16*>(beta), g, (int)n, H);
+    launch_dep(gdn_gates_kernel, blocks_for((size_t)n), THREADS, 0, as_stream(stream), static_cast<const bf16*>(b),
+               static_cast<const bf16*>(a), ld, static_cast<const bf16*>(A_log), static_cast<const bf16*>(dt_bias),
+               static_cast<bf16*>(beta), g, (int)n, H);
     return cudaGetLastError();
 }
 

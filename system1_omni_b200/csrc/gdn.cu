@@ -513,6 +513,8 @@ __global__ void __launch_bounds__(PREP2_THREADS, 1)
         }
     };
 
+    grid_dep_trigger();
+    grid_dep_sync();
     // ---- log-decays per chunk: sequential float32 prefix sums, rows past the end have g = beta = 0 ----
     if (tid < R2) {
         const int row = r0 + tid;
@@ -912,6 +914,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2)
     const bf16* p_g = ws.p + (size_t)h * NC * (C * LDT);
     const float* decay_g = ws.decay + (size_t)h * NC;
 
+    grid_dep_trigger();
     if (tid == 0) {
         tc5::mbar_init(&wu_bar[0], 1);
         tc5::mbar_init(&wu_bar[1], 1);
@@ -920,6 +923,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2)
         tc5::mbar_init_fence();
     }
     __syncthreads();
+    grid_dep_sync();
     // Issued by one thread: two bulk copies (w, u) into buffer c & 1, three (qd, kd, P) into the
     // single buffer of the second half of a chunk step.
     auto load_wu = [&](int c) {
@@ -1134,9 +1138,7 @@ int gdn_run(const void* q, const void* k, const void* v, const float* g, const v
         if (e != cudaSuccess) return e;
         CUtensorMap map_v;  // [64 rows, 64 columns] boxes, 128-byte swizzle
         if (!tensor_map_2d(v, (uint64_t)T, (uint64_t)H * D, (uint64_t)H * D, C, &map_v)) return CS1_ERR_TENSOR_MAP;
-        gdn_prep_tc5<<<dim3((NC + 1) / 2, H), PREP2_THREADS, PREP2_SMEM, st>>>(
-            map_v, static_cast<const bf16*>(q), static_cast<const bf16*>(k), g, static_cast<const bf16*>(beta), ws, T, H,
-            HK, NC, scale);
+        launch_dep(gdn_prep_tc5, dim3((NC + 1) / 2, H), PREP2_THREADS, PREP2_SMEM, st, map_v, static_cast<const bf16*>(q), static_cast<const bf16*>(k), g, static_cast<const bf16*>(beta), ws, T, H, HK, NC, scale);
     } else {
         // v and k rows of a chunk as [64 rows, 128 columns] tiles of the caller's [T, heads, 128] arrays
         CUtensorMap map_k, map_v;
@@ -1152,11 +1154,11 @@ int gdn_run(const void* q, const void* k, const void* v, const float* g, const v
     if (ws.vs == 32) {
         e = set_smem_once(gdn_scan<32, 8>, ScanSmem<32>::BYTES, scan32_done);
         if (e != cudaSuccess) return e;
-        gdn_scan<32, 8><<<dim3(H, D / 32), 256, ScanSmem<32>::BYTES, st>>>(ws, static_cast<bf16*>(o), T, H, NC, si, so);
+        launch_dep(gdn_scan<32, 8>, dim3(H, D / 32), 256, ScanSmem<32>::BYTES, st, ws, static_cast<bf16*>(o), T, H, NC, si, so);
     } else {
         e = set_smem_once(gdn_scan<16, 4>, ScanSmem<16>::BYTES, scan16_done);
         if (e != cudaSuccess) return e;
-        gdn_scan<16, 4><<<dim3(H, D / 16), 128, ScanSmem<16>::BYTES, st>>>(ws, static_cast<bf16*>(o), T, H, NC, si, so);
+        launch_dep(gdn_scan<16, 4>, dim3(H, D / 16), 128, ScanSmem<16>::BYTES, st, ws, static_cast<bf16*>(o), T, H, NC, si, so);
     }
     return cudaGetLastError();
 }

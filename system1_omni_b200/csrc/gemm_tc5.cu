@@ -86,10 +86,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         tmem_alloc(tmem_slot, G::TMEM_COLS);
         tmem_relinquish();
     }
+    grid_dep_trigger();
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    grid_dep_sync();  // barriers, tensor memory and descriptors are ready; x may still be in the making
 
     const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN;
     const int tiles = num_m * num_n, kblocks = (K + BK - 1) / BK;
@@ -332,9 +334,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     }
     fence_before_sync();
     __syncthreads();
+    grid_dep_trigger();
     cluster_sync();  // both blocks' barriers exist before anything arrives on them
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    grid_dep_sync();  // the prologue above ran under the previous kernel's tail
 
     // swiglu: w is [gate (N rows) | up (N rows)]; a tile pairs BN / 2 gate columns (loaded by the
     // pair's first block) with the same BN / 2 up columns (second block), so both land in one
@@ -768,8 +772,8 @@ int launch(const void* x, const void* w, void* y, int M, int N, int K, int ldy, 
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = tiles < info->sms ? tiles : info->sms;
     const int vec_ok = (ldy % 8 == 0) && aligned16(y);
-    gemm_tc5_kernel<BN><<<grid, GEMM_THREADS, G::SMEM, st>>>(mx, mw, static_cast<bf16*>(y), M, N, K, ldy, vec_ok);
-    return cudaGetLastError();
+    return launch_dep(gemm_tc5_kernel<BN>, grid, GEMM_THREADS, G::SMEM, st, mx, mw, static_cast<bf16*>(y), M, N, K, ldy,
+                      vec_ok);
 }
 
 // Plan for the pair kernel: the column-block width (a multiple of 32) and how the k-blocks
@@ -852,10 +856,8 @@ int launch_pair(const void* x, const void* w, void* y, int M, int N, int K, int 
     const int units = ((M + 2 * BM - 1) / (2 * BM)) * ((N + bn - 1) / bn) * plan.splits;
     const int grid = plan.mode == 1 ? 2 * pairs : 2 * (units < pairs ? units : pairs);
     const int vec_ok = (ldy % 8 == 0) && aligned16(y);
-    gemm_tc5_pair_kernel<<<grid, GEMM_THREADS, PAIR_SMEM, st>>>(mx, mw, static_cast<bf16*>(y), M, N, K, ldy, vec_ok, bn,
-                                                               plan.splits, plan.mode, static_cast<float*>(partials),
-                                                               counters, 0);
-    return cudaGetLastError();
+    return launch_dep(gemm_tc5_pair_kernel, grid, GEMM_THREADS, PAIR_SMEM, st, mx, mw, static_cast<bf16*>(y), M, N, K, ldy,
+                      vec_ok, bn, plan.splits, plan.mode, static_cast<float*>(partials), counters, 0);
 }
 
 // act [M, I] = silu(x w_gate^T) * (x w_up^T) with w = [gate; up] stacked, [2 I, K]: both
@@ -883,9 +885,8 @@ int launch_pair_swiglu(const void* x, const void* w, void* act, int M, int I, in
     const long tiles = num_m * ((I + bn / 2 - 1) / (bn / 2));
     const int grid = 2 * (int)(tiles < pairs ? tiles : pairs);
     const int vec_ok = (ld % 8 == 0) && aligned16(act);
-    gemm_tc5_pair_kernel<<<grid, GEMM_THREADS, PAIR_SMEM, st>>>(mx, mw, static_cast<bf16*>(act), M, I, K, ld, vec_ok, bn,
-                                                               1, 0, nullptr, nullptr, 1);
-    return cudaGetLastError();
+    return launch_dep(gemm_tc5_pair_kernel, grid, GEMM_THREADS, PAIR_SMEM, st, mx, mw, static_cast<bf16*>(act), M, I, K, ld,
+                      vec_ok, bn, 1, 0, static_cast<float*>(nullptr), static_cast<int*>(nullptr), 1);
 }
 
 bool pair_enabled() {
