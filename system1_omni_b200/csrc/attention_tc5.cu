@@ -279,7 +279,6 @@ __global__ void __launch_bounds__(ATHREADS, 1)
         tmem_alloc(tmem_slot, G::TMEM_COLS);
         tmem_relinquish();
     }
-    grid_dep_trigger();
     fence_before_sync();
     __syncthreads();
     fence_after_sync();

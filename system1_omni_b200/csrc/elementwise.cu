@@ -35,7 +35,6 @@ constexpr int CONV_THREADS = 128;
 __global__ void __launch_bounds__(CONV_THREADS)
     gdn_conv_packed_kernel(const bf16* __restrict__ qkv, int ld, const bf16* __restrict__ w, bf16* __restrict__ q,
                            bf16* __restrict__ k, bf16* __restrict__ v, int T, int key_dim, int value_dim) {
-    grid_dep_trigger();
     grid_dep_sync();
     const int packs = (2 * key_dim + value_dim) / 8;
     const int p = blockIdx.y * CONV_THREADS + threadIdx.x;
@@ -128,7 +127,6 @@ __global__ void gdn_conv_scalar_kernel(const bf16* __restrict__ qkv, int ld, con
 __global__ void gdn_gates_kernel(const bf16* __restrict__ b, const bf16* __restrict__ a, int ld,
                                  const bf16* __restrict__ A_log, const bf16* __restrict__ dt_bias,
                                  bf16* __restrict__ beta, float* __restrict__ g, int n, int H) {
-    grid_dep_trigger();
     grid_dep_sync();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;

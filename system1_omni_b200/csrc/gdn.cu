@@ -513,7 +513,6 @@ __global__ void __launch_bounds__(PREP2_THREADS, 1)
         }
     };
 
-    grid_dep_trigger();
     grid_dep_sync();
     // ---- log-decays per chunk: sequential float32 prefix sums, rows past the end have g = beta = 0 ----
     if (tid < R2) {
@@ -914,7 +913,6 @@ __global__ void __launch_bounds__(WARPS * 32, 2)
     const bf16* p_g = ws.p + (size_t)h * NC * (C * LDT);
     const float* decay_g = ws.decay + (size_t)h * NC;
 
-    grid_dep_trigger();
     if (tid == 0) {
         tc5::mbar_init(&wu_bar[0], 1);
         tc5::mbar_init(&wu_bar[1], 1);

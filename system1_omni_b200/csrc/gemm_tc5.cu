@@ -86,7 +86,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         tmem_alloc(tmem_slot, G::TMEM_COLS);
         tmem_relinquish();
     }
-    grid_dep_trigger();
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
@@ -334,7 +333,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     }
     fence_before_sync();
     __syncthreads();
-    grid_dep_trigger();
     cluster_sync();  // both blocks' barriers exist before anything arrives on them
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
