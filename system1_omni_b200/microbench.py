@@ -339,6 +339,41 @@ def requests(b, out):
     model.close()
 
 
+def latency(b, out):
+    """Prefill time of one request on the 4B-shaped decoder (32 layers, 7.9 GB of bf16 weights) against
+    its length, CUDA-graph replay, ids resident on the device: the short-prompt end is bound by one pass
+    of the weights through HBM and by the number of launches, the long end by the GEMMs."""
+    from . import model as M
+    types = [("full_attention" if (i + 1) % 4 == 0 else "linear_attention") for i in range(32)]
+    cfg = M.Config(hidden=2560, intermediate=9728, layer_types=types, heads=16, kv_heads=4, head_dim=128,
+                   rotary_half=32, lin_k_heads=16, lin_v_heads=32, vocab=151936, eps=1e-6, rope_theta=1e7,
+                   max_positions=262144)
+    hbm, _, _ = peaks()
+    model = M.Model(cfg, device=0)
+    model.init_random(seed=0, std=0.02)
+    model.enable_graphs(True)
+    floor_ms = model.weight_bytes / (hbm * 1e9) * 1e3
+    rng = np.random.default_rng(0)
+    e0, e1 = L.Event(), L.Event()
+    stream = model.stream                      # the model's own stream (a raw handle)
+    for T in (64, 128, 256, 512, 1024, 2048, 4096, 8192, 16384):
+        ids = L.to_device(rng.integers(0, cfg.vocab, T).astype(np.int32), b.stream)
+        lengths = np.array([T], np.int32)
+        for _ in range(3):
+            model.forward_device(ids.at(), lengths)
+        model.synchronize()
+        n = 10 if T <= 4096 else 3
+        e0.record(stream)
+        for _ in range(n):
+            model.forward_device(ids.at(), lengths)
+        e1.record(stream)
+        model.synchronize()
+        ms = e0.elapsed_ms(e1) / n
+        out({"op": "prefill_latency", "model": "4B-shaped", "tokens": T, "ms": ms, "tokens_per_s": T / ms * 1e3,
+             "weights_once_through_hbm_ms": floor_ms})
+    model.close()
+
+
 def attention(b, out):
     lib, st = b.lib, b.stream.handle
     cases = [(dh, hq, hk, T) for dh, hq, hk in [(128, 16, 4), (128, 24, 4), (256, 16, 4), (256, 24, 4)]
@@ -359,7 +394,7 @@ def attention(b, out):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", default="all", choices=["elementwise", "gemm", "gdn", "layer", "attention", "prefix", "requests", "all"])
+    ap.add_argument("--what", default="all", choices=["elementwise", "gemm", "gdn", "layer", "attention", "prefix", "requests", "latency", "all"])
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--out", default=None)
@@ -388,6 +423,8 @@ def main():
             fn(b, out)
     if args.what == "prefix":  # builds a 9B-shaped model (14 GB of weights): only on request
         prefix(b, out)
+    if args.what == "latency":
+        latency(b, out)
     if args.what == "requests":  # builds a 27B-shaped model (47 GB of weights): only on request
         requests(b, out)
     if sink:

@@ -168,3 +168,34 @@ def test_device_random_init_is_seeded_and_shaped(cs1):
     finally:
         m1.close()
         m2.close()
+
+
+@pytest.mark.parametrize("name,shape", [
+    ("9B-shaped", dict(hidden=4096, intermediate=12288, heads=32, kv_heads=8, lin_k=16, lin_v=32)),
+    ("27B-shaped", dict(hidden=5120, intermediate=17408, heads=24, kv_heads=4, lin_k=16, lin_v=48)),
+])
+def test_truncated_large_shapes_match_the_oracle(cs1, name, shape):
+    """One 3 GDN + 1 attention period at the widths of the 9B- and 27B-shaped decoders of
+    BASELINE.json's third and fourth configurations (their depth is cut to four layers so that the
+    CPU oracle finishes in seconds), packed prompts that cross chunk and tile boundaries: per-layer
+    residual streams and last hidden states against the oracle, argmax of a 16-class head identical."""
+    cfg = tiny_config(head_dim=128, vocab=1024, **shape)
+    weights = random_weights(cfg, seed=11)
+    model = M.Model(cfg, device=0)
+    try:
+        model.set_tensors(weights)
+        rng = np.random.default_rng(3)
+        prompts = [rng.integers(0, cfg.vocab, n).tolist() for n in (130, 65)]
+        last, layers = model.forward_batch(prompts, want_layers=True)
+    finally:
+        model.close()
+    want_last, want_layers = O.forward(cfg.oracle_dict(), weights, np.concatenate(prompts), [len(p) for p in prompts],
+                                       want_layers=True)
+    for li in range(cfg.n_layers):
+        assert rel_l2(f32(layers[li]), f32(want_layers[li])) < 2e-2, (name, li)
+    head = np.random.default_rng(7).normal(0, 1.0, (16, cfg.hidden)).astype(np.float32)
+    for s in range(len(prompts)):
+        assert rel_l2(last[s], want_last[s]) < 3e-2, name
+        got, want = M.head_logits(head, last[s]), O.letter_logits(head, want_last[s], 16)
+        if np.sort(want)[-1] - np.sort(want)[-2] > 0.1 * max(1.0, np.abs(want).max()):
+            assert M.answer(got)[0] == O.decide(want)[0], name
