@@ -66,6 +66,10 @@ int s1_gemm_swiglu(void* gemm, const void* x, const void* w, void* act, int M, i
 /* Waits for the device, returns in *code the error word of the tcgen05 GEMM (0 = no bounded
  * wait gave up) and clears it. */
 int s1_gemm_tc5_status(int* code);
+/* Diagnostics: how many clusters of c blocks of the tcgen05 GEMM's single-block kernel of column
+ * width bn (64, 128 or 256) the current device holds at once; 0 = such a launch is not possible.
+ * With at most 128 rows a tile's k-blocks are shared by the blocks of one cluster. */
+int s1_gemm_tc5_cluster_room(int bn, int c);
 
 /* ---- host executor: the decoder prefill the reference keeps in Rust ---- */
 

@@ -55,7 +55,7 @@ __device__ int g_gemm_error = 0;
 template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
-                    bf16* __restrict__ y, int M, int N, int K, int ldy, int vec_ok) {
+                    bf16* __restrict__ y, int M, int N, int K, int ldy, int vec_ok, int splits) {
     using namespace tc5;
     using G = Cfg<BN>;
     extern __shared__ unsigned char smem_raw[];
@@ -94,6 +94,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 
     const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN;
     const int tiles = num_m * num_n, kblocks = (K + BK - 1) / BK;
+    // splits > 1: the launch is made of clusters of `splits` blocks, one cluster per tile, and
+    // the block of cluster rank r accumulates the r-th share of the k-blocks
+    const uint32_t crank = splits > 1 ? cluster_ctarank() : 0u;
+    const int kb_per = (kblocks + splits - 1) / splits;
+    const int kb0 = (int)crank * kb_per, kb1 = min(kblocks, kb0 + kb_per);
+    const int first = splits > 1 ? (int)blockIdx.x / splits : (int)blockIdx.x;
+    const int step = splits > 1 ? tiles : (int)gridDim.x;
+    constexpr int LDS = BN + 4;  // row pitch (floats) of the float32 tile staged for the cluster sum
+    float* staged = reinterpret_cast<float*>(smem);
     auto fail = [&](int code) {
         atomicCAS(&g_gemm_error, 0, code);
         *abort_flag = 1;
@@ -103,9 +112,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
+            for (int tile = first; ok && tile < tiles; tile += step) {
                 const int m_idx = tile % num_m, n_idx = tile / num_m;
-                for (int kb = 0; kb < kblocks; kb++) {
+                for (int kb = kb0; kb < kb1; kb++) {
                     if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
                         fail(1);
                         ok = false;
@@ -128,7 +137,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             constexpr uint32_t idesc = instr_desc(1, BM, BN);
             uint32_t stage = 0, phase = 0, it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x, it++) {
+            for (int tile = first; ok && tile < tiles; tile += step, it++) {
                 const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
                 if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) {
                     fail(3);
@@ -136,7 +145,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 }
                 fence_after_sync();
                 const uint32_t d = tmem_base + acc * BN;
-                for (int kb = 0; kb < kblocks; kb++) {
+                for (int kb = kb0; kb < kb1; kb++) {
                     if (!mbar_wait(&full[stage], phase, abort_flag)) {
                         fail(2);
                         ok = false;
@@ -148,7 +157,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 #pragma unroll
                     for (int k = 0; k < BK / 16; k++) {
                         mma_bf16_ss(d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
-                                    (kb | k) != 0);
+                                    ((kb - kb0) | k) != 0);
                     }
                     mma_commit(&empty[stage]);
                     if (++stage == G::STAGES) {
@@ -163,7 +172,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     } else {
         const int quarter = warp & 3;  // tensor-memory lanes [32 quarter, 32 quarter + 32) belong to this warp
         uint32_t it = 0;
-        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, it++) {
+        for (int tile = first; tile < tiles; tile += step, it++) {
             const int m_idx = tile % num_m, n_idx = tile / num_m;
             const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
             if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) {
@@ -178,7 +187,17 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + cc * 32, v);
                 tmem_ld_wait();
                 const int col0 = n_idx * BN + cc * 32;
-                if (row < M && col0 < N) {
+                if (splits > 1) {
+                    // this block's share of the sum over k, float32, into the stage ring (all of its
+                    // loads have been consumed: the accumulator barrier follows the last MMA)
+                    if (row < M) {
+                        float4* dst = reinterpret_cast<float4*>(staged + (quarter * 32 + lane) * LDS + cc * 32);
+#pragma unroll
+                        for (int j = 0; j < 8; j++)
+                            dst[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                 __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                    }
+                } else if (row < M && col0 < N) {
                     bf16* dst = y + (size_t)row * ldy + col0;
                     if (vec_ok && col0 + 32 <= N) {
 #pragma unroll
@@ -201,6 +220,57 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             __syncwarp();
             if (lane == 0) mbar_arrive(&tempty[acc]);
         }
+    }
+
+    if (splits > 1) {
+        // Sum over the cluster in rank order (the same order whatever the timing): every block reads
+        // its share of the tile's elements from all the blocks' staged tiles through distributed
+        // shared memory, rounds once and stores. Both cluster barriers are reached by every thread
+        // of every block, also after a wait gave up, so no block is left waiting at one.
+        __syncwarp();
+        cluster_sync();
+        if (!*abort_flag && first < tiles) {
+            const int m_idx = first % num_m, n_idx = first / num_m;
+            const int rows = min(BM, M - m_idx * BM);
+            constexpr int Q = BN / 4;
+            const int total = rows * Q;
+            const int lo = (int)((long)total * crank / splits), hi = (int)((long)total * (crank + 1) / splits);
+            uint32_t peer[8];
+#pragma unroll
+            for (int p = 0; p < 8; p++) peer[p] = p < splits ? map_to_rank(smem_addr(staged), p) : 0u;
+            for (int idx = lo + (int)threadIdx.x; idx < hi; idx += GEMM_THREADS) {
+                const int r = idx / Q, c4 = idx % Q;
+                const uint32_t off = (uint32_t)(r * LDS + c4 * 4) * 4u;
+                float4 part[8];
+#pragma unroll
+                for (int p = 0; p < 8; p++)
+                    if (p < splits) part[p] = ld_cluster_f4(peer[p] + off);
+                float4 sum = part[0];
+#pragma unroll
+                for (int p = 1; p < 8; p++)
+                    if (p < splits) {
+                        sum.x += part[p].x;
+                        sum.y += part[p].y;
+                        sum.z += part[p].z;
+                        sum.w += part[p].w;
+                    }
+                const int col = n_idx * BN + c4 * 4;
+                if (col < N) {
+                    bf16* dst = y + (size_t)(m_idx * BM + r) * ldy + col;
+                    if (vec_ok && col + 4 <= N) {
+                        uint2 o;
+                        o.x = pack2(sum.x, sum.y);
+                        o.y = pack2(sum.z, sum.w);
+                        *reinterpret_cast<uint2*>(dst) = o;
+                    } else {
+                        const float e[4] = {sum.x, sum.y, sum.z, sum.w};
+                        for (int j = 0; j < 4; j++)
+                            if (col + j < N) dst[j] = to_bf16(e[j]);
+                    }
+                }
+            }
+        }
+        cluster_sync();  // no block leaves while another still reads its staged tile
     }
 
     // wind down: after an abort give copies and MMAs in flight time to land before the
@@ -737,6 +807,7 @@ struct DeviceInfo {
     int sms = 0;
     bool smem_set[3] = {false, false, false};
     bool pair_smem_set = false;
+    int cluster_room[3][9] = {};  // clusters of c blocks of the single-block kernel that fit the GPU at once; 0 = not asked yet, -1 = none
 };
 
 DeviceInfo* device_info(cudaError_t* err) {
@@ -756,22 +827,125 @@ DeviceInfo* device_info(cudaError_t* err) {
 }
 
 template <int BN>
-int launch(const void* x, const void* w, void* y, int M, int N, int K, int ldy, DeviceInfo* info, int slot,
+cudaError_t prepare(DeviceInfo* info, int slot) {
+    if (info->smem_set[slot]) return cudaSuccess;
+    using G = Cfg<BN>;
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc5_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM);
+    if (e != cudaSuccess) return e;
+    info->smem_set[slot] = true;
+    return cudaSuccess;
+}
+
+// How many clusters of c blocks of gemm_tc5_kernel<BN> the GPU holds at once (its blocks take a
+// whole SM each, and a cluster must fit one GPC).
+template <int BN>
+int cluster_room(DeviceInfo* info, int slot, int c) {
+    if (c < 2 || c > 8) return 0;
+    if (info->cluster_room[slot][c] == 0) {
+        int n = 0;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(c * info->sms);
+        cfg.blockDim = dim3(GEMM_THREADS);
+        cfg.dynamicSmemBytes = Cfg<BN>::SMEM;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = c;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (prepare<BN>(info, slot) != cudaSuccess ||
+            cudaOccupancyMaxActiveClusters(&n, gemm_tc5_kernel<BN>, &cfg) != cudaSuccess) {
+            cudaGetLastError();
+            n = 0;
+        }
+        info->cluster_room[slot][c] = n > 0 ? n : -1;
+    }
+    return info->cluster_room[slot][c] > 0 ? info->cluster_room[slot][c] : 0;
+}
+
+template <int BN>
+int launch(const void* x, const void* w, void* y, int M, int N, int K, int ldy, DeviceInfo* info, int slot, int splits,
            cudaStream_t st) {
     using G = Cfg<BN>;
-    if (!info->smem_set[slot]) {
-        const cudaError_t e =
-            cudaFuncSetAttribute(gemm_tc5_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM);
-        if (e != cudaSuccess) return e;
-        info->smem_set[slot] = true;
-    }
+    const cudaError_t e = prepare<BN>(info, slot);
+    if (e != cudaSuccess) return e;
     CUtensorMap mx, mw;
     if (!tensor_map(x, M, K, BM, &mx) || !tensor_map(w, N, K, BN, &mw)) return CS1_ERR_TENSOR_MAP;
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    const int grid = tiles < info->sms ? tiles : info->sms;
     const int vec_ok = (ldy % 8 == 0) && aligned16(y);
-    return launch_dep(gemm_tc5_kernel<BN>, grid, GEMM_THREADS, G::SMEM, st, mx, mw, static_cast<bf16*>(y), M, N, K, ldy,
-                      vec_ok);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(splits > 1 ? tiles * splits : (tiles < info->sms ? tiles : info->sms));
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = G::SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (splits > 1) {  // one cluster per tile, its blocks share the k-blocks
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = splits;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        n++;
+    }
+    if (dep_launch_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, gemm_tc5_kernel<BN>, mx, mw, static_cast<bf16*>(y), M, N, K, ldy, vec_ok, splits);
+}
+
+// Plan for at most 128 rows: the column-block width and over how many blocks of a cluster a
+// tile's k-blocks are shared. With so few rows the product streams w once, and the time is set
+// by how many SMs pull on it and for how long. Measured on B200 (microseconds): a block takes a
+// k-block every 0.30 to 0.38 whatever else runs (SMALL_KB_US, by width), all blocks together
+// take w in at about 4.5 MB per microsecond at best, a launch costs about 4 from its first
+// block's set-up to its last store, a launch of clusters 6.5 + 0.2 c (cluster placement, the
+// staged float32 tiles, two cluster barriers and the sum through distributed shared memory),
+// and every further wave of clusters about 6, of a persistent block's next tile about 1.
+struct SmallPlan {
+    int bn, splits;
+};
+constexpr double SMALL_KB_US[3] = {0.38, 0.31, 0.30};  // widths 256, 128, 64
+constexpr double SMALL_W_BYTES_PER_US = 4.5e6;
+
+SmallPlan small_plan(int M, int N, int K, DeviceInfo* info, bool may_split) {
+    const int kblocks = (K + BK - 1) / BK;
+    const int rows = M < BM ? M : BM;
+    int force_bn = 0, force_s = 0;
+    if (const char* f = getenv("S1_GEMM_BN")) force_bn = atoi(f);
+    if (const char* f = getenv("S1_GEMM_SPLITS")) force_s = atoi(f);
+    const int widths[3] = {256, 128, 64};
+    SmallPlan best{64, 1};
+    double best_cost = 1e30;
+    for (int i = 0; i < 3; i++) {
+        const int bn = widths[i];
+        if (force_bn && bn != force_bn) continue;
+        const long tiles = (long)((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+        const double kb_us = SMALL_KB_US[i] + 0.015 * rows / BM;
+        const double stream_us = (double)N * K * 2.0 / SMALL_W_BYTES_PER_US;
+        for (int c = 1; c <= (may_split ? 8 : 1); c++) {
+            if (force_s && c != force_s) continue;
+            const int kb_per = (kblocks + c - 1) / c;
+            long room = info->sms;
+            if (c > 1) {
+                if ((c - 1) * kb_per >= kblocks || kb_per < 4) continue;
+                room = i == 0 ? cluster_room<256>(info, 0, c) : i == 1 ? cluster_room<128>(info, 1, c) : cluster_room<64>(info, 2, c);
+                if (room <= 0) continue;
+            }
+            const long waves = (tiles + room - 1) / room;
+            const double busy = (double)waves * kb_per * kb_us;
+            const double cost = (c > 1 ? 6.5 + 0.2 * c : 4.0) + (waves - 1) * (c > 1 ? 6.0 : 1.0) + (busy > stream_us ? busy : stream_us);
+            if (cost < best_cost - 1e-9) {
+                best_cost = cost;
+                best = SmallPlan{bn, c};
+            }
+        }
+    }
+    return best;
 }
 
 // Plan for the pair kernel: the column-block width (a multiple of 32) and how the k-blocks
@@ -916,27 +1090,12 @@ int s1_gemm_tc5(const void* x, const void* w, void* y, int M, int N, int K, int 
         return launch_pair(x, w, y, M, N, K, ldy, info, scratch ? scratch->partials : nullptr,
                            scratch ? scratch->partial_bytes : 0, scratch ? scratch->counters : nullptr,
                            scratch ? scratch->counter_slots : 0, st);
-    // Pick the widest column block that still gives every SM work; a wider block moves less
-    // shared-memory traffic per flop, a narrower one fills partial waves better.
-    const int num_m = (M + BM - 1) / BM;
-    int best = 256;
-    double best_score = -1.0;
-    const int widths[3] = {256, 128, 64};
-    const double weight[3] = {1.0, 0.85, 0.6};
-    for (int i = 0; i < 3; i++) {
-        const int bn = widths[i];
-        const long tiles = (long)num_m * ((N + bn - 1) / bn);
-        const long waves = (tiles + info->sms - 1) / info->sms;
-        const double useful = (double)N / (double)(((N + bn - 1) / bn) * bn);
-        const double score = weight[i] * useful * (double)tiles / (double)(waves * info->sms);
-        if (score > best_score) {
-            best_score = score;
-            best = bn;
-        }
-    }
-    if (best == 256) return launch<256>(x, w, y, M, N, K, ldy, info, 0, st);
-    if (best == 128) return launch<128>(x, w, y, M, N, K, ldy, info, 1, st);
-    return launch<64>(x, w, y, M, N, K, ldy, info, 2, st);
+    // At most 128 rows: no scratch means the caller wants a sum over k whose order does not depend
+    // on the number of rows, so the k-blocks stay in one block.
+    const SmallPlan plan = small_plan(M, N, K, info, scratch != nullptr);
+    if (plan.bn == 256) return launch<256>(x, w, y, M, N, K, ldy, info, 0, plan.splits, st);
+    if (plan.bn == 128) return launch<128>(x, w, y, M, N, K, ldy, info, 1, plan.splits, st);
+    return launch<64>(x, w, y, M, N, K, ldy, info, 2, plan.splits, st);
 }
 
 bool s1_gemm_tc5_swiglu_supported(const void* x, const void* w, int M, int I, int K) {
@@ -948,6 +1107,15 @@ int s1_gemm_tc5_swiglu(const void* x, const void* w, void* act, int M, int I, in
     DeviceInfo* info = device_info(&err);
     if (!info) return err;
     return launch_pair_swiglu(x, w, act, M, I, K, ld, info, st);
+}
+
+// Diagnostics: how many clusters of c blocks of the single-block kernel of width bn the current
+// device holds at once (0 when that shape of launch is not possible).
+extern "C" int s1_gemm_tc5_cluster_room(int bn, int c) {
+    cudaError_t err;
+    DeviceInfo* info = device_info(&err);
+    if (!info) return 0;
+    return bn == 256 ? cluster_room<256>(info, 0, c) : bn == 128 ? cluster_room<128>(info, 1, c) : bn == 64 ? cluster_room<64>(info, 2, c) : 0;
 }
 
 // Returns the device error word of the current device (0 = no bounded wait ever gave up)

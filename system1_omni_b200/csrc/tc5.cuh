@@ -217,6 +217,21 @@ __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The shared::cluster address of cluster rank `rank`'s copy of this block's shared-memory address.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+// 16 bytes from the shared memory of any block of the cluster (distributed shared memory).
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t caddr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(caddr)
+                 : "memory");
+    return v;
+}
 // Within a cluster the shared::cluster address of rank r's copy of a shared::cta address is
 // the address with r in bits 24 and up; clearing bit 24 names the pair leader's copy.
 constexpr uint32_t PAIR_LEADER_MASK = 0xFEFFFFFFu;

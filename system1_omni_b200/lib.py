@@ -90,6 +90,7 @@ SIGNATURES = {
     "s1_gemm_cublaslt": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "s1_gemm_tcgen05": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "s1_gemm_tc5_status": (i32, [ip]),
+    "s1_gemm_tc5_cluster_room": (i32, [i32, i32]),
     "s1_gemm_unsplit": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "s1_attn_tc5_status": (i32, [ip]),
     "s1_gdn_status": (i32, [ip]),

@@ -151,7 +151,7 @@ def gemm(b, out):
     handle = lib.cs1_gemm_create(32 << 20)
     shapes = []
     for name, (h, I, gdn_in, vd, attn_in, attn_out) in MODEL_SHAPES.items():
-        for M in ((128, 1024, 4096) if name == "4B" else (1024,)):
+        for M in ((64, 128, 1024, 4096) if name == "4B" else (1024,)):
             shapes += [(name, "gdn_in_proj", M, gdn_in, h), (name, "gdn_out_proj", M, h, vd),
                        (name, "attn_qkv", M, attn_in, h), (name, "attn_o", M, h, attn_out),
                        (name, "mlp_gate_up", M, 2 * I, h), (name, "mlp_down", M, h, I)]

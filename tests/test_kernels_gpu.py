@@ -547,6 +547,32 @@ def test_gemm_shared_tile_schedules(cs1, stream, M, N, K, pad, knobs, monkeypatc
     cs1.cs1_gemm_destroy(handle)
 
 
+@pytest.mark.parametrize("M,N,K,pad", [(64, 2560, 9728, 0), (128, 2560, 4096, 0), (1, 2560, 4096, 8), (77, 1000, 2048, 3),
+                                       (128, 12352, 2560, 0), (33, 515, 1024, 0)])
+@pytest.mark.parametrize("knobs", [{}, {"S1_GEMM_SPLITS": "2", "S1_GEMM_BN": "256"}, {"S1_GEMM_SPLITS": "3", "S1_GEMM_BN": "64"},
+                                   {"S1_GEMM_SPLITS": "4"}, {"S1_GEMM_SPLITS": "5", "S1_GEMM_BN": "128"},
+                                   {"S1_GEMM_SPLITS": "8", "S1_GEMM_BN": "128"}])
+def test_gemm_few_rows_share_k_over_a_cluster(cs1, stream, M, N, K, pad, knobs, monkeypatch):
+    """Up to 128 rows: the blocks of a cluster share a tile's k-blocks and add their float32
+    tiles through distributed shared memory in rank order - as planned and with cluster sizes
+    and widths forced: the oracle's result, repeatable bit for bit, padding untouched."""
+    for k, v in knobs.items():
+        monkeypatch.setenv(k, v)
+    x, w, ldy = gemm_case(M, N, K, pad, seed=11)
+    xd, wd = dev(x, stream), dev(w, stream)
+    handle = cs1.cs1_gemm_create(32 << 20)
+    outs = []
+    for _ in range(3):
+        y = dev(np.full((M, ldy), 0x7FC0, np.uint16), stream)
+        L.check(cs1.s1_gemm_tcgen05(handle, xd.at(), wd.at(), y.at(), M, N, K, ldy, stream.handle), "gemm")
+        outs.append(host(y, (M, ldy), stream))
+    assert L.gemm_status() == 0
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+    check_gemm(outs[0], x, w, N)
+    assert np.all(outs[0][:, N:] == 0x7FC0)
+    cs1.cs1_gemm_destroy(handle)
+
+
 @pytest.mark.parametrize("M,I,K,pad", [(1024, 9728, 2560, 0), (300, 1000, 512, 8), (129, 96, 64, 0), (700, 17408, 1024, 0),
                                        (257, 40, 128, 3)])
 def test_gemm_swiglu_equals_the_two_operators(cs1, stream, M, I, K, pad):
