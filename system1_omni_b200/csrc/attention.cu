@@ -29,6 +29,7 @@ __global__ void __launch_bounds__(256)
                      const bf16* __restrict__ kw, const bf16* __restrict__ cos_t, const bf16* __restrict__ sin_t,
                      bf16* __restrict__ q, bf16* __restrict__ gate, bf16* __restrict__ k, long long total, int Hq,
                      int Hk, int half, float eps) {
+    grid_dep_trigger();
     grid_dep_sync();
     constexpr int LANES = DH / 8;
     const int sub = threadIdx.x % LANES;

@@ -236,6 +236,7 @@ __global__ void __launch_bounds__(ATHREADS, 1)
     using namespace tc5;
     using G = ACfg<DH>;
     constexpr int BN = G::BN;
+    grid_dep_trigger();
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);
@@ -417,9 +418,8 @@ int launch_attn(const AttnMaps& maps, const bf16* gate, bf16* out, int T, int Hq
     constexpr float LOG2E = 1.4426950408889634f;
     const dim3 grid((T - q_base + ABM - 1) / ABM, Hq);
     const int vec_ok = aligned16(out) && (!GATED || aligned16(gate));
-    attn_tc5_kernel<DH, GATED, CAUSAL><<<grid, ATHREADS, G::SMEM, st>>>(maps, gate, out, T, Hq, Hk, scale * LOG2E, q_base, own_base,
-                                                               vec_ok);
-    return cudaGetLastError();
+    return launch_dep(attn_tc5_kernel<DH, GATED, CAUSAL>, grid, ATHREADS, G::SMEM, st, maps, gate, out, T, Hq, Hk, scale * LOG2E,
+                      q_base, own_base, vec_ok);
 }
 
 }  // namespace

@@ -5,6 +5,9 @@
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+
+#include <mutex>
+#include <unordered_set>
 #include <stdint.h>
 
 namespace s1 {
@@ -87,29 +90,57 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 
-// ---- programmatic dependent launch (opt-in: S1_PDL=1) ----
-// A kernel launched with launch_dep is queued as a programmatic dependent of the kernel before it on
-// the stream: it may start as soon as that kernel's blocks have exited, without waiting for the
-// flush of its writes, and calls grid_dep_sync() before it touches anything that kernel wrote (or
-// still reads). Every kernel on the hot path calls it before its first global access, after
-// whatever setup it has (barriers, tensor memory), so the order of all memory effects is that of
-// ordinary stream order. Measured on the benchmark step: +0.5 to 1 % with this, and -2 % when the
-// kernels also let their dependents become resident early (griddepcontrol.launch_dependents: the
-// waiting blocks take issue slots and shared memory from the running kernel), so that is not
-// done and the whole mechanism stays off by default. grid_dep_sync() is a no-op in a kernel
-// launched the ordinary way.
+// ---- programmatic dependent launch ----
+// A kernel launched with launch_dep while the switch is on is queued as a programmatic dependent
+// of the kernel before it on the stream: its blocks may become resident as soon as every block of
+// that kernel has called grid_dep_trigger() (the first thing each hot-path kernel does) or has
+// exited, and it calls grid_dep_sync() before it touches anything that kernel wrote or still
+// reads. What a kernel does before grid_dep_sync() - barriers, tensor memory, descriptor
+// prefetch, and in the GEMMs the first stages of weight tiles, which no kernel of a forward pass
+// writes - overlaps the kernels before it; the order of all other memory effects is that of
+// ordinary stream order, since grid_dep_sync() returns only when the kernel before is complete
+// and its writes are visible, and that kernel in turn waited for the one before it.
+// The switch is per host thread: the executor turns it on for short prompts, where launch gaps,
+// prologues and the first trip to HBM are a large part of every kernel, and off for long ones
+// (measured at 1024 tokens: resident blocks that only wait take issue slots and shared memory from
+// the running kernel, 2 % slower). S1_PDL=1 / S1_PDL=0 in the environment force it on / off.
+// Both instructions are no-ops in a kernel launched the ordinary way.
 __device__ __forceinline__ void grid_dep_sync() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline int& dep_launch_switch() {
+    static thread_local int on = 0;
+    return on;
+}
 
 inline bool dep_launch_enabled() {
-    static const bool on = [] {
+    static const int forced = [] {
         const char* v = getenv("S1_PDL");
-        return v && v[0] == '1';  // off unless asked for
+        return !v ? -1 : (v[0] == '1' ? 1 : 0);
     }();
-    return on;
+    return forced >= 0 ? forced == 1 : dep_launch_switch() != 0;
+}
+
+// An SM changes its split between L1 and shared memory only when it is empty, so a block that
+// needs most of the shared memory (the GEMMs, attention, the delta-rule kernels) cannot join
+// blocks that were placed under a small shared-memory split. Every kernel launched through
+// launch_dep therefore asks for the largest shared-memory split once (none of them relies on L1:
+// their loads are streaming or staged by hand), and the SMs keep one configuration from the first
+// kernel of a pass to the last.
+inline void prefer_max_shared(const void* kernel) {
+    static std::mutex lock;
+    static std::unordered_set<const void*> done[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return;
+    std::lock_guard<std::mutex> hold(lock);
+    if (done[dev].insert(kernel).second)
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
+            cudaGetLastError();  // a hint: nothing depends on it
 }
 
 template <typename... KArgs, typename... Args>
 cudaError_t launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    prefer_max_shared(reinterpret_cast<const void*>(kernel));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;

@@ -18,6 +18,8 @@ inline unsigned blocks_for(size_t n, int per = THREADS) { return (unsigned)((n +
 // ---- embedding ----
 __global__ void __launch_bounds__(128) embed_kernel(const int32_t* __restrict__ ids, const uint4* __restrict__ table,
                                                     uint4* __restrict__ out, int packs) {
+    grid_dep_trigger();
+    grid_dep_sync();
     const size_t t = blockIdx.x;
     const size_t id = (size_t)ids[t];
     const uint4* src = table + id * packs;
@@ -35,6 +37,7 @@ constexpr int CONV_THREADS = 128;
 __global__ void __launch_bounds__(CONV_THREADS)
     gdn_conv_packed_kernel(const bf16* __restrict__ qkv, int ld, const bf16* __restrict__ w, bf16* __restrict__ q,
                            bf16* __restrict__ k, bf16* __restrict__ v, int T, int key_dim, int value_dim) {
+    grid_dep_trigger();
     grid_dep_sync();
     const int packs = (2 * key_dim + value_dim) / 8;
     const int p = blockIdx.y * CONV_THREADS + threadIdx.x;
@@ -127,6 +130,7 @@ __global__ void gdn_conv_scalar_kernel(const bf16* __restrict__ qkv, int ld, con
 __global__ void gdn_gates_kernel(const bf16* __restrict__ b, const bf16* __restrict__ a, int ld,
                                  const bf16* __restrict__ A_log, const bf16* __restrict__ dt_bias,
                                  bf16* __restrict__ beta, float* __restrict__ g, int n, int H) {
+    grid_dep_trigger();
     grid_dep_sync();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
@@ -146,6 +150,8 @@ __global__ void sigmoid_gate_kernel(bf16* __restrict__ x, const bf16* __restrict
 }
 
 __global__ void sigmoid_gate_packed_kernel(uint4* __restrict__ x, const uint4* __restrict__ gate, size_t packs) {
+    grid_dep_trigger();
+    grid_dep_sync();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= packs) return;
     float xv[8], gv[8];
@@ -168,6 +174,8 @@ __global__ void silu_mul_kernel(const bf16* __restrict__ gate_up, int ld, bf16* 
 // Two packs per thread keep more loads in flight per warp.
 __global__ void __launch_bounds__(THREADS)
     silu_mul_packed_kernel(const uint4* __restrict__ gate_up, int ld, uint4* __restrict__ out, int I, size_t n) {
+    grid_dep_trigger();
+    grid_dep_sync();
     const size_t base = ((size_t)blockIdx.x * blockDim.x) * 2 + threadIdx.x;
     uint4 g[2], u[2];
     size_t idx[2];
@@ -203,8 +211,8 @@ extern "C" int cs1_embed(const int32_t* ids, const void* table, void* out, int T
     if (D % 8 != 0 || D <= 0) return cudaErrorInvalidValue;
     if (T <= 0) return cudaSuccess;
     if (!aligned16(table) || !aligned16(out)) return cudaErrorInvalidValue;
-    embed_kernel<<<T, 128, 0, as_stream(stream)>>>(ids, static_cast<const uint4*>(table), static_cast<uint4*>(out),
-                                                   D / 8);
+    launch_dep(embed_kernel, T, 128, 0, as_stream(stream), ids, static_cast<const uint4*>(table), static_cast<uint4*>(out),
+               D / 8);
     return cudaGetLastError();
 }
 
@@ -244,8 +252,8 @@ extern "C" int cs1_gdn_gates(const void* b, const void* a, int ld, const void* A
 extern "C" int cs1_sigmoid_gate(void* x, const void* gate, size_t n, void* stream) {
     if (n == 0) return cudaSuccess;
     if (n % 8 == 0 && aligned16(x) && aligned16(gate)) {
-        sigmoid_gate_packed_kernel<<<blocks_for(n / 8), THREADS, 0, as_stream(stream)>>>(
-            static_cast<uint4*>(x), static_cast<const uint4*>(gate), n / 8);
+        launch_dep(sigmoid_gate_packed_kernel, blocks_for(n / 8), THREADS, 0, as_stream(stream), static_cast<uint4*>(x),
+                   static_cast<const uint4*>(gate), n / 8);
     } else {
         sigmoid_gate_kernel<<<blocks_for(n), THREADS, 0, as_stream(stream)>>>(static_cast<bf16*>(x),
                                                                              static_cast<const bf16*>(gate), n);
@@ -258,8 +266,8 @@ extern "C" int cs1_silu_mul(const void* gate_up, int ld, void* out, int T, int I
     const size_t n = (size_t)T * I;
     if (n == 0) return cudaSuccess;
     if (I % 8 == 0 && ld % 8 == 0 && aligned16(gate_up) && aligned16(out)) {
-        silu_mul_packed_kernel<<<blocks_for(n / 8, 2 * THREADS), THREADS, 0, as_stream(stream)>>>(
-            static_cast<const uint4*>(gate_up), ld / 8, static_cast<uint4*>(out), I / 8, n / 8);
+        launch_dep(silu_mul_packed_kernel, blocks_for(n / 8, 2 * THREADS), THREADS, 0, as_stream(stream),
+                   static_cast<const uint4*>(gate_up), ld / 8, static_cast<uint4*>(out), I / 8, n / 8);
     } else {
         silu_mul_kernel<<<blocks_for(n), THREADS, 0, as_stream(stream)>>>(static_cast<const bf16*>(gate_up), ld,
                                                                          static_cast<bf16*>(out), I, n);

@@ -476,6 +476,7 @@ __global__ void __launch_bounds__(PREP2_THREADS, 1)
                  const float* __restrict__ g, const bf16* __restrict__ beta, Work ws, int T, int H, int HK, int NC,
                  float scale) {
     using namespace tc5;
+    grid_dep_trigger();
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     float* A = reinterpret_cast<float*>(smem + T_A);
@@ -880,6 +881,7 @@ template <int VS, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 2)
     gdn_scan(Work ws, bf16* __restrict__ o, int T, int H, int NC, const float* __restrict__ s_in,
              float* __restrict__ s_out) {
+    grid_dep_trigger();
     using L = ScanSmem<VS>;
     constexpr int LDV = L::LDV;
     constexpr int NT = VS / 8;               // 8-column tiles across the slice

@@ -58,6 +58,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     bf16* __restrict__ y, int M, int N, int K, int ldy, int vec_ok, int splits) {
     using namespace tc5;
     using G = Cfg<BN>;
+    grid_dep_trigger();
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + G::STAGES * G::STAGE);
@@ -90,7 +91,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    grid_dep_sync();  // barriers, tensor memory and descriptors are ready; x may still be in the making
 
     const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN;
     const int tiles = num_m * num_n, kblocks = (K + BK - 1) / BK;
@@ -112,18 +112,32 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            // The first ring-full of w tiles goes out before this kernel waits for the one ahead of
+            // it on the stream: weights are written by no kernel of a forward pass, x may still be
+            // in the making. (The stages are fresh, so there is nothing to wait for on `empty`.)
+            int ahead = 0;
+            if (first < tiles) {
+                ahead = min(kb1 - kb0, G::STAGES);
+                for (int i = 0; i < ahead; i++) {
+                    mbar_expect_tx(&full[i], G::STAGE);
+                    tma_load_2d(smem + i * G::STAGE + G::A_BYTES, &tma_w, (kb0 + i) * BK, (first / num_m) * BN, &full[i]);
+                }
+            }
+            grid_dep_sync();
             for (int tile = first; ok && tile < tiles; tile += step) {
                 const int m_idx = tile % num_m, n_idx = tile / num_m;
                 for (int kb = kb0; kb < kb1; kb++) {
-                    if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
-                        fail(1);
-                        ok = false;
-                        break;
-                    }
                     unsigned char* dst = smem + stage * G::STAGE;
-                    mbar_expect_tx(&full[stage], G::STAGE);
+                    if (tile != first || kb - kb0 >= ahead) {
+                        if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+                            fail(1);
+                            ok = false;
+                            break;
+                        }
+                        mbar_expect_tx(&full[stage], G::STAGE);
+                        tma_load_2d(dst + G::A_BYTES, &tma_w, kb * BK, n_idx * BN, &full[stage]);
+                    }
                     tma_load_2d(dst, &tma_x, kb * BK, m_idx * BM, &full[stage]);
-                    tma_load_2d(dst + G::A_BYTES, &tma_w, kb * BK, n_idx * BN, &full[stage]);
                     if (++stage == G::STAGES) {
                         stage = 0;
                         phase ^= 1;
@@ -170,6 +184,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
         __syncwarp();
     } else {
+        grid_dep_sync();  // these warps store y, which the kernel ahead may still read
         const int quarter = warp & 3;  // tensor-memory lanes [32 quarter, 32 quarter + 32) belong to this warp
         uint32_t it = 0;
         for (int tile = first; tile < tiles; tile += step, it++) {
@@ -371,6 +386,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                          bf16* __restrict__ y, int M, int N, int K, int ldy, int vec_ok, int BN, int splits, int mode,
                          float* __restrict__ partials, int* __restrict__ counters, int swiglu) {
     using namespace tc5;
+    grid_dep_trigger();
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + PAIR_DATA_BYTES);  // used in the leader only
@@ -406,7 +422,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     cluster_sync();  // both blocks' barriers exist before anything arrives on them
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    grid_dep_sync();  // the prologue above ran under the previous kernel's tail
 
     // swiglu: w is [gate (N rows) | up (N rows)]; a tile pairs BN / 2 gate columns (loaded by the
     // pair's first block) with the same BN / 2 up columns (second block), so both land in one
@@ -431,21 +446,38 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            while (ok && pieces.next(pc)) {
+            // As in the single-block kernel: this block's w tiles of the first ring-full of stages go
+            // out before the wait for the kernel ahead on the stream; x follows after it.
+            bool more = pieces.next(pc);
+            int ahead = 0;
+            if (more) {
+                int m_idx, n_idx;
+                pair_tile_coords(pc.tile, num_m, num_n, m_idx, n_idx);
+                const int n0 = swiglu ? n_idx * half_n + (int)rank * N : n_idx * BN + (int)rank * half_n;
+                ahead = min(pc.kb1 - pc.kb0, (int)nstages);
+                for (int i = 0; i < ahead; i++) {
+                    if (leader) mbar_expect_tx(&full[i], 2 * stage_bytes);  // both blocks' bytes land on it
+                    tma_load_2d_pair(smem + i * stage_bytes + PAIR_A_BYTES, &tma_w, (pc.kb0 + i) * BK, n0, &full[i]);
+                }
+            }
+            grid_dep_sync();
+            for (bool first_piece = true; ok && more; first_piece = false, more = pieces.next(pc)) {
                 int m_idx, n_idx;
                 pair_tile_coords(pc.tile, num_m, num_n, m_idx, n_idx);
                 const int m0 = m_idx * 2 * BM + (int)rank * BM;
                 const int n0 = swiglu ? n_idx * half_n + (int)rank * N : n_idx * BN + (int)rank * half_n;
                 for (int kb = pc.kb0; kb < pc.kb1; kb++) {
-                    if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
-                        fail(11);
-                        ok = false;
-                        break;
-                    }
                     unsigned char* dst = smem + stage * stage_bytes;
-                    if (leader) mbar_expect_tx(&full[stage], 2 * stage_bytes);  // both blocks' bytes land on it
+                    if (!first_piece || kb - pc.kb0 >= ahead) {
+                        if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+                            fail(11);
+                            ok = false;
+                            break;
+                        }
+                        if (leader) mbar_expect_tx(&full[stage], 2 * stage_bytes);
+                        tma_load_2d_pair(dst + PAIR_A_BYTES, &tma_w, kb * BK, n0, &full[stage]);
+                    }
                     tma_load_2d_pair(dst, &tma_x, kb * BK, m0, &full[stage]);
-                    tma_load_2d_pair(dst + PAIR_A_BYTES, &tma_w, kb * BK, n0, &full[stage]);
                     if (++stage == nstages) {
                         stage = 0;
                         phase ^= 1;
@@ -493,6 +525,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
         }
         __syncwarp();
     } else {
+        grid_dep_sync();  // these warps store y and use the scratch of shared tiles, which the kernel ahead may still use
         const int quarter = warp & 3;
         uint32_t it = 0;
         int* last_flag = const_cast<int*>(abort_flag) + 1;  // shared word next to the abort flag

@@ -30,6 +30,7 @@ __global__ void fill_kernel(bf16* out, size_t n, uint64_t seed, float mean, floa
 
 __global__ void gather_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ ends, uint4* __restrict__ out,
                                    int packs) {
+    grid_dep_trigger();
     grid_dep_sync();
     const size_t src = (size_t)(ends[blockIdx.x] - 1) * packs;
     const size_t dst = (size_t)blockIdx.x * packs;

@@ -19,6 +19,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
     rms_norm_packed_kernel(bf16* __restrict__ residual, const bf16* __restrict__ delta, const bf16* __restrict__ w,
                            bf16* __restrict__ out, int D, float eps) {
     __shared__ float scratch[32];
+    grid_dep_trigger();
     grid_dep_sync();
     const size_t row = (size_t)blockIdx.x * D;
     const int packs = D / 8;
@@ -114,6 +115,7 @@ __global__ void __launch_bounds__(GN_GROUPS * 16)
     gated_rms_norm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ z, int ldz, const bf16* __restrict__ w,
                           bf16* __restrict__ out, int rows, int H, float eps) {
     constexpr int D = 128;
+    grid_dep_trigger();
     grid_dep_sync();
     const int group = threadIdx.x / 16, sub = threadIdx.x & 15;
     uint4 xv[GN_ROWS_PER_GROUP], zv[GN_ROWS_PER_GROUP];

@@ -101,6 +101,8 @@ SIGNATURES = {
     "s1_model_unfilled": (i32, [vp, C.c_char_p, C.c_size_t]),
     "s1_gemm_swiglu": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "s1_model_set_exact_packing": (i32, [vp, i32]),
+    "s1_model_set_overlap_tokens": (i32, [vp, i32]),
+    "s1_set_dependent_launch": (i32, [i32]),
     "s1_model_set_fused_mlp": (i32, [vp, i32]),
     "s1_attention_gated_shared_prefix": (i32, [vp, vp, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp]),
     "s1_prefix_create": (i32, [vp, i32, vp]),

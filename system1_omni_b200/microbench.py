@@ -359,18 +359,27 @@ def latency(b, out):
     for T in (64, 128, 256, 512, 1024, 2048, 4096, 8192, 16384):
         ids = L.to_device(rng.integers(0, cfg.vocab, T).astype(np.int32), b.stream)
         lengths = np.array([T], np.int32)
-        for _ in range(3):
-            model.forward_device(ids.at(), lengths)
-        model.synchronize()
-        n = 10 if T <= 4096 else 3
-        e0.record(stream)
-        for _ in range(n):
-            model.forward_device(ids.at(), lengths)
-        e1.record(stream)
-        model.synchronize()
-        ms = e0.elapsed_ms(e1) / n
-        out({"op": "prefill_latency", "model": "4B-shaped", "tokens": T, "ms": ms, "tokens_per_s": T / ms * 1e3,
-             "weights_once_through_hbm_ms": floor_ms})
+        row = {"op": "prefill_latency", "model": "4B-shaped", "tokens": T}
+        # graph replay and eager issue with the executor's defaults, and eager issue in plain stream
+        # order (no kernel launched as a programmatic dependent of the one before)
+        for key, graphs, limit in (("ms", True, 512), ("ms_eager", False, 512), ("ms_eager_stream_order", False, 0)):
+            if T > 2048 and key != "ms":
+                continue
+            model.enable_graphs(graphs)
+            model.set_overlap_tokens(limit)
+            for _ in range(3):
+                model.forward_device(ids.at(), lengths)
+            model.synchronize()
+            n = 10 if T <= 4096 else 3
+            e0.record(stream)
+            for _ in range(n):
+                model.forward_device(ids.at(), lengths)
+            e1.record(stream)
+            model.synchronize()
+            row[key] = e0.elapsed_ms(e1) / n
+        model.set_overlap_tokens(512)
+        row.update({"tokens_per_s": T / row["ms"] * 1e3, "weights_once_through_hbm_ms": floor_ms})
+        out(row)
     model.close()
 
 

@@ -226,6 +226,10 @@ class Model:
         """Bit-identical results for a prompt alone or in a pack (slower); see s1_executor.h."""
         L.check(L.load().s1_model_set_exact_packing(self.handle, int(on)), "exact packing")
 
+    def set_overlap_tokens(self, tokens):
+        """Passes of at most `tokens` tokens launch their kernels as programmatic dependents of one another."""
+        L.check(L.load().s1_model_set_overlap_tokens(self.handle, int(tokens)), "overlap tokens")
+
     def set_fused_mlp(self, on=True):
         """Gate/up projection + SiLU-multiply as one kernel (default) or as the two operators."""
         L.check(L.load().s1_model_set_fused_mlp(self.handle, int(on)), "fused mlp")
