@@ -51,6 +51,13 @@ int s1_attention_gated_shared_prefix(const void* q, const void* k, const void* v
  * gdn_prefill.cu:170-203): out = bf16(x * rsqrt(sum x^2 + 1e-6) * scale) over `rows` rows of 128 bf16;
  * for the elementwise benchmark sweep and for checks. x and out 16-byte aligned. */
 int s1_l2norm_heads(const void* x, void* out, long long rows, float scale, void* stream);
+/* cs1_gdn_conv and cs1_gdn_gates of the same T rows (of pitch ld) in one launch: b and a point at
+ * the two gate columns of the first row, as in cs1_gdn_gates. The same bits as the two operators
+ * (the reference runs them one after the other, model.rs:640-668). CS1_ERR_UNSUPPORTED where
+ * cs1_gdn_conv would take its scalar path (widths not multiples of 8, unaligned): run the two. */
+int s1_gdn_conv_gates(const void* qkv, int ld, const void* w, void* q, void* k, void* v, int T, int key_dim,
+                      int value_dim, const void* b, const void* a, const void* A_log, const void* dt_bias, void* beta,
+                      float* g, int H, void* stream);
 
 /* The attention kernel's counterpart of s1_gemm_tc5_status: its device error word (0 = no bounded
  * wait ever gave up), read after waiting for all queued work, then cleared. */
@@ -117,8 +124,10 @@ int s1_model_enable_graphs(void* model, int on);
  * planner may share K by the row count: faster on a few shapes, and equal to single execution
  * within rounding (the reference's gate is 0.01 on the logits). */
 int s1_model_set_exact_packing(void* model, int on);
-/* The MLP's gate/up projection and SiLU-multiply as one kernel (s1_gemm_swiglu; on by default,
- * same bits as the two operators). Off: always the reference's two-operator sequence. */
+/* The executor's fused kernels, on by default, each with the same bits as the operators it
+ * replaces: the MLP's gate/up projection and SiLU-multiply as one kernel (s1_gemm_swiglu), and the
+ * convolution and the gates of a GDN layer as one launch (s1_gdn_conv_gates). Off: always the
+ * reference's operator sequence. */
 int s1_model_set_fused_mlp(void* model, int on);
 /* Forward passes of at most `tokens` tokens launch their kernels as programmatic dependents of one
  * another (s1_set_dependent_launch); longer ones launch in plain stream order. Default 512

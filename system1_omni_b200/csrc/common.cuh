@@ -5,9 +5,6 @@
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
-
-#include <mutex>
-#include <unordered_set>
 #include <stdint.h>
 
 namespace s1 {
@@ -121,26 +118,8 @@ inline bool dep_launch_enabled() {
     return forced >= 0 ? forced == 1 : dep_launch_switch() != 0;
 }
 
-// An SM changes its split between L1 and shared memory only when it is empty, so a block that
-// needs most of the shared memory (the GEMMs, attention, the delta-rule kernels) cannot join
-// blocks that were placed under a small shared-memory split. Every kernel launched through
-// launch_dep therefore asks for the largest shared-memory split once (none of them relies on L1:
-// their loads are streaming or staged by hand), and the SMs keep one configuration from the first
-// kernel of a pass to the last.
-inline void prefer_max_shared(const void* kernel) {
-    static std::mutex lock;
-    static std::unordered_set<const void*> done[64];
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return;
-    std::lock_guard<std::mutex> hold(lock);
-    if (done[dev].insert(kernel).second)
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
-            cudaGetLastError();  // a hint: nothing depends on it
-}
-
 template <typename... KArgs, typename... Args>
 cudaError_t launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
-    prefer_max_shared(reinterpret_cast<const void*>(kernel));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;

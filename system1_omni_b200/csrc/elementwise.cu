@@ -34,11 +34,9 @@ __global__ void __launch_bounds__(128) embed_kernel(const int32_t* __restrict__ 
 constexpr int CONV_TT = 16;
 constexpr int CONV_THREADS = 128;
 
-__global__ void __launch_bounds__(CONV_THREADS)
-    gdn_conv_packed_kernel(const bf16* __restrict__ qkv, int ld, const bf16* __restrict__ w, bf16* __restrict__ q,
-                           bf16* __restrict__ k, bf16* __restrict__ v, int T, int key_dim, int value_dim) {
-    grid_dep_trigger();
-    grid_dep_sync();
+__device__ __forceinline__ void conv_block(const bf16* __restrict__ qkv, int ld, const bf16* __restrict__ w,
+                                           bf16* __restrict__ q, bf16* __restrict__ k, bf16* __restrict__ v, int T,
+                                           int key_dim, int value_dim) {
     const int packs = (2 * key_dim + value_dim) / 8;
     const int p = blockIdx.y * CONV_THREADS + threadIdx.x;
     if (p >= packs) return;
@@ -104,6 +102,14 @@ __global__ void __launch_bounds__(CONV_THREADS)
     }
 }
 
+__global__ void __launch_bounds__(CONV_THREADS)
+    gdn_conv_packed_kernel(const bf16* __restrict__ qkv, int ld, const bf16* __restrict__ w, bf16* __restrict__ q,
+                           bf16* __restrict__ k, bf16* __restrict__ v, int T, int key_dim, int value_dim) {
+    grid_dep_trigger();
+    grid_dep_sync();
+    conv_block(qkv, ld, w, q, k, v, T, key_dim, value_dim);
+}
+
 __global__ void gdn_conv_scalar_kernel(const bf16* __restrict__ qkv, int ld, const bf16* __restrict__ w,
                                        bf16* __restrict__ q, bf16* __restrict__ k, bf16* __restrict__ v, int T,
                                        int key_dim, int value_dim) {
@@ -127,6 +133,17 @@ __global__ void gdn_conv_scalar_kernel(const bf16* __restrict__ qkv, int ld, con
 }
 
 // ---- gates ----
+__device__ __forceinline__ void gate_element(const bf16* __restrict__ b, const bf16* __restrict__ a, int ld,
+                                             const bf16* __restrict__ A_log, const bf16* __restrict__ dt_bias,
+                                             bf16* __restrict__ beta, float* __restrict__ g, int i, int H) {
+    const int h = i % H;
+    const size_t src = (size_t)(i / H) * ld + h;
+    beta[i] = to_bf16(sigmoid(f32(b[src])));
+    const float x = f32(a[src]) + f32(dt_bias[h]);
+    const float sp = x > 20.f ? x : log1pf(expf(x));
+    g[i] = -expf(f32(A_log[h])) * sp;
+}
+
 __global__ void gdn_gates_kernel(const bf16* __restrict__ b, const bf16* __restrict__ a, int ld,
                                  const bf16* __restrict__ A_log, const bf16* __restrict__ dt_bias,
                                  bf16* __restrict__ beta, float* __restrict__ g, int n, int H) {
@@ -134,12 +151,27 @@ __global__ void gdn_gates_kernel(const bf16* __restrict__ b, const bf16* __restr
     grid_dep_sync();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const int h = i % H;
-    const size_t src = (size_t)(i / H) * ld + h;
-    beta[i] = to_bf16(sigmoid(f32(b[src])));
-    const float x = f32(a[src]) + f32(dt_bias[h]);
-    const float sp = x > 20.f ? x : log1pf(expf(x));
-    g[i] = -expf(f32(A_log[h])) * sp;
+    gate_element(b, a, ld, A_log, dt_bias, beta, g, i, H);
+}
+
+// The convolution and the gates of one token range in one launch: both read the rows the input
+// projection wrote. Blocks with blockIdx.y below conv_blocks are convolution blocks, the row of
+// blocks after them computes the gates of the same CONV_TT tokens. Same arithmetic per element as
+// the two kernels above.
+__global__ void __launch_bounds__(CONV_THREADS)
+    gdn_conv_gates_kernel(const bf16* __restrict__ qkv, int ld, const bf16* __restrict__ w, bf16* __restrict__ q,
+                          bf16* __restrict__ k, bf16* __restrict__ v, int T, int key_dim, int value_dim, int conv_blocks,
+                          const bf16* __restrict__ b, const bf16* __restrict__ a, const bf16* __restrict__ A_log,
+                          const bf16* __restrict__ dt_bias, bf16* __restrict__ beta, float* __restrict__ g, int H) {
+    grid_dep_trigger();
+    grid_dep_sync();
+    if ((int)blockIdx.y < conv_blocks) {
+        conv_block(qkv, ld, w, q, k, v, T, key_dim, value_dim);
+        return;
+    }
+    const int first = blockIdx.x * CONV_TT * H;
+    const int end = min((int)(blockIdx.x + 1) * CONV_TT, T) * H;
+    for (int i = first + (int)threadIdx.x; i < end; i += CONV_THREADS) gate_element(b, a, ld, A_log, dt_bias, beta, g, i, H);
 }
 
 // ---- x * sigmoid(gate) ----
@@ -246,6 +278,24 @@ extern "C" int cs1_gdn_gates(const void* b, const void* a, int ld, const void* A
     launch_dep(gdn_gates_kernel, blocks_for((size_t)n), THREADS, 0, as_stream(stream), static_cast<const bf16*>(b),
                static_cast<const bf16*>(a), ld, static_cast<const bf16*>(A_log), static_cast<const bf16*>(dt_bias),
                static_cast<bf16*>(beta), g, (int)n, H);
+    return cudaGetLastError();
+}
+
+extern "C" int s1_gdn_conv_gates(const void* qkv, int ld, const void* w, void* q, void* k, void* v, int T, int key_dim,
+                                 int value_dim, const void* b, const void* a, const void* A_log, const void* dt_bias,
+                                 void* beta, float* g, int H, void* stream) {
+    if (T < 0 || key_dim < 0 || value_dim < 0 || H < 0 || ld < 2 * key_dim + value_dim || ld < H) return cudaErrorInvalidValue;
+    const int channels = 2 * key_dim + value_dim;
+    if (T == 0) return cudaSuccess;
+    const bool packed = key_dim % 8 == 0 && value_dim % 8 == 0 && ld % 8 == 0 && aligned16(qkv) && aligned16(w) &&
+                        aligned16(q) && aligned16(k) && aligned16(v);
+    if (!packed || channels == 0 || H == 0 || (long long)T * H > 0x7fffffffLL) return CS1_ERR_UNSUPPORTED;
+    const int conv_blocks = (channels / 8 + CONV_THREADS - 1) / CONV_THREADS;
+    const dim3 grid((T + CONV_TT - 1) / CONV_TT, conv_blocks + 1);
+    launch_dep(gdn_conv_gates_kernel, grid, CONV_THREADS, 0, as_stream(stream), static_cast<const bf16*>(qkv), ld,
+               static_cast<const bf16*>(w), static_cast<bf16*>(q), static_cast<bf16*>(k), static_cast<bf16*>(v), T, key_dim,
+               value_dim, conv_blocks, static_cast<const bf16*>(b), static_cast<const bf16*>(a),
+               static_cast<const bf16*>(A_log), static_cast<const bf16*>(dt_bias), static_cast<bf16*>(beta), g, H);
     return cudaGetLastError();
 }
 

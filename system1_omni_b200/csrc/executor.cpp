@@ -367,6 +367,36 @@ int mlp_block(Model* m, size_t li, const int* lengths, int nseq, int t) {
     return 0;
 }
 
+// Convolution and gates of rows [off, off + len) of the input projection's output: one launch
+// where the fused kernel takes the shapes (same bits), else the reference's two operators.
+int conv_gates(Model* m, const Layer& ly, size_t off, int len) {
+    const Scratch& s = m->s;
+    void* st = m->stream;
+    const int kd = m->key_dim(), vd = m->value_dim(), hv = m->cfg.lin_v_heads, gdn_in = m->gdn_in_w(), conv = m->conv_w();
+    const size_t row = s.gdn_in + off * gdn_in * BF16;
+    const size_t b = row + (size_t)(conv + vd) * BF16, a = b + (size_t)hv * BF16;
+    float* g = reinterpret_cast<float*>(s.at(s.g + off * hv * F32));
+    int fused = CS1_ERR_UNSUPPORTED;
+    if (m->fuse_swiglu) {
+        S1_TRY(op(m, S1_FAMILY_CONV, 0, [&] {
+            fused = s1_gdn_conv_gates(s.at(row), gdn_in, m->w(ly.conv), s.at(s.lq + off * kd * BF16),
+                                      s.at(s.lk + off * kd * BF16), s.at(s.lv + off * vd * BF16), len, kd, vd, s.at(b),
+                                      s.at(a), m->w(ly.a_log), m->w(ly.dt_bias), s.at(s.beta + off * hv * BF16), g, hv, st);
+            return fused == CS1_ERR_UNSUPPORTED ? 0 : fused;
+        }));
+        if (fused == 0) m->launches[S1_FAMILY_CONV] += 1;
+    }
+    if (fused == CS1_ERR_UNSUPPORTED) {
+        S1_OP(S1_FAMILY_CONV, 1,
+              cs1_gdn_conv(s.at(row), gdn_in, m->w(ly.conv), s.at(s.lq + off * kd * BF16), s.at(s.lk + off * kd * BF16),
+                           s.at(s.lv + off * vd * BF16), len, kd, vd, st));
+        S1_OP(S1_FAMILY_GATES, 1,
+              cs1_gdn_gates(s.at(b), s.at(a), gdn_in, m->w(ly.a_log), m->w(ly.dt_bias), s.at(s.beta + off * hv * BF16), g,
+                            len, hv, st));
+    }
+    return 0;
+}
+
 // The layer loop (model.rs:1119-1338). Pointwise operators and the input / gate-up GEMMs run
 // once over the packed rows; conv, delta rule, attention prep and attention run per sequence.
 // dump (nullable, host) receives the residual stream after each layer.
@@ -399,19 +429,11 @@ int run(Model* m, const int* lengths, int nseq, char* dump) {
         if (!ly.full) {
             S1_TRY(gemm(m, s.x, ly.in_proj, s.gdn_in, t, gdn_in, h));
             const size_t z = s.gdn_in + (size_t)conv * BF16;
-            const size_t b = z + (size_t)vd * BF16;
-            const size_t a = b + (size_t)hv * BF16;
             size_t off = 0;
             for (int q = 0; q < nseq; q++) {
-                S1_OP(S1_FAMILY_CONV, 1,
-                      cs1_gdn_conv(s.at(s.gdn_in + off * gdn_in * BF16), gdn_in, m->w(ly.conv),
-                                   s.at(s.lq + off * kd * BF16), s.at(s.lk + off * kd * BF16),
-                                   s.at(s.lv + off * vd * BF16), lengths[q], kd, vd, st));
+                S1_TRY(conv_gates(m, ly, off, lengths[q]));
                 off += lengths[q];
             }
-            S1_OP(S1_FAMILY_GATES, 1,
-                  cs1_gdn_gates(s.at(b), s.at(a), gdn_in, m->w(ly.a_log), m->w(ly.dt_bias), s.at(s.beta),
-                                reinterpret_cast<float*>(s.at(s.g)), t, hv, st));
             off = 0;
             for (int q = 0; q < nseq; q++) {
                 S1_OP(S1_FAMILY_GDN, 2,
@@ -504,8 +526,6 @@ int run_window(Model* m, const int* lengths, int nseq, Prefix* capture, const Pr
         if (!ly.full) {
             S1_TRY(gemm(m, s.x, ly.in_proj, s.gdn_in, t, gdn_in, h));
             const size_t z = s.gdn_in + (size_t)conv * BF16;
-            const size_t b = z + (size_t)vd * BF16;
-            const size_t a = b + (size_t)hv * BF16;
             if (capture)
                 S1_TRY(cs1_copy_dd(capture->tail[la], s.at(s.gdn_in + (size_t)(t - TAIL_ROWS) * gdn_in * BF16), tail_bytes,
                                    st));
@@ -515,11 +535,7 @@ int run_window(Model* m, const int* lengths, int nseq, Prefix* capture, const Pr
                 off += lengths[q];
             }
             // one convolution over the pack: a continuation's first token row sees its lead rows
-            S1_OP(S1_FAMILY_CONV, 1,
-                  cs1_gdn_conv(s.at(s.gdn_in), gdn_in, m->w(ly.conv), s.at(s.lq), s.at(s.lk), s.at(s.lv), t, kd, vd, st));
-            S1_OP(S1_FAMILY_GATES, 1,
-                  cs1_gdn_gates(s.at(b), s.at(a), gdn_in, m->w(ly.a_log), m->w(ly.dt_bias), s.at(s.beta),
-                                reinterpret_cast<float*>(s.at(s.g)), t, hv, st));
+            S1_TRY(conv_gates(m, ly, 0, t));
             off = 0;
             for (int q = 0; q < nseq; q++) {
                 const size_t r = off + lead;

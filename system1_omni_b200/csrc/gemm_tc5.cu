@@ -941,6 +941,7 @@ int launch(const void* x, const void* w, void* y, int M, int N, int K, int ldy, 
 // and every further wave of clusters about 6, of a persistent block's next tile about 1.
 struct SmallPlan {
     int bn, splits;
+    double us;  // the estimate it was chosen by
 };
 constexpr double SMALL_KB_US[3] = {0.38, 0.31, 0.30};  // widths 256, 128, 64
 constexpr double SMALL_W_BYTES_PER_US = 4.5e6;
@@ -952,7 +953,7 @@ SmallPlan small_plan(int M, int N, int K, DeviceInfo* info, bool may_split) {
     if (const char* f = getenv("S1_GEMM_BN")) force_bn = atoi(f);
     if (const char* f = getenv("S1_GEMM_SPLITS")) force_s = atoi(f);
     const int widths[3] = {256, 128, 64};
-    SmallPlan best{64, 1};
+    SmallPlan best{64, 1, 1e30};
     double best_cost = 1e30;
     for (int i = 0; i < 3; i++) {
         const int bn = widths[i];
@@ -974,7 +975,7 @@ SmallPlan small_plan(int M, int N, int K, DeviceInfo* info, bool may_split) {
             const double cost = (c > 1 ? 6.5 + 0.2 * c : 4.0) + (waves - 1) * (c > 1 ? 6.0 : 1.0) + (busy > stream_us ? busy : stream_us);
             if (cost < best_cost - 1e-9) {
                 best_cost = cost;
-                best = SmallPlan{bn, c};
+                best = SmallPlan{bn, c, cost};
             }
         }
     }
@@ -990,7 +991,11 @@ SmallPlan small_plan(int M, int N, int K, DeviceInfo* info, bool may_split) {
 // tile needs float32 room for every partial tile.
 struct PairPlan {
     int bn, splits, mode;
+    double us;  // the estimate in microseconds: cost units x PAIR_UNIT_US + PAIR_LAUNCH_US
 };
+// One cost unit in microseconds, from the wide projections at 1024 rows (82 us for 143 k units,
+// 53 for 88 k, 155 for 262 k), and what a launch costs beside its k-blocks.
+constexpr double PAIR_UNIT_US = 5.9e-4, PAIR_LAUNCH_US = 3.0;
 
 // exposed time of the partial-tile sums, in k-blocks: measured about 5 s^2 for s equal parts (the
 // last piece of a tile reads the other s - 1 partial tiles with few loads in flight)
@@ -1006,7 +1011,7 @@ PairPlan pair_plan(int M, int N, int K, int pairs, size_t partial_bytes, int cou
     if (const char* f = getenv("S1_GEMM_BN")) force_bn = atoi(f);
     if (const char* f = getenv("S1_GEMM_SPLITS")) force_s = atoi(f);
     if (const char* f = getenv("S1_GEMM_RUNS")) force_run = atoi(f);
-    PairPlan best{256, 1, 0};
+    PairPlan best{256, 1, 0, 1e30};
     double best_cost = 1e30;
     for (int bn = 256; bn >= 64; bn -= 32) {
         if (force_bn && bn != force_bn) continue;
@@ -1023,7 +1028,7 @@ PairPlan pair_plan(int M, int N, int K, int pairs, size_t partial_bytes, int cou
             const double cost = ((double)waves * (kb_per + 6) + (s > 1 ? SPLIT_FIXUP_KB * s * s : 0.0)) * (bn + 400);
             if (cost < best_cost - 1e-9) {
                 best_cost = cost;
-                best = PairPlan{bn, s, 0};
+                best = PairPlan{bn, s, 0, cost * PAIR_UNIT_US + PAIR_LAUNCH_US};
             }
         }
         // contiguous runs: every pair gets total / pairs k-blocks in at most
@@ -1038,7 +1043,7 @@ PairPlan pair_plan(int M, int N, int K, int pairs, size_t partial_bytes, int cou
             const double cost = ((double)run + 6.0 * pieces + RUN_FIXUP_KB) * (bn + 400) * RUN_KB_COST;
             if (cost < best_cost - 1e-9) {
                 best_cost = cost;
-                best = PairPlan{bn, 1, 1};
+                best = PairPlan{bn, 1, 1, cost * PAIR_UNIT_US + PAIR_LAUNCH_US};
             }
         }
     }
@@ -1065,6 +1070,20 @@ int launch_pair(const void* x, const void* w, void* y, int M, int N, int K, int 
                       vec_ok, bn, plan.splits, plan.mode, static_cast<float*>(partials), counters, 0);
 }
 
+// Width of the gate/up tile (half of it gate columns, half up columns) for the fused kernel.
+PairPlan swiglu_plan(int M, int I, int K, int pairs) {
+    const long num_m = (M + 2 * BM - 1) / (2 * BM);
+    const int kblocks = (K + BK - 1) / BK;
+    PairPlan best{256, 1, 0, 1e30};
+    double best_cost = 1e30;
+    for (int c = 256; c >= 64; c -= 64) {  // half of it a multiple of 32
+        const long tiles = num_m * ((I + c / 2 - 1) / (c / 2));
+        const double cost = (double)((tiles + pairs - 1) / pairs) * (kblocks + 6) * (c + 400);
+        if (cost < best_cost - 1e-9) best_cost = cost, best = PairPlan{c, 1, 0, cost * PAIR_UNIT_US + PAIR_LAUNCH_US};
+    }
+    return best;
+}
+
 // act [M, I] = silu(x w_gate^T) * (x w_up^T) with w = [gate; up] stacked, [2 I, K]: both
 // projections rounded to bf16 before the activation, as when they are stored and read back.
 int launch_pair_swiglu(const void* x, const void* w, void* act, int M, int I, int K, int ld, DeviceInfo* info,
@@ -1077,14 +1096,7 @@ int launch_pair_swiglu(const void* x, const void* w, void* act, int M, int I, in
     }
     const int pairs = info->sms / 2;
     const long num_m = (M + 2 * BM - 1) / (2 * BM);
-    const int kblocks = (K + BK - 1) / BK;
-    int bn = 256;
-    double best_cost = 1e30;
-    for (int c = 256; c >= 64; c -= 64) {  // half of it a multiple of 32
-        const long tiles = num_m * ((I + c / 2 - 1) / (c / 2));
-        const double cost = (double)((tiles + pairs - 1) / pairs) * (kblocks + 6) * (c + 400);
-        if (cost < best_cost - 1e-9) best_cost = cost, bn = c;
-    }
+    const int bn = swiglu_plan(M, I, K, pairs).bn;
     CUtensorMap mx, mw;
     if (!tensor_map(x, M, K, BM, &mx) || !tensor_map(w, 2 * I, K, bn / 2, &mw)) return CS1_ERR_TENSOR_MAP;
     const long tiles = num_m * ((I + bn / 2 - 1) / (bn / 2));
@@ -1092,6 +1104,19 @@ int launch_pair_swiglu(const void* x, const void* w, void* act, int M, int I, in
     const int vec_ok = (ld % 8 == 0) && aligned16(act);
     return launch_dep(gemm_tc5_pair_kernel, grid, GEMM_THREADS, PAIR_SMEM, st, mx, mw, static_cast<bf16*>(act), M, I, K, ld,
                       vec_ok, bn, 1, 0, static_cast<float*>(nullptr), static_cast<int*>(nullptr), 1);
+}
+
+// Which kernel takes a problem of more than 128 rows: the pair kernel, or the single-block kernel
+// whose clusters share K. By the two planners' estimates; with few rows and a narrow result
+// (N = 2560 ... 5120 at up to some 700 rows) the pair kernel has too few 256-row tiles to fill the
+// GPU and its shared-tile schedules pay for partial tiles in global memory. S1_GEMM_SMALL_ROWS=n
+// The single-block estimate runs up to 20 % low with several row blocks (measured against both
+// kernels on the projections of the three model sizes at 192 to 1024 rows), so it has to win by
+// 15 %. S1_GEMM_SMALL_ROWS=n overrides: up to n rows the single-block kernel, above it the pair kernel.
+bool single_block_wins(double single_us, double pair_us, int M) {
+    if (const char* v = getenv("S1_GEMM_SMALL_ROWS"))
+        if (atoi(v) > 0) return M <= atoi(v);
+    return single_us < 0.85 * pair_us;
 }
 
 bool pair_enabled() {
@@ -1118,21 +1143,33 @@ int s1_gemm_tc5(const void* x, const void* w, void* y, int M, int N, int K, int 
     cudaError_t err;
     DeviceInfo* info = device_info(&err);
     if (!info) return err;
-    // More than one row block: the CTA-pair kernel (S1_GEMM_PAIR=0 keeps the single-block one, for A/B runs).
-    if (M > BM && pair_enabled())
-        return launch_pair(x, w, y, M, N, K, ldy, info, scratch ? scratch->partials : nullptr,
-                           scratch ? scratch->partial_bytes : 0, scratch ? scratch->counters : nullptr,
-                           scratch ? scratch->counter_slots : 0, st);
-    // At most 128 rows: no scratch means the caller wants a sum over k whose order does not depend
-    // on the number of rows, so the k-blocks stay in one block.
+    // No scratch means the caller wants a sum over k whose order does not depend on the number of
+    // rows, so the k-blocks of a tile stay in one block.
     const SmallPlan plan = small_plan(M, N, K, info, scratch != nullptr);
+    // More than one row block: the CTA-pair kernel unless the single-block one is estimated faster
+    // (S1_GEMM_PAIR=0 keeps the single-block one, for A/B runs).
+    if (M > BM && pair_enabled()) {
+        const bool fix = scratch && scratch->partials && scratch->counters;
+        const PairPlan pair = pair_plan(M, N, K, info->sms / 2, fix ? scratch->partial_bytes : 0, fix ? scratch->counter_slots : 0);
+        if (!single_block_wins(plan.us, pair.us, M))
+            return launch_pair(x, w, y, M, N, K, ldy, info, scratch ? scratch->partials : nullptr,
+                               scratch ? scratch->partial_bytes : 0, scratch ? scratch->counters : nullptr,
+                               scratch ? scratch->counter_slots : 0, st);
+    }
     if (plan.bn == 256) return launch<256>(x, w, y, M, N, K, ldy, info, 0, plan.splits, st);
     if (plan.bn == 128) return launch<128>(x, w, y, M, N, K, ldy, info, 1, plan.splits, st);
     return launch<64>(x, w, y, M, N, K, ldy, info, 2, plan.splits, st);
 }
 
 bool s1_gemm_tc5_swiglu_supported(const void* x, const void* w, int M, int I, int K) {
-    return M > BM && I > 0 && K >= 64 && K % 8 == 0 && aligned16(x) && aligned16(w) && pair_enabled();
+    if (!(M > BM && I > 0 && K >= 64 && K % 8 == 0 && aligned16(x) && aligned16(w) && pair_enabled())) return false;
+    cudaError_t err;
+    DeviceInfo* info = device_info(&err);
+    if (!info) return false;
+    // the fused kernel is the pair kernel: against the single-block kernel on [gate | up] followed by
+    // the SiLU-multiply as a kernel of its own (a launch and 6 bytes per element at about 3 TB/s)
+    const double two_ops = small_plan(M, 2 * I, K, info, true).us + 2.5 + 6.0 * M * I / 3e6;
+    return !single_block_wins(two_ops, swiglu_plan(M, I, K, info->sms / 2).us, M);
 }
 
 int s1_gemm_tc5_swiglu(const void* x, const void* w, void* act, int M, int I, int K, int ld, cudaStream_t st) {

@@ -95,6 +95,7 @@ SIGNATURES = {
     "s1_attn_tc5_status": (i32, [ip]),
     "s1_gdn_status": (i32, [ip]),
     "s1_l2norm_heads": (i32, [vp, vp, C.c_longlong, f32, vp]),
+    "s1_gdn_conv_gates": (i32, [vp, i32, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, i32, vp]),
     "s1_checkpoint_inspect": (i32, [C.c_char_p, C.c_char_p, C.c_size_t, ip, i32, C.c_char_p, C.c_size_t, C.c_char_p,
                                     C.c_size_t, ip, vp, vp]),
     "s1_model_load_checkpoint": (i32, [vp, C.c_char_p, C.c_char_p, C.c_size_t]),

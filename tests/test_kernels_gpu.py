@@ -182,6 +182,39 @@ def test_gdn_gates_match_reference(cs1, stream):
         assert np.all(got <= 0) and np.allclose(got, wg, rtol=2e-6, atol=1e-30)
 
 
+@pytest.mark.parametrize("T", [1, 15, 16, 17, 67, 300])
+@pytest.mark.parametrize("kd,vd,H", [(2048, 4096, 32), (256, 512, 4), (128, 384, 3)])
+def test_gdn_conv_and_gates_in_one_launch(cs1, stream, T, kd, vd, H):
+    """The executor's fused launch against cs1_gdn_conv then cs1_gdn_gates on the rows of one input
+    projection ([q | k | v | z | b | a], model.rs:640-668 runs the two one after the other): the same bits."""
+    ch = 2 * kd + vd
+    ld = (ch + vd + 2 * H + 7) // 8 * 8
+    x = O.random_bf16(T * ld, 63 + T, 3.0)
+    w = O.random_bf16(ch * 4, 64, 0.7)
+    A_log = bf(np.random.default_rng(0).uniform(0, np.log(16), H).astype(np.float32))
+    dt = bf(np.random.default_rng(1).normal(0, 0.1, H).astype(np.float32))
+    xd, wd, Ad, dd = dev(x, stream), dev(w, stream), dev(A_log, stream), dev(dt, stream)
+    b_at, a_at = (ch + vd) * 2, (ch + vd + H) * 2
+    outs = []
+    for fused in (False, True):
+        q, k, v = (dev(np.full(T * n, 0x7FC0, np.uint16), stream) for n in (kd, kd, vd))
+        beta, g = dev(np.full(T * H, 0x7FC0, np.uint16), stream), dev(np.full(T * H, np.nan, np.float32), stream)
+        if fused:
+            L.check(cs1.s1_gdn_conv_gates(xd.at(), ld, wd.at(), q.at(), k.at(), v.at(), T, kd, vd, xd.at(b_at), xd.at(a_at),
+                                          Ad.at(), dd.at(), beta.at(), g.at(), H, stream.handle), "fused")
+        else:
+            L.check(cs1.cs1_gdn_conv(xd.at(), ld, wd.at(), q.at(), k.at(), v.at(), T, kd, vd, stream.handle), "conv")
+            L.check(cs1.cs1_gdn_gates(xd.at(b_at), xd.at(a_at), ld, Ad.at(), dd.at(), beta.at(), g.at(), T, H,
+                                      stream.handle), "gates")
+        outs.append([host(q, (T, kd), stream), host(k, (T, kd), stream), host(v, (T, vd), stream),
+                     host(beta, (T, H), stream), host(g, (T, H), stream, np.float32)])
+    for two, one in zip(*outs):
+        assert np.array_equal(two, one)
+    # widths the packed convolution does not take: the caller runs the two operators
+    assert cs1.s1_gdn_conv_gates(xd.at(), ld, wd.at(), None, None, None, T, kd - 4, vd, xd.at(b_at), xd.at(a_at), Ad.at(),
+                                 dd.at(), None, None, H, stream.handle) == 2000
+
+
 def test_device_copy_helpers_roundtrip(cs1, stream):
     # kernels.rs:744-769
     a = dev(O.random_bf16(4099, 1, 2.0), stream)
@@ -548,16 +581,19 @@ def test_gemm_shared_tile_schedules(cs1, stream, M, N, K, pad, knobs, monkeypatc
 
 
 @pytest.mark.parametrize("M,N,K,pad", [(64, 2560, 9728, 0), (128, 2560, 4096, 0), (1, 2560, 4096, 8), (77, 1000, 2048, 3),
-                                       (128, 12352, 2560, 0), (33, 515, 1024, 0)])
+                                       (128, 12352, 2560, 0), (33, 515, 1024, 0), (200, 2560, 4096, 0), (300, 1000, 2048, 3),
+                                       (520, 2560, 9728, 8)])
 @pytest.mark.parametrize("knobs", [{}, {"S1_GEMM_SPLITS": "2", "S1_GEMM_BN": "256"}, {"S1_GEMM_SPLITS": "3", "S1_GEMM_BN": "64"},
                                    {"S1_GEMM_SPLITS": "4"}, {"S1_GEMM_SPLITS": "5", "S1_GEMM_BN": "128"},
                                    {"S1_GEMM_SPLITS": "8", "S1_GEMM_BN": "128"}])
 def test_gemm_few_rows_share_k_over_a_cluster(cs1, stream, M, N, K, pad, knobs, monkeypatch):
-    """Up to 128 rows: the blocks of a cluster share a tile's k-blocks and add their float32
-    tiles through distributed shared memory in rank order - as planned and with cluster sizes
-    and widths forced: the oracle's result, repeatable bit for bit, padding untouched."""
+    """The single-block kernel (up to 128 rows always, more where it is estimated faster than the
+    pair kernel): the blocks of a cluster share a tile's k-blocks and add their float32 tiles
+    through distributed shared memory in rank order - as planned and with cluster sizes and
+    widths forced: the oracle's result, repeatable bit for bit, padding untouched."""
     for k, v in knobs.items():
         monkeypatch.setenv(k, v)
+    monkeypatch.setenv("S1_GEMM_SMALL_ROWS", "4096")        # several row blocks too go to the single-block kernel
     x, w, ldy = gemm_case(M, N, K, pad, seed=11)
     xd, wd = dev(x, stream), dev(w, stream)
     handle = cs1.cs1_gemm_create(32 << 20)
@@ -575,9 +611,12 @@ def test_gemm_few_rows_share_k_over_a_cluster(cs1, stream, M, N, K, pad, knobs, 
 
 @pytest.mark.parametrize("M,I,K,pad", [(1024, 9728, 2560, 0), (300, 1000, 512, 8), (129, 96, 64, 0), (700, 17408, 1024, 0),
                                        (257, 40, 128, 3)])
-def test_gemm_swiglu_equals_the_two_operators(cs1, stream, M, I, K, pad):
+def test_gemm_swiglu_equals_the_two_operators(cs1, stream, M, I, K, pad, monkeypatch):
     """gate/up projection + SiLU-multiply in one kernel against cs1_gemm then cs1_silu_mul
-    (model.rs:1301-1316 runs them as two operators): the same bits, padding untouched."""
+    (model.rs:1301-1316 runs them as two operators): the same bits, padding untouched. (The kernel
+    choice is pinned to the pair kernel above 128 rows: for some of these shapes the planner would
+    take the single-block kernel and leave the activation to cs1_silu_mul.)"""
+    monkeypatch.setenv("S1_GEMM_SMALL_ROWS", "128")
     x = O.random_bf16(M * K, 31, 1.0).reshape(M, K)
     w = O.random_bf16(2 * I * K, 32, 0.08).reshape(2 * I, K)
     xd, wd = dev(x, stream), dev(w, stream)
