@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         for (int tile = first; tile < tiles; tile += step, it++) {
             const int m_idx = tile % num_m, n_idx = tile / num_m;
             const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
-            if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) {
+            if (!mbar_wait_idle(&tfull[acc], acc_phase, abort_flag)) {
                 fail(4);
                 break;
             }
@@ -443,7 +443,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     };
 
     if (warp == 0) {
-        if (lane == 0) {
+        {  // the whole warp runs the loop, one lane issues
+            const bool issuer = elect_one();
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             // As in the single-block kernel: this block's w tiles of the first ring-full of stages go
@@ -455,7 +456,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                 pair_tile_coords(pc.tile, num_m, num_n, m_idx, n_idx);
                 const int n0 = swiglu ? n_idx * half_n + (int)rank * N : n_idx * BN + (int)rank * half_n;
                 ahead = min(pc.kb1 - pc.kb0, (int)nstages);
-                for (int i = 0; i < ahead; i++) {
+                for (int i = 0; i < ahead && issuer; i++) {
                     if (leader) mbar_expect_tx(&full[i], 2 * stage_bytes);  // both blocks' bytes land on it
                     tma_load_2d_pair(smem + i * stage_bytes + PAIR_A_BYTES, &tma_w, (pc.kb0 + i) * BK, n0, &full[i]);
                 }
@@ -474,10 +475,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                             ok = false;
                             break;
                         }
-                        if (leader) mbar_expect_tx(&full[stage], 2 * stage_bytes);
-                        tma_load_2d_pair(dst + PAIR_A_BYTES, &tma_w, kb * BK, n0, &full[stage]);
+                        if (issuer) {
+                            if (leader) mbar_expect_tx(&full[stage], 2 * stage_bytes);
+                            tma_load_2d_pair(dst + PAIR_A_BYTES, &tma_w, kb * BK, n0, &full[stage]);
+                        }
                     }
-                    tma_load_2d_pair(dst, &tma_x, kb * BK, m0, &full[stage]);
+                    if (issuer) tma_load_2d_pair(dst, &tma_x, kb * BK, m0, &full[stage]);
                     if (++stage == nstages) {
                         stage = 0;
                         phase ^= 1;
@@ -487,7 +490,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (leader && lane == 0) {
+        if (leader) {  // the whole warp runs the loop, one lane issues
+            const bool issuer = elect_one();
             const uint32_t idesc = instr_desc(1, 2 * BM, BN);
             uint32_t stage = 0, phase = 0, it = 0;
             bool ok = true;
@@ -509,18 +513,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                     fence_after_sync();
                     const uint32_t a_addr = smem_addr(smem + stage * stage_bytes);
                     const uint32_t b_addr = a_addr + PAIR_A_BYTES;
+                    if (issuer) {
 #pragma unroll
-                    for (int k = 0; k < BK / 16; k++) {
-                        mma_bf16_ss_pair(d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
-                                         (kb > kb0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < BK / 16; k++) {
+                            mma_bf16_ss_pair(d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
+                                             (kb > kb0 || k > 0) ? 1u : 0u);
+                        }
+                        mma_commit_pair(&empty[stage], 3);  // frees the stage in both blocks
                     }
-                    mma_commit_pair(&empty[stage], 3);  // frees the stage in both blocks
                     if (++stage == nstages) {
                         stage = 0;
                         phase ^= 1;
                     }
                 }
-                if (ok) mma_commit_pair(&tfull[acc], 3);  // wakes both blocks' epilogues
+                if (ok && issuer) mma_commit_pair(&tfull[acc], 3);  // wakes both blocks' epilogues
             }
         }
         __syncwarp();
@@ -535,7 +541,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
             int m_idx, n_idx;
             pair_tile_coords(tile, num_m, num_n, m_idx, n_idx);
             const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
-            if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) {
+            if (!mbar_wait_idle(&tfull[acc], acc_phase, abort_flag)) {
                 fail(14);
                 break;
             }

@@ -56,15 +56,59 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t start = global_ns();
+    // The clock is read only once in 1024 failed polls, the first time included: a read of
+    // %globaltimer costs far more than a poll, and in a pipeline that runs at the speed of its
+    // round trips nearly every wait misses its first poll.
+    uint64_t start = 0;
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 0x3ff) == 0) {
             if (*abort_flag) return false;
-            if (global_ns() - start > WAIT_LIMIT_NS) return false;
+            const uint64_t now = global_ns();
+            if (start == 0)
+                start = now;
+            else if (now - start > WAIT_LIMIT_NS)
+                return false;
         }
     }
     return true;
+}
+
+// The same for warps that wait long (an epilogue waiting for a whole tile's k-blocks): they sleep
+// between polls, so that they do not take issue slots from the one thread on their SM
+// sub-partition that feeds the copy engine or the tensor core.
+__device__ __forceinline__ bool mbar_wait_idle(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t sleep_ns = 256) {
+    if (mbar_try_wait(bar, parity)) return true;
+    uint64_t start = 0;
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(sleep_ns);
+        if ((++spins & 0x3ff) == 0) {
+            if (*abort_flag) return false;
+            const uint64_t now = global_ns();
+            if (start == 0)
+                start = now;
+            else if (now - start > WAIT_LIMIT_NS)
+                return false;
+        }
+    }
+    return true;
+}
+
+// One lane of a converged warp. The loops that feed the copy engine and the tensor core are run
+// by all 32 lanes of their warp with only the issuing instructions under this predicate: addresses,
+// descriptors and loop counters then stay warp-uniform, where a loop under `if (lane == 0)` makes
+// every operand of every tcgen05 / TMA instruction a per-thread value.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "elect.sync _|p, 0xffffffff;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(pred));
+    return pred != 0;
 }
 
 // ---- TMA ----
