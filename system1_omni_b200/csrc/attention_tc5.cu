@@ -291,10 +291,13 @@ __global__ void __launch_bounds__(ATHREADS, 1)
     };
 
     if (warp == 0) {
-        if (lane == 0) {
-            mbar_expect_tx(q_full, G::Q_BYTES);
-            for (int c = 0; c < DH / 64; c++)
-                tma_load_2d(smem + c * (ABM * 128), &maps.q, h * DH + c * 64, q0 - own_base, q_full);
+        {  // the whole warp runs the loop, one lane issues (addresses and counters stay warp-uniform)
+            const bool issuer = elect_one();
+            if (issuer) {
+                mbar_expect_tx(q_full, G::Q_BYTES);
+                for (int c = 0; c < DH / 64; c++)
+                    tma_load_2d(smem + c * (ABM * 128), &maps.q, h * DH + c * 64, q0 - own_base, q_full);
+            }
             for (int j = 0; j < ntiles; j++) {
                 const int stage = j & 1;
                 const uint32_t parity = ((j >> 1) & 1) ^ 1;
@@ -303,8 +306,8 @@ __global__ void __launch_bounds__(ATHREADS, 1)
                     fail(21);
                     break;
                 }
-                mbar_expect_tx(&k_full[stage], G::KV_BYTES);
-                for (int c = 0; c < DH / 64; c++)
+                if (issuer) mbar_expect_tx(&k_full[stage], G::KV_BYTES);
+                for (int c = 0; c < DH / 64 && issuer; c++)
                     for (int g = 0; g < BN / 64; g++) {
                         const int r0 = j * BN + g * 64;
                         unsigned char* dst = smem + G::OFF_K + stage * G::KV_BYTES + c * (BN * 128) + g * (64 * 128);
@@ -317,8 +320,8 @@ __global__ void __launch_bounds__(ATHREADS, 1)
                     fail(22);
                     break;
                 }
-                mbar_expect_tx(&v_full[stage], G::KV_BYTES);
-                for (int c = 0; c < DH / 64; c++)
+                if (issuer) mbar_expect_tx(&v_full[stage], G::KV_BYTES);
+                for (int c = 0; c < DH / 64 && issuer; c++)
                     for (int g = 0; g < BN / 64; g++) {
                         const int r0 = j * BN + g * 64;
                         unsigned char* dst = smem + G::OFF_V + stage * G::KV_BYTES + c * (BN * 128) + g * (64 * 128);
@@ -331,7 +334,8 @@ __global__ void __launch_bounds__(ATHREADS, 1)
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0) {
+        {
+            const bool issuer = elect_one();
             constexpr uint32_t idesc_s = instr_desc(1, ABM, BN);
             constexpr uint32_t idesc_o = instr_desc_b_mn(1, ABM, DH);
             const uint32_t q_addr = smem_addr(smem), p_addr = smem_addr(smem + G::OFF_P);
@@ -350,14 +354,16 @@ __global__ void __launch_bounds__(ATHREADS, 1)
                 }
                 fence_after_sync();
                 const uint32_t v_addr = smem_addr(smem + G::OFF_V + stage * G::KV_BYTES);
+                if (issuer) {
 #pragma unroll
-                for (int kk = 0; kk < BN / 16; kk++) {
-                    const uint64_t a = smem_desc_sw128(p_addr + (kk / 4) * (ABM * 128) + (kk % 4) * 32);
-                    const uint64_t b = smem_desc_mn_sw128(v_addr + kk * 2048, BN * 128, 1024);
-                    mma_bf16_ss(tmem_base + G::O_COL, a, b, idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
+                    for (int kk = 0; kk < BN / 16; kk++) {
+                        const uint64_t a = smem_desc_sw128(p_addr + (kk / 4) * (ABM * 128) + (kk % 4) * 32);
+                        const uint64_t b = smem_desc_mn_sw128(v_addr + kk * 2048, BN * 128, 1024);
+                        mma_bf16_ss(tmem_base + G::O_COL, a, b, idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    mma_commit(&v_empty[stage]);
+                    mma_commit(o_done);
                 }
-                mma_commit(&v_empty[stage]);
-                mma_commit(o_done);
                 return true;
             };
             for (int j = 0; ok && j < ntiles; j++) {
@@ -375,14 +381,16 @@ __global__ void __launch_bounds__(ATHREADS, 1)
                 }
                 fence_after_sync();
                 const uint32_t k_addr = smem_addr(smem + G::OFF_K + stage * G::KV_BYTES);
+                if (issuer) {
 #pragma unroll
-                for (int kk = 0; kk < DH / 16; kk++) {
-                    const uint64_t a = smem_desc_sw128(q_addr + (kk / 4) * (ABM * 128) + (kk % 4) * 32);
-                    const uint64_t b = smem_desc_sw128(k_addr + (kk / 4) * (BN * 128) + (kk % 4) * 32);
-                    mma_bf16_ss(tmem_base + stage * BN, a, b, idesc_s, kk > 0 ? 1u : 0u);
+                    for (int kk = 0; kk < DH / 16; kk++) {
+                        const uint64_t a = smem_desc_sw128(q_addr + (kk / 4) * (ABM * 128) + (kk % 4) * 32);
+                        const uint64_t b = smem_desc_sw128(k_addr + (kk / 4) * (BN * 128) + (kk % 4) * 32);
+                        mma_bf16_ss(tmem_base + stage * BN, a, b, idesc_s, kk > 0 ? 1u : 0u);
+                    }
+                    mma_commit(&k_empty[stage]);
+                    mma_commit(&s_full[stage]);
                 }
-                mma_commit(&k_empty[stage]);
-                mma_commit(&s_full[stage]);
                 if (j > 0) ok = issue_pv(j - 1);
             }
             if (ok && ntiles > 0) issue_pv(ntiles - 1);

@@ -109,7 +109,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     };
 
     if (warp == 0) {
-        if (lane == 0) {
+        {  // the whole warp runs the loop, one lane issues (addresses and counters stay warp-uniform)
+            const bool issuer = elect_one();
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             // The first ring-full of w tiles goes out before this kernel waits for the one ahead of
@@ -118,7 +119,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             int ahead = 0;
             if (first < tiles) {
                 ahead = min(kb1 - kb0, G::STAGES);
-                for (int i = 0; i < ahead; i++) {
+                for (int i = 0; i < ahead && issuer; i++) {
                     mbar_expect_tx(&full[i], G::STAGE);
                     tma_load_2d(smem + i * G::STAGE + G::A_BYTES, &tma_w, (kb0 + i) * BK, (first / num_m) * BN, &full[i]);
                 }
@@ -134,10 +135,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                             ok = false;
                             break;
                         }
-                        mbar_expect_tx(&full[stage], G::STAGE);
-                        tma_load_2d(dst + G::A_BYTES, &tma_w, kb * BK, n_idx * BN, &full[stage]);
+                        if (issuer) {
+                            mbar_expect_tx(&full[stage], G::STAGE);
+                            tma_load_2d(dst + G::A_BYTES, &tma_w, kb * BK, n_idx * BN, &full[stage]);
+                        }
                     }
-                    tma_load_2d(dst, &tma_x, kb * BK, m_idx * BM, &full[stage]);
+                    if (issuer) tma_load_2d(dst, &tma_x, kb * BK, m_idx * BM, &full[stage]);
                     if (++stage == G::STAGES) {
                         stage = 0;
                         phase ^= 1;
@@ -147,7 +150,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0) {
+        {
+            const bool issuer = elect_one();
             constexpr uint32_t idesc = instr_desc(1, BM, BN);
             uint32_t stage = 0, phase = 0, it = 0;
             bool ok = true;
@@ -168,18 +172,20 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     fence_after_sync();
                     const uint32_t a_addr = smem_addr(smem + stage * G::STAGE);
                     const uint32_t b_addr = a_addr + G::A_BYTES;
+                    if (issuer) {
 #pragma unroll
-                    for (int k = 0; k < BK / 16; k++) {
-                        mma_bf16_ss(d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
-                                    ((kb - kb0) | k) != 0);
+                        for (int k = 0; k < BK / 16; k++) {
+                            mma_bf16_ss(d, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
+                                        ((kb - kb0) | k) != 0);
+                        }
+                        mma_commit(&empty[stage]);
                     }
-                    mma_commit(&empty[stage]);
                     if (++stage == G::STAGES) {
                         stage = 0;
                         phase ^= 1;
                     }
                 }
-                if (ok) mma_commit(&tfull[acc]);
+                if (ok && issuer) mma_commit(&tfull[acc]);
             }
         }
         __syncwarp();
