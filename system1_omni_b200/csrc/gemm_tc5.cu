@@ -996,38 +996,35 @@ SmallPlan small_plan(int M, int N, int K, DeviceInfo* info, bool may_split) {
 
 // Plan for the pair kernel: the column-block width (a multiple of 32) and how the k-blocks
 // are handed out -- whole tiles, `splits` equal parts per tile, or one contiguous run of all
-// tiles' k-blocks per pair -- minimising k-blocks per pair x per-k-block cost. Measured: a
-// k-block's time depends only weakly on the width (the 128 rows of x each block loads
-// dominate), roughly as bn + 400; a piece costs about 6 k-blocks of fill and drain on top of
-// its own, and combining float32 partial tiles costs a fixed amount at the end. Sharing a
-// tile needs float32 room for every partial tile.
+// tiles' k-blocks per pair -- by an estimate in microseconds built from measurements (4B- and
+// 27B-shaped projections at 1024 and 4096 rows, widths 64 to 256, all three schedules): a
+// k-block of a 256 x bn tile takes 0.00115 (bn + 28) us (the tensor pipe at 85 % of its peak: the
+// width is what counts), a wave of tiles about 5 us beside its k-blocks (fill, drain and the
+// ragged end of a wave), a launch 3; sharing a tile between s pairs costs about 1.7 s^2 for the
+// float32 partial tiles summed by the last piece, and a k-block of a run 1.3 times a tile's
+// (pairs at different k share no operand tiles in L2). Sharing needs float32 room for every
+// partial tile.
 struct PairPlan {
     int bn, splits, mode;
-    double us;  // the estimate in microseconds: cost units x PAIR_UNIT_US + PAIR_LAUNCH_US
+    double us;  // the estimate it was chosen by
 };
-// One cost unit in microseconds, from the wide projections at 1024 rows (82 us for 143 k units,
-// 53 for 88 k, 155 for 262 k), and what a launch costs beside its k-blocks.
-constexpr double PAIR_UNIT_US = 5.9e-4, PAIR_LAUNCH_US = 3.0;
-
-// exposed time of the partial-tile sums, in k-blocks: measured about 5 s^2 for s equal parts (the
-// last piece of a tile reads the other s - 1 partial tiles with few loads in flight)
-constexpr double SPLIT_FIXUP_KB = 5.0;
-constexpr double RUN_FIXUP_KB = 8.0;
-constexpr double RUN_KB_COST = 1.3;      // a k-block of a run costs more: pairs at different k share no operand tiles in L2
+constexpr double PAIR_KB_US = 0.00115, PAIR_KB_BASE = 28.0, PAIR_WAVE_US = 5.0, PAIR_LAUNCH_US = 3.0;
+constexpr double SPLIT_FIXUP_US = 1.7;   // x s^2
+constexpr double RUN_KB_COST = 1.3;
 
 PairPlan pair_plan(int M, int N, int K, int pairs, size_t partial_bytes, int counter_slots) {
     const long num_m = (M + 2 * BM - 1) / (2 * BM);
     const int kblocks = (K + BK - 1) / BK;
-    // tuning knobs (S1_GEMM_RUNS: 0 never, 1 always, otherwise by the cost model)
+    // tuning knobs (S1_GEMM_RUNS: 0 never, 1 always, otherwise by the estimate)
     int force_bn = 0, force_s = 0, force_run = 2;
     if (const char* f = getenv("S1_GEMM_BN")) force_bn = atoi(f);
     if (const char* f = getenv("S1_GEMM_SPLITS")) force_s = atoi(f);
     if (const char* f = getenv("S1_GEMM_RUNS")) force_run = atoi(f);
     PairPlan best{256, 1, 0, 1e30};
-    double best_cost = 1e30;
     for (int bn = 256; bn >= 64; bn -= 32) {
         if (force_bn && bn != force_bn) continue;
         const long tiles = num_m * ((N + bn - 1) / bn);
+        const double kb_us = PAIR_KB_US * (bn + PAIR_KB_BASE);
         for (int s = 1; s <= 8 && force_run != 1; s++) {
             if (force_s && s != force_s) continue;
             const int kb_per = (kblocks + s - 1) / s;
@@ -1037,11 +1034,8 @@ PairPlan pair_plan(int M, int N, int K, int pairs, size_t partial_bytes, int cou
                 if ((size_t)tiles * s * 2 * BM * bn * 4 > partial_bytes || tiles * 2 > counter_slots) continue;
             }
             const long waves = (tiles * s + pairs - 1) / pairs;
-            const double cost = ((double)waves * (kb_per + 6) + (s > 1 ? SPLIT_FIXUP_KB * s * s : 0.0)) * (bn + 400);
-            if (cost < best_cost - 1e-9) {
-                best_cost = cost;
-                best = PairPlan{bn, s, 0, cost * PAIR_UNIT_US + PAIR_LAUNCH_US};
-            }
+            const double cost = (double)waves * (kb_per * kb_us + PAIR_WAVE_US) + PAIR_LAUNCH_US + (s > 1 ? SPLIT_FIXUP_US * s * s : 0.0);
+            if (cost < best.us - 1e-9) best = PairPlan{bn, s, 0, cost};
         }
         // contiguous runs: every pair gets total / pairs k-blocks in at most
         // ceil(run / kblocks) + 1 pieces, two of which share their tile
@@ -1052,11 +1046,10 @@ PairPlan pair_plan(int M, int N, int K, int pairs, size_t partial_bytes, int cou
             (size_t)pairs * 2 * 2 * BM * bn * 4 <= partial_bytes && tiles * 2 <= counter_slots) {
             const long run = (total + pairs - 1) / pairs;
             const long pieces = (run + kblocks - 1) / kblocks + 1;
-            const double cost = ((double)run + 6.0 * pieces + RUN_FIXUP_KB) * (bn + 400) * RUN_KB_COST;
-            if (cost < best_cost - 1e-9) {
-                best_cost = cost;
-                best = PairPlan{bn, 1, 1, cost * PAIR_UNIT_US + PAIR_LAUNCH_US};
-            }
+            // a tile is shared by about kblocks / run + 1 pairs, the last of which sums the others' partial tiles
+            const double parts = (double)kblocks / (double)run + 1.0;
+            const double cost = (double)run * kb_us * RUN_KB_COST + PAIR_WAVE_US * pieces + PAIR_LAUNCH_US + SPLIT_FIXUP_US * parts * parts;
+            if (cost < best.us - 1e-9) best = PairPlan{bn, 1, 1, cost};
         }
     }
     return best;
@@ -1087,11 +1080,10 @@ PairPlan swiglu_plan(int M, int I, int K, int pairs) {
     const long num_m = (M + 2 * BM - 1) / (2 * BM);
     const int kblocks = (K + BK - 1) / BK;
     PairPlan best{256, 1, 0, 1e30};
-    double best_cost = 1e30;
     for (int c = 256; c >= 64; c -= 64) {  // half of it a multiple of 32
         const long tiles = num_m * ((I + c / 2 - 1) / (c / 2));
-        const double cost = (double)((tiles + pairs - 1) / pairs) * (kblocks + 6) * (c + 400);
-        if (cost < best_cost - 1e-9) best_cost = cost, best = PairPlan{c, 1, 0, cost * PAIR_UNIT_US + PAIR_LAUNCH_US};
+        const double cost = (double)((tiles + pairs - 1) / pairs) * (kblocks * PAIR_KB_US * (c + PAIR_KB_BASE) + PAIR_WAVE_US) + PAIR_LAUNCH_US;
+        if (cost < best.us - 1e-9) best = PairPlan{c, 1, 0, cost};
     }
     return best;
 }
