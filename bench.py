@@ -210,6 +210,9 @@ def main():
 
     dist = torch = None
     if world > 1:
+        # whatever NCCL logs (its version banner, when the environment asks for one) goes to stderr:
+        # stdout carries the one JSON line
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(local)
