@@ -28,12 +28,13 @@ int s1_download_async(void* dst, const void* src, size_t bytes, void* stream);
 int s1_memset_async(void* dst, int value, size_t bytes, void* stream);
 int s1_device_sync(void);
 /* Programmatic dependent launch for the calling host thread's later launches of this library's
- * kernels: each may become resident while the kernel before it on the stream still runs, sets up
+ * kernels: mode 1 = every hot-path kernel, 2 = the GEMMs only, 0 = plain stream order. A kernel
+ * launched so may become resident while the kernel before it on the stream still runs, sets up
  * (the GEMMs also fetch their first weight tiles) and waits for that kernel to complete before it
- * touches activations. Results are the same bits either way. Returns the previous setting. The
- * executor switches it per forward pass by the number of tokens (s1_model_set_overlap_tokens);
- * S1_PDL=1 / S1_PDL=0 in the environment force it on / off for every launch. */
-int s1_set_dependent_launch(int on);
+ * touches activations. Results are the same bits in every mode. Returns the previous mode. The
+ * executor picks per forward pass by the number of tokens (s1_model_set_overlap_tokens);
+ * S1_PDL=1 / 2 / 0 in the environment force a mode for every launch. */
+int s1_set_dependent_launch(int mode);
 int s1_mem_info(size_t* free_bytes, size_t* total_bytes);
 
 /* ---- Attention over a window that continues a shared prefix ----
@@ -129,12 +130,13 @@ int s1_model_set_exact_packing(void* model, int on);
  * convolution and the gates of a GDN layer as one launch (s1_gdn_conv_gates). Off: always the
  * reference's operator sequence. */
 int s1_model_set_fused_mlp(void* model, int on);
-/* Forward passes of at most `tokens` tokens launch their kernels as programmatic dependents of one
- * another (s1_set_dependent_launch); longer ones launch in plain stream order. Default 512
- * (S1_PDL_TOKENS in the environment at s1_model_create); a pass recorded into a CUDA graph overlaps
- * only up to 128 tokens, since replay leaves little between kernels to hide. With few tokens a
- * kernel's launch gap, set-up and first trip to HBM are a large part of it; with many, the waiting
- * blocks only take room from the running kernel. The result's bits do not depend on it. */
+/* Forward passes of at most `tokens` tokens that are issued eagerly launch every kernel as a
+ * programmatic dependent of the one before it (s1_set_dependent_launch mode 1); longer ones, and
+ * every pass recorded into a CUDA graph, only the GEMMs (mode 2); tokens < 0: plain stream order
+ * always. Default 128 (S1_PDL_TOKENS in the environment at s1_model_create). With few tokens and
+ * eager issue the gaps between launches are what there is to hide; otherwise short kernels' blocks
+ * that only wait take room from the running GEMM, while a GEMM's early blocks fetch their first
+ * weight tiles under the short kernel ahead. The result's bits do not depend on it. */
 int s1_model_set_overlap_tokens(void* model, int tokens);
 int s1_model_graph_stats(void* model, int* replays, int* captures, int* enabled);
 

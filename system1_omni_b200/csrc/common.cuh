@@ -97,29 +97,35 @@ inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 // writes - overlaps the kernels before it; the order of all other memory effects is that of
 // ordinary stream order, since grid_dep_sync() returns only when the kernel before is complete
 // and its writes are visible, and that kernel in turn waited for the one before it.
-// The switch is per host thread: the executor turns it on for short prompts, where launch gaps,
-// prologues and the first trip to HBM are a large part of every kernel, and off for long ones
-// (measured at 1024 tokens: resident blocks that only wait take issue slots and shared memory from
-// the running kernel, 2 % slower). S1_PDL=1 / S1_PDL=0 in the environment force it on / off.
+// The switch is per host thread and has three settings: every hot-path kernel (the executor's
+// choice for short prompts, where launch gaps, prologues and the first trip to HBM are a large
+// part of every kernel), the GEMMs only (its choice for long ones: measured at 1024 tokens +3 %,
+// where making every kernel a dependent costs 1 %: the short kernels' blocks that only wait take
+// room from the running GEMM, while a GEMM's blocks that arrive early fetch their first ring of
+// weight tiles under the short kernel ahead), or none. S1_PDL=1 / 2 / 0 in the environment force one.
 // Both instructions are no-ops in a kernel launched the ordinary way.
 __device__ __forceinline__ void grid_dep_sync() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// The switch: 0 = plain stream order, 1 = every hot-path kernel, 2 = the GEMMs only.
 inline int& dep_launch_switch() {
-    static thread_local int on = 0;
-    return on;
+    static thread_local int mode = 0;
+    return mode;
 }
 
-inline bool dep_launch_enabled() {
+inline int dep_launch_mode() {
     static const int forced = [] {
-        const char* v = getenv("S1_PDL");
-        return !v ? -1 : (v[0] == '1' ? 1 : 0);
+        const char* e = getenv("S1_PDL");
+        return !e ? -1 : (e[0] == '1' ? 1 : e[0] == '2' ? 2 : 0);
     }();
-    return forced >= 0 ? forced == 1 : dep_launch_switch() != 0;
+    return forced >= 0 ? forced : dep_launch_switch();
 }
+inline bool dep_launch_enabled() { return dep_launch_mode() == 1; }
+inline bool dep_launch_gemm() { return dep_launch_mode() >= 1; }
 
 template <typename... KArgs, typename... Args>
-cudaError_t launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+cudaError_t launch_maybe_dep(bool dependent, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                             Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -129,8 +135,16 @@ cudaError_t launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = dep_launch_enabled() ? 1 : 0;
+    cfg.numAttrs = dependent ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    return launch_maybe_dep(dep_launch_enabled(), kernel, grid, block, smem, st, args...);
+}
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dep_gemm(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    return launch_maybe_dep(dep_launch_gemm(), kernel, grid, block, smem, st, args...);
 }
 
 }  // namespace s1

@@ -81,7 +81,7 @@ struct Model {
     bool graph_enabled = false;
     bool exact_packing = false;
     bool fuse_swiglu = true;  // gate/up GEMM and SiLU-multiply as one kernel where the engine supports it
-    int overlap_tokens = 512;  // passes of at most this many tokens launch their kernels as programmatic dependents
+    int overlap_tokens = 128;  // eager passes of at most this many tokens launch every kernel as a programmatic dependent
     bool capturing = false;    // the pass being issued is recorded into a graph
     int replays = 0, captures = 0;
     std::deque<std::pair<std::vector<int>, void*>> graphs;
@@ -400,15 +400,22 @@ int conv_gates(Model* m, const Layer& ly, size_t off, int len) {
 // The layer loop (model.rs:1119-1338). Pointwise operators and the input / gate-up GEMMs run
 // once over the packed rows; conv, delta rule, attention prep and attention run per sequence.
 // dump (nullable, host) receives the residual stream after each layer.
-// Dependent launch for the launches of one pass, put back on every way out. Measured on the
-// 4B-shaped decoder: issued eagerly a pass gains 16 % at 64 tokens and 8 % at 512 (launch gaps and
-// set-up hidden); replayed from a graph, where the gaps are small already, 3 % at 64 tokens,
-// nothing at 128 and -1 % at 512, so a recorded pass overlaps only up to GRAPH_OVERLAP_TOKENS.
-constexpr int GRAPH_OVERLAP_TOKENS = 128;
+// Dependent launch for the launches of one pass, put back on every way out. Short passes make
+// every kernel a programmatic dependent of the one before it, longer ones only the GEMMs (their
+// blocks arrive under the short kernel ahead and fetch their first ring of weight tiles there);
+// overlap_tokens < 0 keeps plain stream order. Measured on the 4B-shaped decoder (ms per pass,
+// plain / every kernel / GEMMs only): issued eagerly 3.81 / 3.29 / 3.45 at 64 tokens, 4.22 / 3.72 /
+// 3.78 at 128, 4.70 / 4.41 / 4.27 at 256, 9.34 / 9.06 / 9.09 at 1024; replayed from a graph, where
+// the gaps between launches are small already, 3.11 / 3.17 / 2.93 at 64, 4.02 / 4.29 / 3.85 at 256,
+// 8.69 / 8.88 / 8.50 at 1024, no difference from 4096 on. So an eager pass of up to overlap_tokens
+// tokens makes every kernel a dependent, every other pass the GEMMs only.
 struct OverlapScope {
     int before;
-    OverlapScope(const Model* m, int tokens)
-        : before(s1_set_dependent_launch(tokens <= (m->capturing ? std::min(m->overlap_tokens, GRAPH_OVERLAP_TOKENS) : m->overlap_tokens) ? 1 : 0)) {}
+    static int mode(const Model* m, int tokens) {
+        if (m->overlap_tokens < 0) return 0;
+        return !m->capturing && tokens <= m->overlap_tokens ? 1 : 2;
+    }
+    OverlapScope(const Model* m, int tokens) : before(s1_set_dependent_launch(mode(m, tokens))) {}
     ~OverlapScope() { s1_set_dependent_launch(before); }
 };
 
@@ -679,7 +686,7 @@ int s1_model_create(const S1Config* cfg, int device, void** out) {
     }
     const char* flag = getenv("CUA_S1_GRAPH");
     m->graph_enabled = flag && strcmp(flag, "1") == 0;
-    if (const char* n = getenv("S1_PDL_TOKENS")) m->overlap_tokens = atoi(n) > 0 ? atoi(n) : 0;
+    if (const char* n = getenv("S1_PDL_TOKENS")) m->overlap_tokens = atoi(n) >= 0 ? atoi(n) : -1;
     *out = m;
     return 0;
 }
@@ -780,7 +787,8 @@ int s1_model_set_exact_packing(void* model, int on) {
 
 int s1_model_set_overlap_tokens(void* model, int tokens) {
     Model* m = static_cast<Model*>(model);
-    if (!m || tokens < 0) return S1_ERR_ARGUMENT;
+    if (!m) return S1_ERR_ARGUMENT;
+    if (tokens < 0) tokens = -1;
     if (m->overlap_tokens != tokens) clear_graphs(m);
     m->overlap_tokens = tokens;
     return 0;

@@ -933,7 +933,7 @@ int launch(const void* x, const void* w, void* y, int M, int N, int K, int ldy, 
         attr[n].val.clusterDim.z = 1;
         n++;
     }
-    if (dep_launch_enabled()) {
+    if (dep_launch_gemm()) {
         attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[n].val.programmaticStreamSerializationAllowed = 1;
         n++;
@@ -1071,7 +1071,7 @@ int launch_pair(const void* x, const void* w, void* y, int M, int N, int K, int 
     const int units = ((M + 2 * BM - 1) / (2 * BM)) * ((N + bn - 1) / bn) * plan.splits;
     const int grid = plan.mode == 1 ? 2 * pairs : 2 * (units < pairs ? units : pairs);
     const int vec_ok = (ldy % 8 == 0) && aligned16(y);
-    return launch_dep(gemm_tc5_pair_kernel, grid, GEMM_THREADS, PAIR_SMEM, st, mx, mw, static_cast<bf16*>(y), M, N, K, ldy,
+    return launch_dep_gemm(gemm_tc5_pair_kernel, grid, GEMM_THREADS, PAIR_SMEM, st, mx, mw, static_cast<bf16*>(y), M, N, K, ldy,
                       vec_ok, bn, plan.splits, plan.mode, static_cast<float*>(partials), counters, 0);
 }
 
@@ -1106,7 +1106,7 @@ int launch_pair_swiglu(const void* x, const void* w, void* act, int M, int I, in
     const long tiles = num_m * ((I + bn / 2 - 1) / (bn / 2));
     const int grid = 2 * (int)(tiles < pairs ? tiles : pairs);
     const int vec_ok = (ld % 8 == 0) && aligned16(act);
-    return launch_dep(gemm_tc5_pair_kernel, grid, GEMM_THREADS, PAIR_SMEM, st, mx, mw, static_cast<bf16*>(act), M, I, K, ld,
+    return launch_dep_gemm(gemm_tc5_pair_kernel, grid, GEMM_THREADS, PAIR_SMEM, st, mx, mw, static_cast<bf16*>(act), M, I, K, ld,
                       vec_ok, bn, 1, 0, static_cast<float*>(nullptr), static_cast<int*>(nullptr), 1);
 }
 

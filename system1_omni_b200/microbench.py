@@ -362,7 +362,7 @@ def latency(b, out):
         row = {"op": "prefill_latency", "model": "4B-shaped", "tokens": T}
         # graph replay and eager issue with the executor's defaults, and eager issue in plain stream
         # order (no kernel launched as a programmatic dependent of the one before)
-        for key, graphs, limit in (("ms", True, 512), ("ms_eager", False, 512), ("ms_eager_stream_order", False, 0)):
+        for key, graphs, limit in (("ms", True, 128), ("ms_eager", False, 128), ("ms_eager_stream_order", False, -1)):
             if T > 2048 and key != "ms":
                 continue
             model.enable_graphs(graphs)
@@ -377,7 +377,7 @@ def latency(b, out):
             e1.record(stream)
             model.synchronize()
             row[key] = e0.elapsed_ms(e1) / n
-        model.set_overlap_tokens(512)
+        model.set_overlap_tokens(128)
         row.update({"tokens_per_s": T / row["ms"] * 1e3, "weights_once_through_hbm_ms": floor_ms})
         out(row)
     model.close()

@@ -227,7 +227,8 @@ class Model:
         L.check(L.load().s1_model_set_exact_packing(self.handle, int(on)), "exact packing")
 
     def set_overlap_tokens(self, tokens):
-        """Passes of at most `tokens` tokens launch their kernels as programmatic dependents of one another."""
+        """Passes of at most `tokens` tokens launch every kernel as a programmatic dependent of the one
+        before it, longer ones only the GEMMs; tokens < 0: plain stream order."""
         L.check(L.load().s1_model_set_overlap_tokens(self.handle, int(tokens)), "overlap tokens")
 
     def set_fused_mlp(self, on=True):

@@ -113,23 +113,24 @@ def test_exact_packing_on_a_shape_that_splits_k(cs1):
 
 
 def test_dependent_launch_changes_no_bit(setup):
-    """Short passes launch their kernels as programmatic dependents of one another (each sets up,
-    and the GEMMs fetch weight tiles, while the kernel before still runs): the same bits as plain
-    stream order, eager and replayed, over repeated runs."""
+    """Passes launch their kernels (short ones all of them, long ones the GEMMs) as programmatic
+    dependents of the kernel before (each sets up, and the GEMMs fetch weight tiles, while that one
+    still runs): the same bits as plain stream order, eager and replayed, over repeated runs."""
     cfg, weights, model = setup
     rng = np.random.default_rng(9)
     prompts = [rng.integers(0, cfg.vocab, n).tolist() for n in (70, 3, 129)]
-    model.set_overlap_tokens(0)
+    model.set_overlap_tokens(-1)                 # plain stream order
     plain, plain_layers = model.forward_batch(prompts, want_layers=True)
     try:
-        model.set_overlap_tokens(1 << 20)
-        for _ in range(4):
-            got, layers = model.forward_batch(prompts, want_layers=True)
-            assert np.array_equal(got, plain)
-            for a, b in zip(layers, plain_layers):
-                assert np.array_equal(a, b)
-        short = prompts[:2]                      # a recorded pass overlaps only up to 128 tokens
-        model.set_overlap_tokens(0)
+        for limit in (1 << 20, 0):               # every kernel a dependent; the GEMMs only
+            model.set_overlap_tokens(limit)
+            for _ in range(4):
+                got, layers = model.forward_batch(prompts, want_layers=True)
+                assert np.array_equal(got, plain)
+                for a, b in zip(layers, plain_layers):
+                    assert np.array_equal(a, b)
+        short = prompts[:2]                      # a recorded pass makes every kernel a dependent only up to 128 tokens
+        model.set_overlap_tokens(-1)
         plain_short = model.forward_batch(short)
         model.set_overlap_tokens(1 << 20)
         model.enable_graphs(True)
@@ -139,7 +140,7 @@ def test_dependent_launch_changes_no_bit(setup):
         assert model.graph_stats()["replays"] >= 6
     finally:
         model.enable_graphs(False)
-        model.set_overlap_tokens(512)
+        model.set_overlap_tokens(128)
     from system1_omni_b200 import lib as L
     assert L.gemm_status() == 0 and L.attn_status() == 0 and L.gdn_status() == 0
 
