@@ -28,7 +28,8 @@ int s1_download_async(void* dst, const void* src, size_t bytes, void* stream);
 int s1_memset_async(void* dst, int value, size_t bytes, void* stream);
 int s1_device_sync(void);
 /* Programmatic dependent launch for the calling host thread's later launches of this library's
- * kernels: mode 1 = every hot-path kernel, 2 = the GEMMs only, 0 = plain stream order. A kernel
+ * kernels: mode 1 = every hot-path kernel but the two delta-rule kernels, 2 = the GEMMs and the
+ * norms, 0 = plain stream order. A kernel
  * launched so may become resident while the kernel before it on the stream still runs, sets up
  * (the GEMMs also fetch their first weight tiles) and waits for that kernel to complete before it
  * touches activations. Results are the same bits in every mode. Returns the previous mode. The
@@ -132,7 +133,7 @@ int s1_model_set_exact_packing(void* model, int on);
 int s1_model_set_fused_mlp(void* model, int on);
 /* Forward passes of at most `tokens` tokens that are issued eagerly launch every kernel as a
  * programmatic dependent of the one before it (s1_set_dependent_launch mode 1); longer ones, and
- * every pass recorded into a CUDA graph, only the GEMMs (mode 2); tokens < 0: plain stream order
+ * every pass recorded into a CUDA graph, only the GEMMs and norms (mode 2); tokens < 0: plain stream order
  * always. Default 128 (S1_PDL_TOKENS in the environment at s1_model_create). With few tokens and
  * eager issue the gaps between launches are what there is to hide; otherwise short kernels' blocks
  * that only wait take room from the running GEMM, while a GEMM's early blocks fetch their first

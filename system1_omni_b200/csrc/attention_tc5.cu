@@ -426,7 +426,7 @@ int launch_attn(const AttnMaps& maps, const bf16* gate, bf16* out, int T, int Hq
     constexpr float LOG2E = 1.4426950408889634f;
     const dim3 grid((T - q_base + ABM - 1) / ABM, Hq);
     const int vec_ok = aligned16(out) && (!GATED || aligned16(gate));
-    return launch_dep(attn_tc5_kernel<DH, GATED, CAUSAL>, grid, ATHREADS, G::SMEM, st, maps, gate, out, T, Hq, Hk, scale * LOG2E,
+    return launch_dep_family(DEP_ATTENTION, attn_tc5_kernel<DH, GATED, CAUSAL>, grid, ATHREADS, G::SMEM, st, maps, gate, out, T, Hq, Hk, scale * LOG2E,
                       q_base, own_base, vec_ok);
 }
 

@@ -97,17 +97,18 @@ inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 // writes - overlaps the kernels before it; the order of all other memory effects is that of
 // ordinary stream order, since grid_dep_sync() returns only when the kernel before is complete
 // and its writes are visible, and that kernel in turn waited for the one before it.
-// The switch is per host thread and has three settings: every hot-path kernel (the executor's
-// choice for short prompts, where launch gaps, prologues and the first trip to HBM are a large
-// part of every kernel), the GEMMs only (its choice for long ones: measured at 1024 tokens +3 %,
-// where making every kernel a dependent costs 1 %: the short kernels' blocks that only wait take
-// room from the running GEMM, while a GEMM's blocks that arrive early fetch their first ring of
-// weight tiles under the short kernel ahead), or none. S1_PDL=1 / 2 / 0 in the environment force one.
+// The switch is per host thread and has three settings: nearly every hot-path kernel (the
+// executor's choice for short prompts issued eagerly, where launch gaps, prologues and the first
+// trip to HBM are a large part of every kernel), the GEMMs and the norms after them (its choice
+// otherwise: measured at 1024 tokens +3 %, where making every kernel a dependent costs 1 %: blocks
+// that only wait take room from the running kernel, while a GEMM's blocks that arrive early fetch
+// their first ring of weight tiles under the short kernel ahead), or none. S1_PDL=1 / 2 / 0 in the
+// environment force one.
 // Both instructions are no-ops in a kernel launched the ordinary way.
 __device__ __forceinline__ void grid_dep_sync() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// The switch: 0 = plain stream order, 1 = every hot-path kernel, 2 = the GEMMs only.
+// The switch: 0 = plain stream order, 1 = every hot-path kernel but the delta-rule pair, 2 = the GEMMs and norms.
 inline int& dep_launch_switch() {
     static thread_local int mode = 0;
     return mode;
@@ -120,8 +121,27 @@ inline int dep_launch_mode() {
     }();
     return forced >= 0 ? forced : dep_launch_switch();
 }
-inline bool dep_launch_enabled() { return dep_launch_mode() == 1; }
-inline bool dep_launch_gemm() { return dep_launch_mode() >= 1; }
+// Kernel families, for the choice of which launches become dependents.
+enum DepFamily { DEP_GEMM = 1, DEP_GDN = 2, DEP_ATTENTION = 4, DEP_NORM = 8, DEP_OTHER = 16 };
+// What the two modes cover, from measurements on the 4B-shaped decoder: the delta-rule kernels are
+// never launched as dependents (their blocks take nearly all of an SM's shared memory while they
+// wait: -4 % at 1024 tokens, and short passes are faster without them too); mode 1 takes everything
+// else, mode 2 the GEMMs and the norms that follow them. S1_PDL_MASK1 / S1_PDL_MASK override, for
+// experiments.
+inline int dep_launch_mask(int mode) {
+    static const int mask1 = [] {
+        const char* e = getenv("S1_PDL_MASK1");
+        return e ? atoi(e) : (int)(DEP_GEMM | DEP_ATTENTION | DEP_NORM | DEP_OTHER);
+    }();
+    static const int mask2 = [] {
+        const char* e = getenv("S1_PDL_MASK");
+        return e ? atoi(e) : (int)(DEP_GEMM | DEP_NORM);
+    }();
+    return mode == 1 ? mask1 : mode == 2 ? mask2 : 0;
+}
+inline bool dep_launch_family(int family) { return (dep_launch_mask(dep_launch_mode()) & family) != 0; }
+inline bool dep_launch_enabled() { return dep_launch_family(DEP_OTHER); }
+inline bool dep_launch_gemm() { return dep_launch_family(DEP_GEMM); }
 
 template <typename... KArgs, typename... Args>
 cudaError_t launch_maybe_dep(bool dependent, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
@@ -141,6 +161,11 @@ cudaError_t launch_maybe_dep(bool dependent, void (*kernel)(KArgs...), dim3 grid
 template <typename... KArgs, typename... Args>
 cudaError_t launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
     return launch_maybe_dep(dep_launch_enabled(), kernel, grid, block, smem, st, args...);
+}
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dep_family(int family, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args... args) {
+    return launch_maybe_dep(dep_launch_family(family), kernel, grid, block, smem, st, args...);
 }
 template <typename... KArgs, typename... Args>
 cudaError_t launch_dep_gemm(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {

@@ -401,10 +401,10 @@ int conv_gates(Model* m, const Layer& ly, size_t off, int len) {
 // once over the packed rows; conv, delta rule, attention prep and attention run per sequence.
 // dump (nullable, host) receives the residual stream after each layer.
 // Dependent launch for the launches of one pass, put back on every way out. Short passes make
-// every kernel a programmatic dependent of the one before it, longer ones only the GEMMs (their
+// (nearly) every kernel a programmatic dependent of the one before it, longer ones the GEMMs and norms (a GEMM's
 // blocks arrive under the short kernel ahead and fetch their first ring of weight tiles there);
 // overlap_tokens < 0 keeps plain stream order. Measured on the 4B-shaped decoder (ms per pass,
-// plain / every kernel / GEMMs only): issued eagerly 3.81 / 3.29 / 3.45 at 64 tokens, 4.22 / 3.72 /
+// plain / every kernel / GEMMs only; leaving out the delta-rule kernels and adding the norms gained 2-5 % more): issued eagerly 3.81 / 3.29 / 3.45 at 64 tokens, 4.22 / 3.72 /
 // 3.78 at 128, 4.70 / 4.41 / 4.27 at 256, 9.34 / 9.06 / 9.09 at 1024; replayed from a graph, where
 // the gaps between launches are small already, 3.11 / 3.17 / 2.93 at 64, 4.02 / 4.29 / 3.85 at 256,
 // 8.69 / 8.88 / 8.50 at 1024, no difference from 4096 on. So an eager pass of up to overlap_tokens

@@ -1138,7 +1138,7 @@ int gdn_run(const void* q, const void* k, const void* v, const float* g, const v
         if (e != cudaSuccess) return e;
         CUtensorMap map_v;  // [64 rows, 64 columns] boxes, 128-byte swizzle
         if (!tensor_map_2d(v, (uint64_t)T, (uint64_t)H * D, (uint64_t)H * D, C, &map_v)) return CS1_ERR_TENSOR_MAP;
-        launch_dep(gdn_prep_tc5, dim3((NC + 1) / 2, H), PREP2_THREADS, PREP2_SMEM, st, map_v, static_cast<const bf16*>(q), static_cast<const bf16*>(k), g, static_cast<const bf16*>(beta), ws, T, H, HK, NC, scale);
+        launch_dep_family(DEP_GDN, gdn_prep_tc5, dim3((NC + 1) / 2, H), PREP2_THREADS, PREP2_SMEM, st, map_v, static_cast<const bf16*>(q), static_cast<const bf16*>(k), g, static_cast<const bf16*>(beta), ws, T, H, HK, NC, scale);
     } else {
         // v and k rows of a chunk as [64 rows, 128 columns] tiles of the caller's [T, heads, 128] arrays
         CUtensorMap map_k, map_v;
@@ -1154,11 +1154,11 @@ int gdn_run(const void* q, const void* k, const void* v, const float* g, const v
     if (ws.vs == 32) {
         e = set_smem_once(gdn_scan<32, 8>, ScanSmem<32>::BYTES, scan32_done);
         if (e != cudaSuccess) return e;
-        launch_dep(gdn_scan<32, 8>, dim3(H, D / 32), 256, ScanSmem<32>::BYTES, st, ws, static_cast<bf16*>(o), T, H, NC, si, so);
+        launch_dep_family(DEP_GDN, gdn_scan<32, 8>, dim3(H, D / 32), 256, ScanSmem<32>::BYTES, st, ws, static_cast<bf16*>(o), T, H, NC, si, so);
     } else {
         e = set_smem_once(gdn_scan<16, 4>, ScanSmem<16>::BYTES, scan16_done);
         if (e != cudaSuccess) return e;
-        launch_dep(gdn_scan<16, 4>, dim3(H, D / 16), 128, ScanSmem<16>::BYTES, st, ws, static_cast<bf16*>(o), T, H, NC, si, so);
+        launch_dep_family(DEP_GDN, gdn_scan<16, 4>, dim3(H, D / 16), 128, ScanSmem<16>::BYTES, st, ws, static_cast<bf16*>(o), T, H, NC, si, so);
     }
     return cudaGetLastError();
 }

@@ -94,10 +94,10 @@ int launch_norm(void* residual, const void* delta, const void* w, void* out, int
     if (packed) {
         const int per = (D / 8 + NORM_THREADS - 1) / NORM_THREADS;
         switch (per) {
-            case 1: launch_dep(rms_norm_packed_kernel<ADD, 1>, rows, NORM_THREADS, 0, st, r, d, wp, o, D, eps); break;
-            case 2: launch_dep(rms_norm_packed_kernel<ADD, 2>, rows, NORM_THREADS, 0, st, r, d, wp, o, D, eps); break;
-            case 3: launch_dep(rms_norm_packed_kernel<ADD, 3>, rows, NORM_THREADS, 0, st, r, d, wp, o, D, eps); break;
-            default: launch_dep(rms_norm_packed_kernel<ADD, 4>, rows, NORM_THREADS, 0, st, r, d, wp, o, D, eps); break;
+            case 1: launch_dep_family(DEP_NORM, rms_norm_packed_kernel<ADD, 1>, rows, NORM_THREADS, 0, st, r, d, wp, o, D, eps); break;
+            case 2: launch_dep_family(DEP_NORM, rms_norm_packed_kernel<ADD, 2>, rows, NORM_THREADS, 0, st, r, d, wp, o, D, eps); break;
+            case 3: launch_dep_family(DEP_NORM, rms_norm_packed_kernel<ADD, 3>, rows, NORM_THREADS, 0, st, r, d, wp, o, D, eps); break;
+            default: launch_dep_family(DEP_NORM, rms_norm_packed_kernel<ADD, 4>, rows, NORM_THREADS, 0, st, r, d, wp, o, D, eps); break;
         }
     } else {
         rms_norm_scalar_kernel<ADD><<<rows, NORM_THREADS, 0, st>>>(r, d, wp, o, D, eps);
@@ -198,7 +198,7 @@ extern "C" int cs1_gated_rms_norm(const void* x, const void* z, int ldz, const v
     if (rows > 0x7fffffffLL) return cudaErrorInvalidValue;
     const bf16 *xp = static_cast<const bf16*>(x), *zp = static_cast<const bf16*>(z), *wp = static_cast<const bf16*>(w);
     if (ldz % 8 == 0 && aligned16(x) && aligned16(z) && aligned16(w) && aligned16(out)) {
-        launch_dep(gated_rms_norm_kernel, (unsigned)((rows + GN_ROWS_PER_BLOCK - 1) / GN_ROWS_PER_BLOCK), GN_GROUPS * 16, 0,
+        launch_dep_family(DEP_NORM, gated_rms_norm_kernel, (unsigned)((rows + GN_ROWS_PER_BLOCK - 1) / GN_ROWS_PER_BLOCK), GN_GROUPS * 16, 0,
                    as_stream(stream), xp, zp, ldz, wp, static_cast<bf16*>(out), (int)rows, H, eps);
     } else {
         gated_rms_norm_scalar_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, as_stream(stream)>>>(
