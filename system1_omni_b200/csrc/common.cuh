@@ -55,6 +55,12 @@ __device__ __forceinline__ uint4 pack8(const float (&in)[8]) {
 
 __device__ __forceinline__ uint4 ld16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 __device__ __forceinline__ void st16(void* p, const uint4& v) { *reinterpret_cast<uint4*>(p) = v; }
+// 32 bytes (a whole sector) in one store; p must be 32-byte aligned.
+__device__ __forceinline__ void st32(void* p, const uint4& a, const uint4& b) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w),
+                 "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+                 : "memory");
+}
 // Streaming variants for data touched once: keep it out of L1 and mark it evict-first.
 __device__ __forceinline__ uint4 ld16_stream(const void* p) {
     uint4 v;

@@ -221,14 +221,20 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 } else if (row < M && col0 < N) {
                     bf16* dst = y + (size_t)row * ldy + col0;
                     if (vec_ok && col0 + 32 <= N) {
+                        uint4 o[4];
 #pragma unroll
                         for (int j = 0; j < 4; j++) {
-                            uint4 o;
-                            o.x = pack2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
-                            o.y = pack2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
-                            o.z = pack2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
-                            o.w = pack2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
-                            st16(dst + 8 * j, o);
+                            o[j].x = pack2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+                            o[j].y = pack2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+                            o[j].z = pack2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+                            o[j].w = pack2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+                        }
+                        if (vec_ok == 2) {  // whole 32-byte sectors per store
+                            st32(dst, o[0], o[1]);
+                            st32(dst + 16, o[2], o[3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 4; j++) st16(dst + 8 * j, o[j]);
                         }
                     } else {
 #pragma unroll
@@ -576,14 +582,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                             o32[j] = rbf(silu_fast(rbf(__uint_as_float(g[j])))) * rbf(__uint_as_float(u[j]));
                         bf16* dst = y + (size_t)row * ldy + col0;
                         if (vec_ok && col0 + 32 <= N) {
+                            uint4 o[4];
 #pragma unroll
                             for (int j = 0; j < 4; j++) {
-                                uint4 o;
-                                o.x = pack2(o32[8 * j + 0], o32[8 * j + 1]);
-                                o.y = pack2(o32[8 * j + 2], o32[8 * j + 3]);
-                                o.z = pack2(o32[8 * j + 4], o32[8 * j + 5]);
-                                o.w = pack2(o32[8 * j + 6], o32[8 * j + 7]);
-                                st16(dst + 8 * j, o);
+                                o[j].x = pack2(o32[8 * j + 0], o32[8 * j + 1]);
+                                o[j].y = pack2(o32[8 * j + 2], o32[8 * j + 3]);
+                                o[j].z = pack2(o32[8 * j + 4], o32[8 * j + 5]);
+                                o[j].w = pack2(o32[8 * j + 6], o32[8 * j + 7]);
+                            }
+                            if (vec_ok == 2) {
+                                st32(dst, o[0], o[1]);
+                                st32(dst + 16, o[2], o[3]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 4; j++) st16(dst + 8 * j, o[j]);
                             }
                         } else {
 #pragma unroll
@@ -694,14 +706,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                 } else if (row < M && col0 < N) {
                     bf16* dst = y + (size_t)row * ldy + col0;
                     if (vec_ok && col0 + 32 <= N) {
+                        uint4 o[4];
 #pragma unroll
                         for (int j = 0; j < 4; j++) {
-                            uint4 o;
-                            o.x = pack2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
-                            o.y = pack2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
-                            o.z = pack2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
-                            o.w = pack2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
-                            st16(dst + 8 * j, o);
+                            o[j].x = pack2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+                            o[j].y = pack2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+                            o[j].z = pack2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+                            o[j].w = pack2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+                        }
+                        if (vec_ok == 2) {  // whole 32-byte sectors per store
+                            st32(dst, o[0], o[1]);
+                            st32(dst + 16, o[2], o[3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 4; j++) st16(dst + 8 * j, o[j]);
                         }
                     } else {
 #pragma unroll
@@ -871,6 +889,12 @@ DeviceInfo* device_info(cudaError_t* err) {
     return &info[dev];
 }
 
+// How the epilogue may store a row's 32-column chunk: 2 = 32-byte stores (whole sectors), 1 = 16-byte, 0 = by element.
+int store_width(const void* y, int ldy) {
+    if (ldy % 16 == 0 && (reinterpret_cast<uintptr_t>(y) & 31) == 0) return 2;
+    return ldy % 8 == 0 && aligned16(y) ? 1 : 0;
+}
+
 template <int BN>
 cudaError_t prepare(DeviceInfo* info, int slot) {
     if (info->smem_set[slot]) return cudaSuccess;
@@ -918,7 +942,7 @@ int launch(const void* x, const void* w, void* y, int M, int N, int K, int ldy, 
     CUtensorMap mx, mw;
     if (!tensor_map(x, M, K, BM, &mx) || !tensor_map(w, N, K, BN, &mw)) return CS1_ERR_TENSOR_MAP;
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    const int vec_ok = (ldy % 8 == 0) && aligned16(y);
+    const int vec_ok = store_width(y, ldy);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(splits > 1 ? tiles * splits : (tiles < info->sms ? tiles : info->sms));
     cfg.blockDim = dim3(GEMM_THREADS);
@@ -1070,7 +1094,7 @@ int launch_pair(const void* x, const void* w, void* y, int M, int N, int K, int 
     if (!tensor_map(x, M, K, BM, &mx) || !tensor_map(w, N, K, bn / 2, &mw)) return CS1_ERR_TENSOR_MAP;
     const int units = ((M + 2 * BM - 1) / (2 * BM)) * ((N + bn - 1) / bn) * plan.splits;
     const int grid = plan.mode == 1 ? 2 * pairs : 2 * (units < pairs ? units : pairs);
-    const int vec_ok = (ldy % 8 == 0) && aligned16(y);
+    const int vec_ok = store_width(y, ldy);
     return launch_dep_gemm(gemm_tc5_pair_kernel, grid, GEMM_THREADS, PAIR_SMEM, st, mx, mw, static_cast<bf16*>(y), M, N, K, ldy,
                       vec_ok, bn, plan.splits, plan.mode, static_cast<float*>(partials), counters, 0);
 }
@@ -1105,7 +1129,7 @@ int launch_pair_swiglu(const void* x, const void* w, void* act, int M, int I, in
     if (!tensor_map(x, M, K, BM, &mx) || !tensor_map(w, 2 * I, K, bn / 2, &mw)) return CS1_ERR_TENSOR_MAP;
     const long tiles = num_m * ((I + bn / 2 - 1) / (bn / 2));
     const int grid = 2 * (int)(tiles < pairs ? tiles : pairs);
-    const int vec_ok = (ld % 8 == 0) && aligned16(act);
+    const int vec_ok = store_width(act, ld);
     return launch_dep_gemm(gemm_tc5_pair_kernel, grid, GEMM_THREADS, PAIR_SMEM, st, mx, mw, static_cast<bf16*>(act), M, I, K, ld,
                       vec_ok, bn, 1, 0, static_cast<float*>(nullptr), static_cast<int*>(nullptr), 1);
 }
