@@ -31,9 +31,12 @@ __global__ void __launch_bounds__(128) embed_kernel(const int32_t* __restrict__ 
 // One thread owns 8 adjacent channels and walks TT consecutive tokens with the three
 // previous rows held in registers, so each input row is fetched once per token block
 // (plus a 3-row halo) instead of four times.
-constexpr int CONV_TT = 16;
+constexpr int CONV_TT = 16;     // tokens per thread for long inputs
+constexpr int CONV_TT_SHORT = 8; // up to CONV_SHORT_TOKENS tokens: twice the blocks, so that loads and arithmetic of different warps overlap
+constexpr int CONV_SHORT_TOKENS = 2048;
 constexpr int CONV_THREADS = 128;
 
+template <int CONV_TT>
 __device__ __forceinline__ void conv_block(const bf16* __restrict__ qkv, int ld, const bf16* __restrict__ w,
                                            bf16* __restrict__ q, bf16* __restrict__ k, bf16* __restrict__ v, int T,
                                            int key_dim, int value_dim) {
@@ -102,12 +105,13 @@ __device__ __forceinline__ void conv_block(const bf16* __restrict__ qkv, int ld,
     }
 }
 
+template <int TT>
 __global__ void __launch_bounds__(CONV_THREADS)
     gdn_conv_packed_kernel(const bf16* __restrict__ qkv, int ld, const bf16* __restrict__ w, bf16* __restrict__ q,
                            bf16* __restrict__ k, bf16* __restrict__ v, int T, int key_dim, int value_dim) {
     grid_dep_trigger();
     grid_dep_sync();
-    conv_block(qkv, ld, w, q, k, v, T, key_dim, value_dim);
+    conv_block<TT>(qkv, ld, w, q, k, v, T, key_dim, value_dim);
 }
 
 __global__ void gdn_conv_scalar_kernel(const bf16* __restrict__ qkv, int ld, const bf16* __restrict__ w,
@@ -158,6 +162,7 @@ __global__ void gdn_gates_kernel(const bf16* __restrict__ b, const bf16* __restr
 // projection wrote. Blocks with blockIdx.y below conv_blocks are convolution blocks, the row of
 // blocks after them computes the gates of the same CONV_TT tokens. Same arithmetic per element as
 // the two kernels above.
+template <int TT>
 __global__ void __launch_bounds__(CONV_THREADS)
     gdn_conv_gates_kernel(const bf16* __restrict__ qkv, int ld, const bf16* __restrict__ w, bf16* __restrict__ q,
                           bf16* __restrict__ k, bf16* __restrict__ v, int T, int key_dim, int value_dim, int conv_blocks,
@@ -166,11 +171,11 @@ __global__ void __launch_bounds__(CONV_THREADS)
     grid_dep_trigger();
     grid_dep_sync();
     if ((int)blockIdx.y < conv_blocks) {
-        conv_block(qkv, ld, w, q, k, v, T, key_dim, value_dim);
+        conv_block<TT>(qkv, ld, w, q, k, v, T, key_dim, value_dim);
         return;
     }
-    const int first = blockIdx.x * CONV_TT * H;
-    const int end = min((int)(blockIdx.x + 1) * CONV_TT, T) * H;
+    const int first = blockIdx.x * TT * H;
+    const int end = min((int)(blockIdx.x + 1) * TT, T) * H;
     for (int i = first + (int)threadIdx.x; i < end; i += CONV_THREADS) gate_element(b, a, ld, A_log, dt_bias, beta, g, i, H);
 }
 
@@ -257,10 +262,11 @@ extern "C" int cs1_gdn_conv(const void* qkv, int ld, const void* w, void* q, voi
     const bool packed = key_dim % 8 == 0 && value_dim % 8 == 0 && ld % 8 == 0 && aligned16(qkv) && aligned16(w) &&
                         aligned16(q) && aligned16(k) && aligned16(v);
     if (packed) {
-        const dim3 grid((T + CONV_TT - 1) / CONV_TT, (channels / 8 + CONV_THREADS - 1) / CONV_THREADS);
-        launch_dep(gdn_conv_packed_kernel, grid, CONV_THREADS, 0, as_stream(stream), static_cast<const bf16*>(qkv), ld,
-                   static_cast<const bf16*>(w), static_cast<bf16*>(q), static_cast<bf16*>(k), static_cast<bf16*>(v), T,
-                   key_dim, value_dim);
+        const int tt = T <= CONV_SHORT_TOKENS ? CONV_TT_SHORT : CONV_TT;
+        const dim3 grid((T + tt - 1) / tt, (channels / 8 + CONV_THREADS - 1) / CONV_THREADS);
+        launch_dep(tt == CONV_TT ? gdn_conv_packed_kernel<CONV_TT> : gdn_conv_packed_kernel<CONV_TT_SHORT>, grid, CONV_THREADS, 0,
+                   as_stream(stream), static_cast<const bf16*>(qkv), ld, static_cast<const bf16*>(w), static_cast<bf16*>(q),
+                   static_cast<bf16*>(k), static_cast<bf16*>(v), T, key_dim, value_dim);
     } else {
         gdn_conv_scalar_kernel<<<blocks_for(n), THREADS, 0, as_stream(stream)>>>(
             static_cast<const bf16*>(qkv), ld, static_cast<const bf16*>(w), static_cast<bf16*>(q),
@@ -291,8 +297,10 @@ extern "C" int s1_gdn_conv_gates(const void* qkv, int ld, const void* w, void* q
                         aligned16(q) && aligned16(k) && aligned16(v);
     if (!packed || channels == 0 || H == 0 || (long long)T * H > 0x7fffffffLL) return CS1_ERR_UNSUPPORTED;
     const int conv_blocks = (channels / 8 + CONV_THREADS - 1) / CONV_THREADS;
-    const dim3 grid((T + CONV_TT - 1) / CONV_TT, conv_blocks + 1);
-    launch_dep(gdn_conv_gates_kernel, grid, CONV_THREADS, 0, as_stream(stream), static_cast<const bf16*>(qkv), ld,
+    const int tt = T <= CONV_SHORT_TOKENS ? CONV_TT_SHORT : CONV_TT;
+    const dim3 grid((T + tt - 1) / tt, conv_blocks + 1);
+    launch_dep(tt == CONV_TT ? gdn_conv_gates_kernel<CONV_TT> : gdn_conv_gates_kernel<CONV_TT_SHORT>, grid, CONV_THREADS, 0,
+               as_stream(stream), static_cast<const bf16*>(qkv), ld,
                static_cast<const bf16*>(w), static_cast<bf16*>(q), static_cast<bf16*>(k), static_cast<bf16*>(v), T, key_dim,
                value_dim, conv_blocks, static_cast<const bf16*>(b), static_cast<const bf16*>(a),
                static_cast<const bf16*>(A_log), static_cast<const bf16*>(dt_bias), static_cast<bf16*>(beta), g, H);

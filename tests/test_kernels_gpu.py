@@ -123,7 +123,7 @@ def test_embed_copies_rows(cs1, stream):
 def test_gdn_conv_matches_reference(cs1, stream, kd, vd, extra):
     ch = 2 * kd + vd
     ld = ch + extra
-    for T in (1, 2, 3, 4, 17, 67):
+    for T in (1, 2, 3, 4, 17, 67) + ((2100,) if kd <= 24 else ()):      # above 2048 tokens: 16 tokens per thread
         x = O.random_bf16(T * ld, 61, 2.0)
         w = O.random_bf16(ch * 4, 62, 0.7)
         xd, wd = dev(x, stream), dev(w, stream)
@@ -182,7 +182,7 @@ def test_gdn_gates_match_reference(cs1, stream):
         assert np.all(got <= 0) and np.allclose(got, wg, rtol=2e-6, atol=1e-30)
 
 
-@pytest.mark.parametrize("T", [1, 15, 16, 17, 67, 300])
+@pytest.mark.parametrize("T", [1, 7, 8, 9, 15, 16, 17, 67, 300, 2100])
 @pytest.mark.parametrize("kd,vd,H", [(2048, 4096, 32), (256, 512, 4), (128, 384, 3)])
 def test_gdn_conv_and_gates_in_one_launch(cs1, stream, T, kd, vd, H):
     """The executor's fused launch against cs1_gdn_conv then cs1_gdn_gates on the rows of one input
