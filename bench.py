@@ -210,13 +210,22 @@ def main():
 
     dist = torch = None
     if world > 1:
-        # whatever NCCL logs (its version banner, when the environment asks for one) goes to stderr:
-        # stdout carries the one JSON line
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # Whatever NCCL prints while its communicator comes up (a version banner, when the environment
+        # asks for one) goes to stderr: stdout carries the one JSON line.
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
 
     from system1_omni_b200 import lib as L
     from system1_omni_b200 import model as M
