@@ -1,25 +1,33 @@
-"""Prefill throughput of the Qwen3.5-style hybrid decoder on B200, one process per GPU.
+"""Prefill throughput of the 27B-shaped Qwen3.5-style hybrid decoder on B200, one process per GPU.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Workload (every N): the 4B-shaped decoder of BASELINE.json's second config - 32 layers, three
-Gated DeltaNet to one gated GQA attention layer, hidden 2560, MLP 9728, vocab 151936, bf16
-weights N(0, 0.02) generated on the device - prefilling one request of 1024 uniform-random
-token ids per GPU (weak scaling: requests shard across GPUs with replicated weights; the
-only exchange is the gather of the 16 decision logits to rank 0). A step is one prefill.
+Workload: 64 layers, three Gated DeltaNet to one gated GQA attention layer, hidden 5120, MLP
+17408, 16 qk / 48 v delta-rule heads, 24 q / 4 kv attention heads of 128, vocab 151936, bf16
+weights N(0, 0.02) generated on each GPU (replicated). One seeded list of 64 request lengths,
+log-uniform on [512, 16384]; a run on N GPUs takes its first 8 N requests (N = 8 is the whole
+list; the work per GPU stays the same, hence weak scaling), assigns whole requests to ranks
+longest-first on the cost a T + b T^2 (fitted from this run's own pack times), and every rank
+prefills its share in packs of at most 16 prompts / 4096 tokens through the library's
+dispatcher (include/s1_dispatch.h: C++, NCCL bound at run time; this file imports no torch).
+A float64 host head gives 16 decision logits per request, gathered to rank 0 in request order.
+A step is one pass over the rank's share.
 
 One JSON line on rank 0:
-  value      tokens/s over all GPUs with the ids already in HBM, device-timed (CUDA events on
-             the executor's stream, max over ranks)
-  e2e        the same through the public call with host buffers: pinned ids -> H2D -> layers ->
-             last row D2H -> float64 head on the host (-> NCCL gather of logits when N > 1)
-  roofline   the dominant kernel family (the bf16 GEMMs): algorithmic FLOPs per step over its
-             device time, measured with events around every launch in profiled steps
+  value      prompt tokens of all ranks per second with the ids already in HBM: CUDA events on
+             the executor's stream around K steps, the maximum over ranks
+  e2e        the same from ids in pinned host memory to logits on rank 0: H2D of every pack's
+             ids, layers, last rows D2H, head, NCCL gather; wall clock, the maximum over ranks
+  roofline   the bf16 GEMM family: algorithmic FLOPs of this rank's tokens over the family's
+             device time (events around every launch of one eager profiled step)
+  balance    per-rank tokens and busy milliseconds, their max / mean, the gather's microseconds
+  dispatch_check  rank 0 runs packs of another rank again through the public call and compares
+             the logits bit for bit with what the gather delivered
   cpu_baseline  the CPU oracle (a port of the reference's arithmetic, OpenMP) on a bounded
              sample of the same workload, N = 1 only
---impl reference times that CPU oracle as the reference arm (the reference has no CPU
-forward pass of its own: its CPU code for this path is the float64 test oracles the port restates).
+--impl reference times that CPU oracle as the reference arm (the reference has no CPU forward
+pass of its own: its CPU code for this path is the float64 test oracles the port restates).
 """
 import argparse
 import ctypes as C
@@ -36,25 +44,38 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-TOKENS = 1024
 N_CLASSES = 16
-WORKLOAD = ("cfg2: 4B-shaped hybrid decoder (32 layers 3:1 GDN/attention, hidden 2560, MLP 9728, vocab 151936, "
-            "16-class head), 1 request x 1024 uniform-random ids per GPU")
-# DRAM bytes of one launch of the pair kernel (ncu, dram__bytes_read.sum + dram__bytes_write.sum) on the
-# widest projection of this workload; the capture and its command are under profiles/.
-GEMM_TRAFFIC = {"bytes": 72.9e6,
-                "of": "one launch, y[1024,12352] = x[1024,2560] w^T (GDN in_proj): algorithmic 93.7e6 bytes "
-                      "(x 5.2e6 + w 63.2e6 + y 25.3e6, most of y still in L2 when the launch ends)"}
+REQUESTS_TOTAL = 64
+REQUESTS_PER_GPU = 8
+LENGTH_SEED = 20260
+SAMPLE_TOKENS = 1024        # the CPU arms' sample: one 4-layer period at this many tokens
+WORKLOAD = ("cfg4: 27B-shaped hybrid decoder (64 layers 3:1 GDN/attention, hidden 5120, MLP 17408, 16 qk / 48 v GDN "
+            "heads, 24 q / 4 kv heads of 128, vocab 151936, 16-class head), 64 requests log-uniform on [512, 16384] "
+            f"(seed {LENGTH_SEED}), the first 8 per GPU, token-balanced over the GPUs, logits gathered to rank 0")
 FAMILIES = ["gemm", "gdn_prefill", "attention", "gdn_conv", "gdn_gates", "rms_norm", "gated_rms_norm", "silu_mul",
             "attn_prep", "other"]
+# DRAM bytes of one launch of the pair kernel (ncu, dram__bytes_read.sum + dram__bytes_write.sum) on the
+# widest projection of this workload at one full pack; the capture and its command are under profiles/.
+GEMM_TRAFFIC = {"bytes": None, "of": "no capture of a 27B-shaped launch yet"}
 
 
-def cfg2(layers=32):
+def cfg4(layers=64):
     from system1_omni_b200.model import Config
     types = [("full_attention" if (i + 1) % 4 == 0 else "linear_attention") for i in range(layers)]
-    return Config(hidden=2560, intermediate=9728, layer_types=types, heads=16, kv_heads=4, head_dim=128,
-                  rotary_half=32, lin_k_heads=16, lin_v_heads=32, vocab=151936, eps=1e-6, rope_theta=1e7,
+    return Config(hidden=5120, intermediate=17408, layer_types=types, heads=24, kv_heads=4, head_dim=128,
+                  rotary_half=32, lin_k_heads=16, lin_v_heads=48, vocab=151936, eps=1e-6, rope_theta=1e7,
                   max_positions=262144)
+
+
+def request_lengths():
+    rng = np.random.default_rng(LENGTH_SEED)
+    return np.exp(rng.uniform(np.log(512), np.log(16384), REQUESTS_TOTAL)).astype(np.int32)
+
+
+def request_ids(lengths, vocab):
+    """All requests' token ids, concatenated in request order; request i has its own seed."""
+    return np.concatenate([np.random.default_rng(1000 + i).integers(0, vocab, int(n)).astype(np.int32)
+                           for i, n in enumerate(lengths)])
 
 
 def gemm_flops_per_token(cfg):
@@ -127,22 +148,28 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+_CPU_WEIGHTS = {}
+
+
 def cpu_sample(periods=1, seed=0):
     """The CPU oracle on `periods` x (3 Gated DeltaNet + 1 attention) layers of the workload's
-    shape at 1024 tokens, random hidden states in. Returns (seconds, layers run, threads)."""
+    shape at SAMPLE_TOKENS tokens, random hidden states in, on every host core.
+    Returns (seconds, layers run, threads)."""
     import oracle as O
-    cfg = cfg2(4 * periods)
+    O.set_threads(os.cpu_count() or 1)     # a launcher may have exported OMP_NUM_THREADS=1
+    cfg = cfg4(4 * periods)
     from system1_omni_b200.model import tensor_shapes
-    rng = np.random.default_rng(seed)
-    cache, weights = {}, {}
+    rng = np.random.default_rng(0)
+    weights = {}
     for name, shape in tensor_shapes(cfg).items():
         if name == "embed_tokens.weight":
             weights[name] = np.zeros((1, cfg.hidden), np.uint16)      # not read: hidden states are given
             continue
-        # layers of every period share one set of arrays: the arithmetic and its cost are the same
+        # layers of one kind share one set of arrays (made once per process): the arithmetic and
+        # its cost do not depend on the values
         parts = name.split(".")
-        key = ".".join([str(int(parts[1]) % 4)] + parts[2:]) if parts[0] == "layers" else name
-        if key not in cache:
+        key = ".".join(parts[2:]) if parts[0] == "layers" else name
+        if key not in _CPU_WEIGHTS:
             n = int(np.prod(shape))
             if name.endswith("A_log"):
                 a = rng.uniform(0, np.log(16), n).astype(np.float32)
@@ -152,224 +179,268 @@ def cpu_sample(periods=1, seed=0):
                 a = (1 + rng.normal(0, 0.02, n)).astype(np.float32)
             else:
                 a = rng.standard_normal(n, dtype=np.float32) * np.float32(0.02)
-            cache[key] = O.f32_to_bf16(a).reshape(shape)
-        weights[name] = cache[key]
-    x = O.f32_to_bf16(rng.standard_normal((TOKENS, cfg.hidden), dtype=np.float32))
-    d = cfg.oracle_dict()
+            _CPU_WEIGHTS[key] = O.f32_to_bf16(a).reshape(shape)
+        weights[name] = _CPU_WEIGHTS[key]
+    x = O.f32_to_bf16(np.random.default_rng(seed).standard_normal((SAMPLE_TOKENS, cfg.hidden), dtype=np.float32))
+    d = cfg.shape_dict()
     d["vocab"] = 1
     t0 = time.perf_counter()
-    O.forward(d, weights, None, [TOKENS], x_in=x)
+    O.forward(d, weights, None, [SAMPLE_TOKENS], x_in=x)
     return time.perf_counter() - t0, cfg.n_layers, O.threads()
 
 
-def run_reference(args, rank, world):
+def cpu_line(secs, layers, threads):
+    """tokens/s of the whole decoder from samples of `layers` of its 64 layers."""
+    factor = 64 / layers
+    mean = float(np.mean(secs))
+    value = SAMPLE_TOKENS / (mean * factor)
+    sample = (f"oracle port on all {threads} host threads, {layers} of 64 layers (one 3 GDN + 1 attention period) at "
+              f"{SAMPLE_TOKENS} tokens: measured {mean:.2f} s per sample over {len(secs)} samples, whole decoder = "
+              f"sample x {factor:g} (the sample's attention sees {SAMPLE_TOKENS} keys, the workload's requests up to 16384)")
+    return value, mean * factor, {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample,
+                                  "measured_s_per_sample": mean, "extrapolation_factor": factor}
+
+
+def run_reference(args, rank):
     """The reference arm: the reference project has no CPU forward pass, so its arithmetic as
-    restated by the oracle is timed on the host cores; each step is one period (4 layers) of
-    the 32-layer workload at 1024 tokens, scaled by 32/4."""
+    restated by the oracle is timed on the host cores of this box, once per box (rank 0), on
+    every core; a step is one 4-layer period of the 64-layer workload at SAMPLE_TOKENS tokens."""
     if rank != 0:
         return
     secs = []
     layers = threads = None
     for i in range(args.warmup + args.steps):
-        if i >= 1 and sum(secs) > 240:       # keep the whole run within a few minutes
+        if i >= 1 and sum(secs) > 150:       # keep the whole run within a few minutes
             break
         t, layers, threads = cpu_sample(1, seed=i)
         if i >= min(args.warmup, 1):
             secs.append(t)
-    step = float(np.mean(secs)) * 32 / layers
-    value = TOKENS / step
-    sample = (f"oracle port, {layers} of 32 layers (one 3 GDN + 1 attention period) at {TOKENS} tokens, "
-              f"time x {32 // layers}, {len(secs)} timed samples")
+    value, step_s, cpu = cpu_line(secs, layers, threads)
     line = {"impl": "reference", "metric": "prefill tokens/s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
-            "steps": len(secs), "warmup": min(args.warmup, 1), "ms_per_step": step * 1e3, "higher_is_better": True,
+            "steps": len(secs), "warmup": min(args.warmup, 1), "ms_per_step": step_s * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "layers": 32, "tokens_per_gpu": TOKENS,
+            "config": {"workload": WORKLOAD, "layers": 64,
+                       "note": "one box has one set of host cores: the figure does not grow with the number of GPUs",
                        "weights": "N(0,0.02) bf16, generated on the host"},
-            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+            "cpu_baseline": cpu,
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+def fit_cost(samples):
+    """Least squares of pack milliseconds on (sum T, sum T^2) over every rank's packs; a, b >= 0."""
+    s = np.asarray([r for r in samples if r[2] > 0], np.float64)
+    if len(s) < 2:
+        return None
+    X, y = s[:, :2], s[:, 2]
+    coef, *_ = np.linalg.lstsq(X, y, rcond=None)
+    a, b = float(coef[0]), float(coef[1])
+    if b < 0 or a <= 0:           # not enough spread in this run's lengths to see the quadratic term
+        a, b = float((X[:, 0] @ y) / (X[:, 0] @ X[:, 0])), 0.0
+    return a, b
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--layers", type=int, default=32, help="fewer layers for a quick functional check only")
+    ap.add_argument("--layers", type=int, default=64, help="fewer layers for a quick functional check only")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--graphs", type=int, default=1, help="CUDA-graph replay of the layer loop (0 = eager)")
+    ap.add_argument("--graphs", type=int, default=1, help="CUDA-graph replay of repeated packs (0 = eager)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
-        run_reference(args, rank, world)
+        run_reference(args, rank)
         return
     args.warmup = max(args.warmup, 3)
 
-    dist = torch = None
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local)
-        # Whatever NCCL prints while its communicator comes up (a version banner, when the environment
-        # asks for one) goes to stderr: stdout carries the one JSON line.
-        sys.stdout.flush()
-        saved_stdout = os.dup(1)
-        os.dup2(2, 1)
-        try:
-            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-            dist.barrier()
-            torch.cuda.synchronize()
-        finally:
-            sys.stdout.flush()
-            os.dup2(saved_stdout, 1)
-            os.close(saved_stdout)
+    # stdout carries the one JSON line: whatever a library prints meanwhile (NCCL's log, when the
+    # environment asks for one) goes to stderr
+    sys.stdout.flush()
+    json_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
 
+    from system1_omni_b200 import dispatch as D
     from system1_omni_b200 import lib as L
     from system1_omni_b200 import model as M
     lib = L.load()                  # raises when the CUDA library is missing: there is no other path
     L.set_device(local)
-    cfg = cfg2(args.layers)
+    cfg = cfg4(args.layers)
     model = M.Model(cfg, device=local)
     model.init_random(seed=0, std=0.02)
-    stream = model.stream
-    rng = np.random.default_rng(1000 + rank)
-    ids = rng.integers(0, cfg.vocab, TOKENS).astype(np.int32)
-    head = np.random.default_rng(7).normal(0, 1.0, (N_CLASSES, cfg.hidden)).astype(np.float32)
-    lengths = np.array([TOKENS], np.int32)
-
-    # pinned host ids for the end-to-end leg, device-resident ids for the kernel leg
-    pinned = C.c_void_p()
-    L.check(lib.s1_host_alloc(C.byref(pinned), ids.nbytes), "pinned")
-    host_ids = np.ctypeslib.as_array(C.cast(pinned, C.POINTER(C.c_int32)), shape=(TOKENS,))
-    host_ids[:] = ids
-    ids_dev = L.DeviceBuffer(ids.nbytes)
-    L.check(lib.cs1_upload(ids_dev.at(), pinned, ids.nbytes, stream), "upload ids")
-
-    def barrier():
-        model.synchronize()
-        if dist:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    def max_over_ranks(x):
-        if not dist:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
     model.enable_graphs(bool(args.graphs))
+    stream = model.stream
+    disp = D.Dispatcher(rank, world, local)
+
+    lengths = request_lengths()[: min(REQUESTS_TOTAL, REQUESTS_PER_GPU * world)]
+    ids_all = request_ids(lengths, cfg.vocab)
+    head = np.random.default_rng(7).normal(0, 1.0, (N_CLASSES, cfg.hidden)).astype(np.float32)
+    disp.plan(model, lengths, N_CLASSES)
+    disp.stage(ids_all)
+    disp.upload()
+
+    # ---- the assignment's cost model from this run's own pack times (every rank, same arithmetic) ----
+    disp.enqueue(resident=True)          # first pass: kernel attributes, tensor maps
+    disp.enqueue(resident=True)
+    ms = disp.pack_ms()
+    mine = np.zeros((REQUESTS_PER_GPU * 2, 3), np.float64)
+    edges = list(disp.pack_start) + [len(disp.local)]
+    for p in range(disp.n_packs):
+        t = lengths[disp.local[edges[p]:edges[p + 1]]].astype(np.float64)
+        mine[p] = (t.sum(), (t * t).sum(), ms[p])
+    fit = fit_cost(disp.allgather(mine).reshape(-1, 3))
+    cost = {"a_ms_per_token": None, "b_ms_per_token2": None, "source": "default (a = 1, b = 4e-6)"}
+    if fit:
+        a = disp.max_over_ranks(fit[0])
+        b = disp.max_over_ranks(fit[1])
+        disp.set_cost(a, b)
+        disp.plan(model, lengths, N_CLASSES)
+        disp.stage(ids_all)
+        disp.upload()
+        cost = {"a_ms_per_token": a, "b_ms_per_token2": b, "source": "least squares over this run's pack times"}
+    local_tokens = disp.local_tokens
+    total_tokens = int(lengths.sum())
+
     for _ in range(args.warmup):
-        model.forward_device(ids_dev.at(), lengths)
+        disp.enqueue(resident=True)
     model.synchronize()
     lib.s1_model_profile_read(model.handle, None, None, None)      # reset the launch counters
-
     sampler = ClockSampler(local)
+
     # ---- device-timed steps, ids resident in HBM ----
     e0, e1 = L.Event(), L.Event()
-    barrier()
+    disp.barrier()
     e0.record(stream)
     for _ in range(args.steps):
-        model.forward_device(ids_dev.at(), lengths)
+        disp.enqueue(resident=True)
     e1.record(stream)
-    barrier()
-    ms_total = max_over_ranks(e0.elapsed_ms(e1))
+    disp.barrier()
+    busy_ms = e0.elapsed_ms(e1)
+    ms_step = disp.max_over_ranks(busy_ms) / args.steps
     launches = (C.c_longlong * len(FAMILIES))()
     lib_launches = C.c_longlong()
     L.check(lib.s1_model_profile_read(model.handle, None, launches, C.byref(lib_launches)), "profile read")
     stats = model.graph_stats()
-    ms_step = ms_total / args.steps
-    value = world * TOKENS / (ms_step * 1e-3)
+    value = total_tokens / (ms_step * 1e-3)
+    per_rank = disp.allgather([local_tokens, busy_ms / args.steps, disp.n_packs, len(disp.local)])
 
-    # ---- end to end through the public call, host buffers ----
-    logits_all = None
-    gather_buf = [torch.zeros(N_CLASSES, device="cuda") for _ in range(world)] if dist else None
-
-    def e2e_step():
-        last = model.forward_flat(host_ids, lengths)
-        logits = M.head_logits(head, last[0])
-        if dist:
-            dist.all_gather(gather_buf, torch.from_numpy(logits).cuda())
-            return torch.stack(gather_buf).cpu().numpy()
-        return logits[None]
-
+    # ---- end to end: pinned host ids -> H2D -> layers -> rows D2H -> host head -> gather to rank 0 ----
+    logits = None
+    gather_us = []
     for _ in range(2):
-        e2e_step()
-    barrier()
+        disp.run(head)
+    disp.barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        logits_all = e2e_step()
-    barrier()
-    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / args.steps
+        logits, us = disp.run(head)
+        gather_us.append(us)
+    disp.barrier()
+    e2e_ms = disp.max_over_ranks((time.perf_counter() - t0) * 1e3) / args.steps
     clocks = sampler.stop()
-    decisions = [int(M.answer(row)[0]) for row in logits_all]
+    status = L.device_status()
+    status_all = disp.allgather([float(any(status))])
+    if status_all.max() > 0:
+        raise RuntimeError(f"a device-side bounded wait gave up (gemm, attention, delta rule = {status} on rank {rank}): "
+                           "the numbers of this run are void")
 
-    # ---- per-family device time: eager profiled steps right after the timed ones ----
+    # ---- rank 0 runs packs of another rank again through the public call: same bits expected ----
+    check = None
+    if rank == 0:
+        other = 1 if world > 1 else 0
+        _, theirs, packs = D.layout(lengths, world, other, disp_cost(cost)[0], disp_cost(cost)[1])
+        first = np.concatenate([[0], np.cumsum(lengths)])
+        picked = [packs[0]] if len(packs) == 1 else [packs[0], packs[len(packs) // 2]]
+        equal, compared = True, []
+        for group in picked:
+            reqs = [int(theirs[j]) for j in group]
+            last = model.forward_batch([ids_all[first[i]:first[i + 1]] for i in reqs])
+            for row, i in zip(last, reqs):
+                again = M.head_logits(head, row)
+                equal = equal and np.array_equal(again.view(np.uint32), logits[i].view(np.uint32))
+                compared.append(i)
+        check = {"rank_rerun": other, "requests": compared, "bit_equal": bool(equal)}
+
+    # ---- per-family device time: one eager profiled step ----
     model.enable_graphs(False)
+    model.synchronize()
+    lib.s1_model_profile_read(model.handle, None, None, None)
     lib.s1_model_profile(model.handle, 1)
-    prof_steps = 3
-    for _ in range(prof_steps):
-        model.forward_device(ids_dev.at(), lengths)
+    disp.enqueue(resident=True)
     fam_ms = (C.c_float * len(FAMILIES))()
     fam_launch = (C.c_longlong * len(FAMILIES))()
     fam_lib = C.c_longlong()
     L.check(lib.s1_model_profile_read(model.handle, fam_ms, fam_launch, C.byref(fam_lib)), "profile read")
     lib.s1_model_profile(model.handle, 0)
-    per_family = {name: {"ms_per_step": fam_ms[i] / prof_steps, "launches_per_step": fam_launch[i] / prof_steps}
+    per_family = {name: {"ms_per_step": fam_ms[i], "launches_per_step": int(fam_launch[i])}
                   for i, name in enumerate(FAMILIES)}
     gemm_ms = per_family["gemm"]["ms_per_step"]
-    gemm_launches = (fam_launch[0] + fam_lib.value) / prof_steps
-    flops = gemm_flops_per_token(cfg) * TOKENS
+    flops = gemm_flops_per_token(cfg) * local_tokens
     pk = peaks()
     achieved = flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
-    engine = "tcgen05 (this library)" if fam_launch[0] > 0 else "cuBLASLt"
 
     if rank != 0:
+        disp.close()
         model.close()
-        if dist:
-            dist.destroy_process_group()
         return
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         secs, layers, threads = cpu_sample(1)
-        cpu = {"value": TOKENS / (secs * cfg.n_layers / layers), "unit": "tokens/s", "cores": threads, "kind": "port",
-               "sample": f"oracle port on {layers} of {cfg.n_layers} layers (one 3 GDN + 1 attention period) at "
-                         f"{TOKENS} tokens, {secs:.1f} s, scaled by {cfg.n_layers}/{layers}"}
-    own_per_step = int(sum(fam_launch)) // prof_steps
-    own = int(sum(launches)) + int(stats["replays"]) * own_per_step      # a replay launches a whole step's kernels
+        cpu = cpu_line([secs], layers, threads)[2]
+    own = int(sum(launches))
+    tokens_by_rank = [int(r[0]) for r in per_rank]
+    busy_by_rank = [float(r[1]) for r in per_rank]
     line = {
         "metric": "prefill tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "layers": cfg.n_layers, "tokens_per_gpu": TOKENS, "weights": "N(0,0.02) bf16, generated on device",
-                   "l2": f"per step {model.weight_bytes / 1e9:.1f} GB of weights stream through a 126 MB L2",
-                   "graphs": bool(args.graphs), "gemm_engine": engine},
-        "e2e": {"value": world * TOKENS / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": int(ids.nbytes + 4), "d2h_bytes_per_step": int(cfg.hidden * 2)},
+        "config": {"workload": WORKLOAD, "layers": cfg.n_layers, "requests": int(lengths.size), "tokens": total_tokens,
+                   "request_lengths": [int(x) for x in lengths],
+                   "weights": "N(0,0.02) bf16, generated on device, replicated per GPU",
+                   "l2": f"per pack {model.weight_bytes / 1e9:.1f} GB of weights stream through a 126 MB L2",
+                   "graphs": bool(args.graphs), "cost_model": cost},
+        "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": int(local_tokens * 4 + 4 * len(disp.local) + (N_CLASSES * 4 * len(disp.local) if world > 1 else 0)),
+                "d2h_bytes_per_step": int(len(disp.local) * cfg.hidden * 2 + 12 + (N_CLASSES * 4 * int(lengths.size) if world > 1 else 0)),
+                "bytes_of": "rank 0: ids and pack offsets in, last-token rows and status words out, logits through the gather"},
         "gpu_launches": own,
-        "launch_detail": {"own_kernels_in_timed_region": own,
-                          "own_kernels_launched_eagerly_in_timed_region": int(sum(launches)), "library_launches_in_timed_region": int(lib_launches.value),
-                          "graph_replays": stats["replays"], "own_kernels_per_eager_step": own_per_step,
-                          "library_launches_per_eager_step": int(fam_lib.value) // prof_steps},
+        "launch_detail": {"own_kernels_in_timed_region_rank0": own, "graph_replays": stats["replays"],
+                          "graph_captures": stats["captures"], "library_launches_in_timed_region": int(lib_launches.value),
+                          "own_kernels_per_eager_step": int(sum(fam_launch)),
+                          "library_launches_per_eager_step": int(fam_lib.value)},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
-                     "frac": achieved / pk["tflops"], "traffic": GEMM_TRAFFIC["bytes"] if fam_launch[0] > 0 else None,
-                     "traffic_of": GEMM_TRAFFIC["of"], "kernel": f"bf16 GEMM, {engine}",
-                     "launches_per_step": gemm_launches, "flops_per_step": flops, "ms_per_step": gemm_ms,
+                     "frac": achieved / pk["tflops"], "traffic": GEMM_TRAFFIC["bytes"], "traffic_of": GEMM_TRAFFIC["of"],
+                     "kernel": "bf16 GEMM family, tcgen05 (this library), rank 0's share",
+                     "launches_per_step": int(fam_launch[0]), "flops_per_step": flops, "ms_per_step": gemm_ms,
                      "peak_source": pk["source"] + " (sustained cuBLAS bf16)"},
         "per_family": per_family,
+        "balance": {"tokens_by_rank": tokens_by_rank, "busy_ms_by_rank": busy_by_rank,
+                    "packs_by_rank": [int(r[2]) for r in per_rank], "requests_by_rank": [int(r[3]) for r in per_rank],
+                    "tokens_max_over_mean": max(tokens_by_rank) / (sum(tokens_by_rank) / world),
+                    "busy_max_over_mean": max(busy_by_rank) / (sum(busy_by_rank) / world),
+                    "gather_us_median": float(np.median(gather_us)),
+                    "gather_us_note": "host time of H2D + all-gather + D2H on rank 0, which includes the wait for the slowest rank"},
+        "dispatch_check": check,
+        "device_status": {"rank0": list(status), "any_rank_nonzero": bool(status_all.max() > 0)},
         "clocks": clocks,
-        "decisions": decisions,
+        "decisions": [int(M.answer(row)[0]) for row in logits],
     }
     if cpu:
         line["cpu_baseline"] = cpu
-    print(json.dumps(line), flush=True)
+    json_out.write(json.dumps(line) + "\n")
+    json_out.flush()
+    disp.close()
     model.close()
-    if dist:
-        dist.destroy_process_group()
+
+
+def disp_cost(cost):
+    if cost["a_ms_per_token"] is None:
+        return 1.0, 4e-6
+    return cost["a_ms_per_token"], cost["b_ms_per_token2"]
 
 
 if __name__ == "__main__":

@@ -67,6 +67,16 @@ int s1_attn_tc5_status(int* code);
 
 /* The same for the delta-rule kernels (a bounded wait for a TMA or bulk copy gave up). */
 int s1_gdn_status(int* code);
+/* All three words of the current device with one wait for the device (each out pointer nullable);
+ * cleared when any is set. The executor's calls that read results back (s1_model_forward_batch,
+ * s1_model_forward_continue, s1_model_prefix_capture, s1_model_read_rows) check them themselves
+ * and return CS1_ERR_DEVICE_CHECK, the way the reference turns every device failure into an
+ * error (src/models/qwen3_5/native/src/cuda.rs:177-187). */
+int s1_device_status(int* gemm, int* attention, int* gdn);
+/* Self-test of that path, without any fault: queues a one-thread kernel that waits on a barrier
+ * nothing completes; its bounded wait gives up after limit_us microseconds, records code 99 in
+ * the GEMM's error word and the kernel returns. The context stays usable. */
+int s1_selftest_wait_runs_out(int limit_us, void* stream);
 
 /* ---- GEMM engines behind cs1_gemm, pinned (benchmark arms and parity tests) ---- */
 int s1_gemm_cublaslt(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream);
@@ -113,10 +123,19 @@ int s1_model_tensor(void* model, const char* name, void** device_ptr, size_t* by
  * weights N(0, std), the gated norm weight 1 + N(0, std), A_log U(0, ln 16), dt_bias N(0, 0.1). */
 int s1_model_init_random(void* model, uint64_t seed, float std);
 size_t s1_model_weight_bytes(void* model);
+/* The model's shape (full_attention points into the model). */
+int s1_model_config(void* model, S1Config* out);
+/* Grows the scratch to hold passes of up to `tokens` tokens now (the reference grows on demand in
+ * 1024-token steps, model.rs:747-761, which drops recorded graphs): a host that knows its largest
+ * pack calls this once, before it queues passes. */
+int s1_model_reserve(void* model, int tokens);
 void* s1_model_stream(void* model);
-/* CUDA-graph replay per ordered length vector (64 entries, first in first out; eager on a
- * miss; a failed capture switches replay off): model.rs:797-897. Off by default, or on when
- * CUA_S1_GRAPH=1 is in the environment at creation, as in the reference (model.rs:695). */
+/* CUDA-graph replay per ordered length vector (64 entries, first in first out; a failed capture
+ * switches replay off): model.rs:797-897. Off by default, or on when CUA_S1_GRAPH=1 is in the
+ * environment at creation, as in the reference (model.rs:695). Unlike the reference, which
+ * records every new vector right after running it, a vector is recorded when it is seen for the
+ * second time (the pass is recorded and the recording launched, with no wait for the stream):
+ * ragged request sets rarely repeat a vector, and a first sight then costs one eager pass only. */
 int s1_model_enable_graphs(void* model, int on);
 /* Exact packing (off by default): a prompt's hidden states come out bit-identical whether it
  * runs alone, inside a pack, or as a continuation of a captured prefix. Every GEMM then runs on
@@ -154,6 +173,15 @@ int s1_model_forward_batch(void* model, const int32_t* ids, const int* lengths, 
  * call); queue-only, no host synchronisation. */
 int s1_model_forward_device(void* model, const int32_t* ids_device, const int* lengths, int nseq, void** last_rows);
 int s1_model_sync(void* model);
+/* The same pass, queue-only, for a host that keeps several packs in flight: ids in host memory
+ * (pinned, if the copy is to overlap; they must stay unchanged until the pass has run), the
+ * last-token rows written as bf16 [nseq, hidden] to rows_device, a device buffer of the caller.
+ * Validates like s1_model_forward_batch. No host synchronisation. */
+int s1_model_forward_queue(void* model, const int32_t* ids_host, const int* lengths, int nseq, void* rows_device);
+/* Copies `bytes` from rows_device to dst_host behind everything queued, waits for the stream and
+ * checks the device error words as of the last pass: 0, or CS1_ERR_DEVICE_CHECK when a bounded
+ * wait gave up (the rows must not be used then). bytes == 0 only waits and checks. */
+int s1_model_read_rows(void* model, void* dst_host, const void* rows_device, size_t bytes);
 
 /* ---- Prefix capture and continuation (PrefixState, alloc_prefix, forward_multimodal_capture /
  * _continue, model.rs:557-588, 954-1073; run_window, model.rs:1340-1638), for text positions.
@@ -207,7 +235,7 @@ int s1_model_unfilled(void* model, char* name_out, size_t cap);
 int s1_model_profile(void* model, int on);
 /* Waits for the stream, then returns and resets: device milliseconds per family since the
  * last read (profile mode only; ms nullable), kernels of this library launched per family
- * (nullable) and launches handed to cuBLASLt (nullable). Graph replays are not counted. */
+ * (nullable, a graph replay counts the kernels it holds) and launches handed to cuBLASLt (nullable). */
 int s1_model_profile_read(void* model, float* ms, long long* launches, long long* library_launches);
 /* 1 if cs1_gemm would run this problem on the tcgen05 kernel of this library, 0 if on cuBLASLt. */
 int s1_gemm_engine(void* gemm, const void* x, const void* w, int M, int N, int K);

@@ -29,6 +29,7 @@
 #include "attention_tc5.h"
 #include "common.cuh"
 #include "cs1_ops.h"
+#include "status.h"
 #include "tc5.cuh"
 #include "tmap.h"
 
@@ -494,5 +495,13 @@ extern "C" int s1_attn_tc5_status(int* code) {
         e = cudaMemcpyToSymbol(g_attn_error, &zero, sizeof(int));
     }
     *code = v;
+    return e;
+}
+
+// Device address of this device's error word, for the executor's status copy.
+int s1::attn_error_address(int** p) {
+    void* a = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&a, s1::g_attn_error);
+    *p = static_cast<int*>(a);
     return e;
 }

@@ -18,6 +18,7 @@
 #include "cs1_ops.h"
 #include "exec_kernels.h"
 #include "s1_executor.h"
+#include "status.h"
 
 namespace {
 
@@ -43,7 +44,7 @@ struct Scratch {
     size_t cap = 0;
     void* buf = nullptr;
     size_t ids, res, x, delta, gdn_in, beta, g, lq, lk, lv, lo, ln, workspace, attn_in, aq, agate, ak, ao, gate_up,
-        act, cos, sin, ends, last, total;
+        act, cos, sin, ends, last, status, total;
     char* at(size_t off) const { return static_cast<char*>(buf) + off; }
 };
 
@@ -84,9 +85,17 @@ struct Model {
     int overlap_tokens = 128;  // eager passes of at most this many tokens launch every kernel as a programmatic dependent
     bool capturing = false;    // the pass being issued is recorded into a graph
     int replays = 0, captures = 0;
-    std::deque<std::pair<std::vector<int>, void*>> graphs;
+    struct Recorded {
+        std::vector<int> key;
+        void* exec;
+        long long kernels[S1_FAMILIES];  // what one replay launches, per family
+    };
+    std::deque<Recorded> graphs;
     int* ends_host = nullptr;  // pinned ring of ENDS_RING slots of cap ints
     size_t ends_slot = 0;
+    cudaEvent_t ends_event[ENDS_RING] = {};  // recorded behind the copy out of a slot; awaited before the slot is rewritten
+    int* status_host = nullptr;               // pinned: the three device error words as of the last pass read back
+    std::deque<std::vector<int>> seen_once;   // length vectors run eagerly once, captured when they come again
     void* last_host = nullptr;  // pinned staging of the last rows
     size_t last_host_bytes = 0;
 
@@ -100,8 +109,9 @@ struct Model {
 };
 
 void clear_graphs(Model* m) {
-    for (auto& g : m->graphs) cs1_graph_destroy(g.second);
+    for (auto& g : m->graphs) cs1_graph_destroy(g.exec);
     m->graphs.clear();
+    m->seen_once.clear();
 }
 
 // What the kernels implement (model.rs:134-180), with head_dim 128 accepted besides 256.
@@ -258,6 +268,7 @@ int make_scratch(Model* m, size_t cap) {
     s.sin = take(cap * c.rotary_half * BF16);
     s.ends = take(cap * 4);
     s.last = take(cap * h * BF16);  // at most one row per prompt, at most cap prompts
+    s.status = take(4 * sizeof(int));
     s.total = next;
     S1_TRY(cs1_malloc(&s.buf, s.total));
     s.cap = cap;
@@ -596,45 +607,58 @@ int run_window(Model* m, const int* lengths, int nseq, Prefix* capture, const Pr
     return 0;
 }
 
-// Replay a captured graph for this ordered length vector, or run eagerly and capture
-// (model.rs:797-813, 862-897). The eager result of a miss is kept: run() advances the
-// residual in place, so replaying on top of it would advance it twice.
+// Replay a captured graph for this ordered length vector (model.rs:797-813, 862-897). A vector
+// seen for the first time runs eagerly and is only remembered: ragged request sets rarely repeat
+// a vector, and recording one costs a second host pass over the layer loop. When a remembered
+// vector comes again the pass is recorded first and the recording launched (one host pass, no
+// wait for the stream); if recording fails the pass runs eagerly and replay is switched off.
 int run_or_replay(Model* m, const int* lengths, int nseq) {
     if (!m->graph_enabled) return run(m, lengths, nseq, nullptr);
     const std::vector<int> key(lengths, lengths + nseq);
-    for (auto& g : m->graphs) {
-        if (g.first == key) {
-            m->replays++;
-            return cs1_graph_launch(g.second, m->stream);
-        }
+    auto replay = [m](const Model::Recorded& g) {
+        m->replays++;
+        for (int f = 0; f < S1_FAMILIES; f++) m->launches[f] += g.kernels[f];
+        return cs1_graph_launch(g.exec, m->stream);
+    };
+    for (auto& g : m->graphs)
+        if (g.key == key) return replay(g);
+    auto seen = std::find(m->seen_once.begin(), m->seen_once.end(), key);
+    if (seen == m->seen_once.end()) {
+        if ((int)m->seen_once.size() == GRAPH_CACHE) m->seen_once.pop_front();
+        m->seen_once.push_back(key);
+        return run(m, lengths, nseq, nullptr);
     }
-    S1_TRY(run(m, lengths, nseq, nullptr));
-    S1_TRY(cs1_stream_sync(m->stream));
-    void* exec = nullptr;
+    m->seen_once.erase(seen);
+    Model::Recorded rec{key, nullptr, {}};
+    void*& exec = rec.exec;
+    long long before[S1_FAMILIES];
+    memcpy(before, m->launches, sizeof(before));
     int rc = cs1_graph_begin(m->stream);
     if (rc == 0) {
         m->capturing = true;
         const int body = run(m, lengths, nseq, nullptr);
         m->capturing = false;
+        for (int f = 0; f < S1_FAMILIES; f++) rec.kernels[f] = m->launches[f] - before[f];  // recorded, not launched
+        memcpy(m->launches, before, sizeof(before));
         rc = cs1_graph_end(m->stream, &exec);
         if (rc == 0 && body != 0) {
             cs1_graph_destroy(exec);
             rc = body;
         }
     }
-    if (rc == 0) {
-        if ((int)m->graphs.size() == GRAPH_CACHE) {
-            cs1_graph_destroy(m->graphs.front().second);
-            m->graphs.pop_front();
-        }
-        m->graphs.emplace_back(key, exec);
-        m->captures++;
-    } else {
-        // keep the eager result, stop trying to capture
+    if (rc != 0) {
+        // nothing of the pass has run yet: run it eagerly and stop trying to record
         m->graph_enabled = false;
         clear_graphs(m);
+        return run(m, lengths, nseq, nullptr);
     }
-    return 0;
+    if ((int)m->graphs.size() == GRAPH_CACHE) {
+        cs1_graph_destroy(m->graphs.front().exec);
+        m->graphs.pop_front();
+    }
+    m->graphs.push_back(rec);
+    m->captures++;
+    return replay(m->graphs.back());
 }
 
 int check_batch(const Model* m, const int* lengths, int nseq, long* total) {
@@ -649,15 +673,52 @@ int check_batch(const Model* m, const int* lengths, int nseq, long* total) {
     return 0;
 }
 
+// The end offsets of a pack, through a ring of pinned slots. A slot is rewritten only after the
+// copy queued out of it ENDS_RING passes ago has run, so any number of passes may be queued
+// without waiting for the stream.
 int stage_ends(Model* m, const int* lengths, int nseq) {
-    int* slot = m->ends_host + (m->ends_slot++ % ENDS_RING) * m->s.cap;
+    const size_t k = m->ends_slot++ % ENDS_RING;
+    cudaStream_t st = static_cast<cudaStream_t>(m->stream);
+    if (!m->ends_event[k]) {
+        S1_TRY((int)cudaEventCreateWithFlags(&m->ends_event[k], cudaEventDisableTiming));
+    } else {
+        S1_TRY((int)cudaEventSynchronize(m->ends_event[k]));
+    }
+    int* slot = m->ends_host + k * m->s.cap;
     int end = 0;
     for (int i = 0; i < nseq; i++) {
         end += lengths[i];
         slot[i] = end;
     }
-    return (int)cudaMemcpyAsync(m->s.at(m->s.ends), slot, (size_t)nseq * sizeof(int), cudaMemcpyHostToDevice,
-                                static_cast<cudaStream_t>(m->stream));
+    S1_TRY((int)cudaMemcpyAsync(m->s.at(m->s.ends), slot, (size_t)nseq * sizeof(int), cudaMemcpyHostToDevice, st));
+    return (int)cudaEventRecord(m->ends_event[k], st);
+}
+
+// Behind a pass: each prompt's last-token row gathered into `rows` (bf16 [nseq, hidden], device)
+// and the three device error words copied into the scratch's status slot.
+int finish_pass(Model* m, int nseq, void* rows) {
+    const Scratch& s = m->s;
+    cudaStream_t st = static_cast<cudaStream_t>(m->stream);
+    S1_OP(S1_FAMILY_OTHER, 1,
+          s1::gather_rows(s.at(s.x), reinterpret_cast<const int*>(s.at(s.ends)), rows, nseq, m->cfg.hidden, st));
+    S1_OP(S1_FAMILY_OTHER, 1, s1::collect_status(reinterpret_cast<int*>(s.at(s.status)), st));
+    return 0;
+}
+
+// Reads `bytes` of last rows (nullable dst) and the status slot back, waits for the stream, and
+// turns a non-zero error word into CS1_ERR_DEVICE_CHECK (clearing the words so that the next
+// pass starts clean): a bounded wait that gave up left rows that must not be used.
+int read_back(Model* m, void* dst, const void* src, size_t bytes) {
+    cudaStream_t st = static_cast<cudaStream_t>(m->stream);
+    if (!m->status_host) S1_TRY((int)cudaHostAlloc(reinterpret_cast<void**>(&m->status_host), 4 * sizeof(int), cudaHostAllocDefault));
+    if (dst && bytes) S1_TRY((int)cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, st));
+    S1_TRY((int)cudaMemcpyAsync(m->status_host, m->s.at(m->s.status), 3 * sizeof(int), cudaMemcpyDeviceToHost, st));
+    S1_TRY(cs1_stream_sync(m->stream));
+    if (m->status_host[0] | m->status_host[1] | m->status_host[2]) {
+        S1_TRY(s1::clear_status());
+        return CS1_ERR_DEVICE_CHECK;
+    }
+    return 0;
 }
 
 }  // namespace
@@ -702,6 +763,9 @@ void s1_model_destroy(void* model) {
     if (m->arena) cs1_free(m->arena);
     if (m->ends_host) cudaFreeHost(m->ends_host);
     if (m->last_host) cudaFreeHost(m->last_host);
+    if (m->status_host) cudaFreeHost(m->status_host);
+    for (cudaEvent_t e : m->ends_event)
+        if (e) cudaEventDestroy(e);
     for (cudaEvent_t e : m->events) cudaEventDestroy(e);
     if (m->stream) cs1_stream_destroy(m->stream);
     delete m;
@@ -774,6 +838,19 @@ int s1_model_init_random(void* model, uint64_t seed, float std) {
     return cs1_stream_sync(m->stream);
 }
 
+int s1_model_config(void* model, S1Config* out) {
+    Model* m = static_cast<Model*>(model);
+    if (!m || !out) return S1_ERR_ARGUMENT;
+    *out = m->cfg;  // full_attention points into the model and lives as long as it
+    return 0;
+}
+
+int s1_model_reserve(void* model, int tokens) {
+    Model* m = static_cast<Model*>(model);
+    if (!m || tokens <= 0) return S1_ERR_ARGUMENT;
+    return prepare_scratch(m, (size_t)tokens);
+}
+
 size_t s1_model_weight_bytes(void* model) { return model ? static_cast<Model*>(model)->arena_bytes : 0; }
 void* s1_model_stream(void* model) { return model ? static_cast<Model*>(model)->stream : nullptr; }
 
@@ -839,9 +916,7 @@ int s1_model_forward_batch(void* model, const int32_t* ids, const int* lengths, 
         S1_TRY(run(m, lengths, nseq, static_cast<char*>(layer_out)));
     else
         S1_TRY(run_or_replay(m, lengths, nseq));
-    S1_OP(S1_FAMILY_OTHER, 1,
-          s1::gather_rows(s.at(s.x), reinterpret_cast<const int*>(s.at(s.ends)), s.at(s.last), nseq, h,
-                          static_cast<cudaStream_t>(m->stream)));
+    S1_TRY(finish_pass(m, nseq, s.at(s.last)));
     const size_t bytes = (size_t)nseq * h * BF16;
     if (m->last_host_bytes < bytes) {
         if (m->last_host) cudaFreeHost(m->last_host);
@@ -850,7 +925,7 @@ int s1_model_forward_batch(void* model, const int32_t* ids, const int* lengths, 
         S1_TRY((int)cudaHostAlloc(&m->last_host, bytes, cudaHostAllocDefault));
         m->last_host_bytes = bytes;
     }
-    S1_TRY(cs1_download(m->last_host, s.at(s.last), bytes, m->stream));
+    S1_TRY(read_back(m, m->last_host, s.at(s.last), bytes));
     const uint16_t* rows = static_cast<const uint16_t*>(m->last_host);
     for (size_t i = 0; i < (size_t)nseq * h; i++) last_hidden[i] = bf2f(rows[i]);
     return 0;
@@ -867,11 +942,35 @@ int s1_model_forward_device(void* model, const int32_t* ids_device, const int* l
     S1_TRY(stage_ends(m, lengths, nseq));
     S1_OP(S1_FAMILY_OTHER, 1, cs1_embed(ids_device, m->w(m->embed), s.at(s.res), (int)total, h, m->stream));
     S1_TRY(run_or_replay(m, lengths, nseq));
-    S1_OP(S1_FAMILY_OTHER, 1,
-          s1::gather_rows(s.at(s.x), reinterpret_cast<const int*>(s.at(s.ends)), s.at(s.last), nseq, h,
-                          static_cast<cudaStream_t>(m->stream)));
+    S1_TRY(finish_pass(m, nseq, s.at(s.last)));
     if (last_rows) *last_rows = s.at(s.last);
     return 0;
+}
+
+int s1_model_forward_queue(void* model, const int32_t* ids_host, const int* lengths, int nseq, void* rows_device) {
+    Model* m = static_cast<Model*>(model);
+    if (!m || !ids_host || !rows_device) return S1_ERR_ARGUMENT;
+    long total = 0;
+    S1_TRY(check_batch(m, lengths, nseq, &total));
+    for (long i = 0; i < total; i++)
+        if (ids_host[i] < 0 || ids_host[i] >= m->cfg.vocab) return S1_ERR_ARGUMENT;
+    S1_TRY(prepare_scratch(m, (size_t)total));
+    const Scratch& s = m->s;
+    S1_TRY(s1_upload_async(s.at(s.ids), ids_host, (size_t)total * 4, m->stream));
+    S1_TRY(stage_ends(m, lengths, nseq));
+    S1_OP(S1_FAMILY_OTHER, 1,
+          cs1_embed(reinterpret_cast<const int32_t*>(s.at(s.ids)), m->w(m->embed), s.at(s.res), (int)total,
+                    m->cfg.hidden, m->stream));
+    S1_TRY(run_or_replay(m, lengths, nseq));
+    return finish_pass(m, nseq, rows_device);
+}
+
+int s1_model_read_rows(void* model, void* dst_host, const void* rows_device, size_t bytes) {
+    Model* m = static_cast<Model*>(model);
+    if (!m || (bytes && (!dst_host || !rows_device))) return S1_ERR_ARGUMENT;
+    S1_TRY(cs1_set_device(m->device));
+    if (!m->s.buf) return bytes ? S1_ERR_ARGUMENT : cs1_stream_sync(m->stream);
+    return read_back(m, dst_host, rows_device, bytes);
 }
 
 // ---- prefix capture / continuation (alloc_prefix, forward_multimodal_capture / _continue,
@@ -938,7 +1037,8 @@ int s1_model_prefix_capture(void* model, const int32_t* ids, int len, void* pref
           cs1_embed(reinterpret_cast<const int32_t*>(s.at(s.ids)), m->w(m->embed), s.at(s.res), len, m->cfg.hidden,
                     m->stream));
     S1_TRY(run_window(m, &len, 1, p, nullptr));
-    S1_TRY(cs1_stream_sync(m->stream));
+    S1_OP(S1_FAMILY_OTHER, 1, s1::collect_status(reinterpret_cast<int*>(s.at(s.status)), static_cast<cudaStream_t>(m->stream)));
+    S1_TRY(read_back(m, nullptr, nullptr, 0));
     p->ready = true;
     return 0;
 }
@@ -978,11 +1078,9 @@ int s1_model_forward_continue(void* model, const void* prefix, const int32_t* id
     S1_OP(S1_FAMILY_OTHER, 1,
           cs1_embed(reinterpret_cast<const int32_t*>(s.at(s.ids)), m->w(m->embed), s.at(s.res), (int)rows, h, m->stream));
     S1_TRY(run_window(m, packed_len.data(), nseq, nullptr, p));
-    S1_OP(S1_FAMILY_OTHER, 1,
-          s1::gather_rows(s.at(s.x), reinterpret_cast<const int*>(s.at(s.ends)), s.at(s.last), nseq, h,
-                          static_cast<cudaStream_t>(m->stream)));
+    S1_TRY(finish_pass(m, nseq, s.at(s.last)));
     std::vector<uint16_t> out((size_t)nseq * h);
-    S1_TRY(cs1_download(out.data(), s.at(s.last), out.size() * BF16, m->stream));
+    S1_TRY(read_back(m, out.data(), s.at(s.last), out.size() * BF16));
     for (size_t i = 0; i < out.size(); i++) last_hidden[i] = bf2f(out[i]);
     return 0;
 }

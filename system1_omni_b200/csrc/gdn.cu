@@ -32,6 +32,7 @@
 #include "common.cuh"
 #include "cs1_ops.h"
 #include "mma.cuh"
+#include "status.h"
 #include "tc5.cuh"
 #include "tmap.h"
 
@@ -1259,4 +1260,12 @@ extern "C" int cs1_gdn_prefill_static(const void* q, const void* k, const void* 
     const int rc = static_scratch_address(&scratch);
     if (rc != 0) return rc;
     return s1::gdn_run(q, k, v, g, beta, o, scratch, T, H, HK, scale, nullptr, nullptr, stream);
+}
+
+// Device address of this device's error word, for the executor's status copy.
+int s1::gdn_error_address(int** p) {
+    void* a = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&a, s1::g_gdn_error);
+    *p = static_cast<int*>(a);
+    return e;
 }

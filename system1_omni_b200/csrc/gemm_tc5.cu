@@ -31,6 +31,7 @@
 #include "common.cuh"
 #include "cs1_ops.h"
 #include "gemm_tc5.h"
+#include "status.h"
 #include "tc5.cuh"
 
 namespace s1 {
@@ -1230,4 +1231,40 @@ extern "C" int s1_gemm_tc5_status(int* code) {
     }
     *code = v;
     return e;
+}
+
+// Device address of this device's error word, for the executor's status copy.
+int s1::gemm_error_address(int** p) {
+    void* a = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&a, s1::g_gemm_error);
+    *p = static_cast<int*>(a);
+    return e;
+}
+
+namespace s1 {
+namespace {
+// One block, one thread: waits on an mbarrier that nothing ever completes. The bounded wait
+// runs out after limit_ns, the thread records code 99 in the GEMM's error word the way the
+// kernels above do, and the kernel returns. No copy, tensor memory or MMA is in flight.
+__global__ void wait_runs_out_kernel(uint64_t limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    tc5::mbar_init(&bar, 1);
+    abort_flag = 0;
+    tc5::mbar_init_fence();
+    if (!tc5::mbar_wait(&bar, 0, &abort_flag, limit_ns)) atomicCAS(&g_gemm_error, 0, 99);
+}
+}  // namespace
+}  // namespace s1
+
+// Self-test of the give-up path of the bounded waits: queues a one-thread kernel whose wait is
+// made to run out after limit_us microseconds (clamped to [1, 100000]) and which then records
+// code 99 in the GEMM's error word and returns. The next status read (s1_device_status,
+// s1_gemm_tc5_status, or any executor call that reads results back) reports it; the context
+// stays usable.
+extern "C" int s1_selftest_wait_runs_out(int limit_us, void* stream) {
+    if (limit_us < 1) limit_us = 1;
+    if (limit_us > 100000) limit_us = 100000;
+    wait_runs_out_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>((uint64_t)limit_us * 1000ull);
+    return cudaGetLastError();
 }

@@ -2,6 +2,8 @@
 // and the gather of each prompt's last-token row.
 #include "common.cuh"
 #include "exec_kernels.h"
+#include "s1_executor.h"
+#include "status.h"
 
 namespace s1 {
 namespace {
@@ -37,7 +39,35 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ x, const int* __res
     for (int i = threadIdx.x; i < packs; i += blockDim.x) out[dst + i] = x[src + i];
 }
 
+__global__ void collect_status_kernel(const int* a, const int* b, const int* c, int* out) {
+    out[0] = *a;
+    out[1] = *b;
+    out[2] = *c;
+}
+
 }  // namespace
+
+int collect_status(int* out3_device, cudaStream_t st) {
+    int *a = nullptr, *b = nullptr, *c = nullptr;
+    cudaError_t e;
+    if ((e = (cudaError_t)gemm_error_address(&a)) != cudaSuccess) return e;
+    if ((e = (cudaError_t)attn_error_address(&b)) != cudaSuccess) return e;
+    if ((e = (cudaError_t)gdn_error_address(&c)) != cudaSuccess) return e;
+    collect_status_kernel<<<1, 1, 0, st>>>(a, b, c, out3_device);
+    return cudaGetLastError();
+}
+
+int clear_status() {
+    int* p[3] = {};
+    cudaError_t e;
+    if ((e = (cudaError_t)gemm_error_address(&p[0])) != cudaSuccess) return e;
+    if ((e = (cudaError_t)attn_error_address(&p[1])) != cudaSuccess) return e;
+    if ((e = (cudaError_t)gdn_error_address(&p[2])) != cudaSuccess) return e;
+    if ((e = cudaDeviceSynchronize()) != cudaSuccess) return e;
+    for (int i = 0; i < 3; i++)
+        if ((e = cudaMemset(p[i], 0, sizeof(int))) != cudaSuccess) return e;
+    return cudaSuccess;
+}
 
 int fill_bf16(void* out, size_t n, uint64_t seed, float mean, float std, int kind, cudaStream_t st) {
     if (n == 0) return 0;
@@ -53,3 +83,25 @@ int gather_rows(const void* x, const int* ends_device, void* out, int nseq, int 
 }
 
 }  // namespace s1
+
+// The three device error words of the current device after waiting for all queued work
+// (0 = no bounded wait gave up), cleared when any is set. Every out pointer is nullable.
+extern "C" int s1_device_status(int* gemm, int* attention, int* gdn) {
+    int* p[3] = {};
+    cudaError_t e;
+    if ((e = (cudaError_t)s1::gemm_error_address(&p[0])) != cudaSuccess) return e;
+    if ((e = (cudaError_t)s1::attn_error_address(&p[1])) != cudaSuccess) return e;
+    if ((e = (cudaError_t)s1::gdn_error_address(&p[2])) != cudaSuccess) return e;
+    if ((e = cudaDeviceSynchronize()) != cudaSuccess) return e;
+    int v[3] = {};
+    for (int i = 0; i < 3; i++)
+        if ((e = cudaMemcpy(&v[i], p[i], sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess) return e;
+    if (v[0] | v[1] | v[2]) {
+        const int rc = s1::clear_status();
+        if (rc != 0) return rc;
+    }
+    if (gemm) *gemm = v[0];
+    if (attention) *attention = v[1];
+    if (gdn) *gdn = v[2];
+    return 0;
+}

@@ -54,7 +54,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Wait for the phase with this parity; gives up after limit_ns and returns false.
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          uint64_t limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     // The clock is read only once in 1024 failed polls, the first time included: a read of
     // %globaltimer costs far more than a poll, and in a pipeline that runs at the speed of its
@@ -67,7 +68,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
             const uint64_t now = global_ns();
             if (start == 0)
                 start = now;
-            else if (now - start > WAIT_LIMIT_NS)
+            else if (now - start > limit_ns)
                 return false;
         }
     }

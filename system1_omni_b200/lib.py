@@ -26,6 +26,7 @@ class S1Config(C.Structure):
 
 
 # name -> (restype, argtypes); every cs1_* symbol of include/cs1_ops.h and s1_* of include/s1_executor.h
+# and include/s1_dispatch.h
 SIGNATURES = {
     "cs1_abi_version": (C.c_uint32, []),
     "cs1_error_string": (C.c_char_p, [i32]),
@@ -131,6 +132,28 @@ SIGNATURES = {
     "s1_decide": (i32, [vp, i32, f64, vp]),
     "s1_batch_ranges": (i32, [vp, i32, vp]),
     "s1_assign_requests": (i32, [vp, i32, i32, f64, f64, vp]),
+    "s1_device_status": (i32, [ip, ip, ip]),
+    "s1_selftest_wait_runs_out": (i32, [i32, vp]),
+    "s1_model_config": (i32, [vp, C.POINTER(S1Config)]),
+    "s1_model_reserve": (i32, [vp, i32]),
+    "s1_model_forward_queue": (i32, [vp, vp, vp, i32, vp]),
+    "s1_model_read_rows": (i32, [vp, vp, vp, sz]),
+    # include/s1_dispatch.h
+    "s1_dispatch_create": (i32, [i32, i32, i32, C.c_char_p, C.c_char_p, vpp]),
+    "s1_dispatch_destroy": (None, [vp]),
+    "s1_dispatch_set_cost": (i32, [vp, f64, f64]),
+    "s1_dispatch_layout": (i32, [vp, i32, i32, f64, f64, i32, vp, vp, ip, vp]),
+    "s1_dispatch_plan": (i32, [vp, vp, vp, i32, i32]),
+    "s1_dispatch_info": (i32, [vp, ip, C.POINTER(C.c_longlong), ip, vp]),
+    "s1_dispatch_local": (i32, [vp, vp, vp]),
+    "s1_dispatch_stage": (i32, [vp, vp]),
+    "s1_dispatch_upload": (i32, [vp]),
+    "s1_dispatch_enqueue": (i32, [vp, i32]),
+    "s1_dispatch_pack_ms": (i32, [vp, vp]),
+    "s1_dispatch_collect": (i32, [vp, vp, vp, vp, C.POINTER(f64)]),
+    "s1_dispatch_barrier": (i32, [vp]),
+    "s1_dispatch_allreduce_max": (i32, [vp, vp, i32]),
+    "s1_dispatch_allgather": (i32, [vp, vp, i32, vp]),
 }
 
 _LIB = None
@@ -253,6 +276,13 @@ def from_device(buf, shape, dtype, stream, offset_bytes=0):
         check(load().cs1_download(out.ctypes.data_as(C.c_void_p), buf.at(offset_bytes), out.nbytes, stream.handle),
               "download")
     return out
+
+
+def device_status():
+    """(gemm, attention, delta rule) error words of the current device after a device sync; cleared."""
+    g, a, d = C.c_int(0), C.c_int(0), C.c_int(0)
+    check(load().s1_device_status(C.byref(g), C.byref(a), C.byref(d)), "device status")
+    return g.value, a.value, d.value
 
 
 def gemm_status():

@@ -51,7 +51,7 @@ class Config:
     def full_attention(self):
         return [t == "full_attention" for t in self.layer_types]
 
-    def oracle_dict(self):
+    def shape_dict(self):
         return dict(hidden=self.hidden, intermediate=self.intermediate, layer_types=list(self.layer_types),
                     heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim, rotary_half=self.rotary_half,
                     lin_k_heads=self.lin_k_heads, lin_v_heads=self.lin_v_heads, vocab=self.vocab, eps=self.eps,

@@ -36,7 +36,15 @@ def worker(rank, world, port, result_path):
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        out = dispatch.run_sharded(make_requests(), fake_forward, N_CLASSES, rank, world, dist=dist, b=1e-3)
+        import torch
+
+        def gather(block):
+            mine = torch.from_numpy(block)
+            every = [torch.zeros_like(mine) for _ in range(world)]
+            dist.all_gather(every, mine)
+            return [t.numpy() for t in every]
+
+        out = dispatch.run_sharded(make_requests(), fake_forward, N_CLASSES, rank, world, gather=gather, b=1e-3)
         if rank == 0:
             np.save(result_path, out)
         else:
@@ -64,15 +72,27 @@ def test_two_ranks_equal_one_rank(tmp_path):
 
 def test_shards_are_balanced_and_complete():
     from system1_omni_b200 import dispatch
+    from system1_omni_b200 import model as M
     rng = np.random.default_rng(0)
     lengths = np.exp(rng.uniform(np.log(512), np.log(16384), 64)).astype(np.int32)     # the 27B config's request set
-    for world in (2, 4, 8):
-        where = dispatch.shard(lengths, world, a=1.0, b=2e-5)
+    for world in (1, 2, 4, 8):
         cost = lengths + 2e-5 * lengths.astype(np.float64) ** 2
+        seen = []
+        for rank in range(world):
+            where, mine, packs = dispatch.layout(lengths, world, rank, a=1.0, b=2e-5)
+            assert np.array_equal(where, M.assign_requests(lengths, world, 1.0, 2e-5))
+            assert sorted(mine.tolist()) == np.flatnonzero(where == rank).tolist()
+            # run order: by length, so that short prompts share packs
+            assert np.all(np.diff(lengths[mine]) >= 0)
+            # packs cover the rank's requests in order and respect the reference's limits
+            assert [j for g in packs for j in g] == list(range(len(mine)))
+            for g in packs:
+                assert len(g) <= 16 and (len(g) == 1 or lengths[mine[list(g)]].sum() <= 4096)
+            seen += mine.tolist()
+        assert sorted(seen) == list(range(64))
         loads = np.array([cost[where == r].sum() for r in range(world)])
         assert loads.max() / loads.mean() < 1.15
-        assert np.bincount(where, minlength=world).sum() == 64
-    # packs respect the reference's limits and keep order
-    groups = dispatch.packs([4000, 100, 50, 5000] + [10] * 40)
+    # the pack limits themselves, order kept (batching.rs:9-25)
+    groups = M.ranges([4000, 100, 50, 5000] + [10] * 40)
     assert [list(g) for g in groups][:3] == [[0], [1, 2], [3]]
     assert all(len(g) <= 16 for g in groups)

@@ -40,7 +40,7 @@ def test_layer_outputs_and_last_hidden_match_the_oracle(setup):
     rng = np.random.default_rng(0)
     prompts = [rng.integers(0, cfg.vocab, n).tolist() for n in (150, 1, 67)]
     last, layers = model.forward_batch(prompts, want_layers=True)
-    want_last, want_layers = O.forward(cfg.oracle_dict(), weights, np.concatenate(prompts), [len(p) for p in prompts],
+    want_last, want_layers = O.forward(cfg.shape_dict(), weights, np.concatenate(prompts), [len(p) for p in prompts],
                                        want_layers=True)
     # per-layer residual stream: bf16 activations, float32 accumulation on both sides
     for li in range(cfg.n_layers):
@@ -154,15 +154,26 @@ def test_graph_replay_equals_eager(setup):
     eager_a, eager_b = model.forward_batch(a), model.forward_batch(b)
     model.enable_graphs(True)
     try:
-        miss = model.forward_batch(a)          # eager + capture
+        base = model.graph_stats()             # the counters run over the model's life
+
+        def since():
+            now = model.graph_stats()
+            return now["captures"] - base["captures"], now["replays"] - base["replays"]
+
+        first = model.forward_batch(a)         # first sight of the length vector: eager, remembered
+        assert since() == (0, 0)
+        second = model.forward_batch(a)        # second sight: recorded, and the recording launched
+        assert since() == (1, 1)
         hit_a = model.forward_batch(a)         # replay
         hit_b = model.forward_batch(b)         # replay with other ids
-        stats = model.graph_stats()
-        assert stats["captures"] >= 1 and stats["replays"] >= 2 and stats["enabled"]
-        assert np.array_equal(miss, eager_a) and np.array_equal(hit_a, eager_a) and np.array_equal(hit_b, eager_b)
-        for n in range(1, 66):                 # 65 distinct shapes: the first capture is evicted
+        assert since() == (1, 3) and model.graph_stats()["enabled"]
+        assert np.array_equal(first, eager_a) and np.array_equal(second, eager_a)
+        assert np.array_equal(hit_a, eager_a) and np.array_equal(hit_b, eager_b)
+        for n in range(1, 66):                 # 65 distinct shapes recorded: the first recording is evicted
+            model.forward_batch([[1] * n])
             model.forward_batch([[1] * n])
         before = model.graph_stats()["captures"]
+        model.forward_batch(a)                 # forgotten: seen "for the first time" again
         model.forward_batch(a)
         assert model.graph_stats()["captures"] == before + 1
     finally:
@@ -222,7 +233,7 @@ def test_truncated_large_shapes_match_the_oracle(cs1, name, shape):
         last, layers = model.forward_batch(prompts, want_layers=True)
     finally:
         model.close()
-    want_last, want_layers = O.forward(cfg.oracle_dict(), weights, np.concatenate(prompts), [len(p) for p in prompts],
+    want_last, want_layers = O.forward(cfg.shape_dict(), weights, np.concatenate(prompts), [len(p) for p in prompts],
                                        want_layers=True)
     for li in range(cfg.n_layers):
         assert rel_l2(f32(layers[li]), f32(want_layers[li])) < 2e-2, (name, li)
