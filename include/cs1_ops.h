@@ -132,7 +132,7 @@ void cs1_gemm_destroy(void* gemm);
 int cs1_gemm(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream);
 
 /* ---- vision tower (single image, hidden 1024, 16 heads of 64): ops.h:125-138, vision.cu, gemm.cu:137-163.
- * linear: y = bf16(x w^T + bias), the bias joining the float32 sum (cuBLASLt, as in the reference);
+ * linear: y = bf16(x w^T + bias), the bias joining the float32 sum (a library call in the reference, the tcgen05 kernel's bias epilogue here);
  * gemm_f32: float32 throughout; norm: LayerNorm eps 1e-6; position: x += bf16(sum of four table rows times
  * their weights), separate float32 multiplies and adds; rope: q, k out of the fused [n, 3072] projection, cos / sin
  * [n, 32] float32, both products rounded before the add; attention: every query over all n keys, v a slice of

@@ -33,8 +33,7 @@ int s1_device_sync(void);
  * launched so may become resident while the kernel before it on the stream still runs, sets up
  * (the GEMMs also fetch their first weight tiles) and waits for that kernel to complete before it
  * touches activations. Results are the same bits in every mode. Returns the previous mode. The
- * executor picks per forward pass by the number of tokens (s1_model_set_overlap_tokens);
- * S1_PDL=1 / 2 / 0 in the environment force a mode for every launch. */
+ * executor picks per forward pass by the number of tokens (s1_model_set_overlap_tokens). */
 int s1_set_dependent_launch(int mode);
 int s1_mem_info(size_t* free_bytes, size_t* total_bytes);
 
@@ -78,16 +77,23 @@ int s1_device_status(int* gemm, int* attention, int* gdn);
  * the GEMM's error word and the kernel returns. The context stays usable. */
 int s1_selftest_wait_runs_out(int limit_us, void* stream);
 
-/* ---- GEMM engines behind cs1_gemm, pinned (benchmark arms and parity tests) ---- */
-int s1_gemm_cublaslt(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream);
+/* ---- the two kernels behind cs1_gemm, pinned (benchmark arms and parity tests) ---- */
+/* The plain CUDA-core kernel that serves what TMA cannot address (K below 64 or not a multiple
+ * of 8, unaligned operands): float32 FMAs over k in order, any sizes. */
+int s1_gemm_plain(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream);
+/* Planner overrides of the tcgen05 kernels, for the schedule tests and tuning runs: tile width
+ * (0 = the planner's choice), K shares per tile (0 = the planner's), contiguous runs in the pair
+ * kernel (0 never, 1 always, 2 by the estimate), and the row count up to which the single-block
+ * kernel takes problems of more than 128 rows (0 = by the estimates). Process-wide. */
+int s1_gemm_plan_override(int bn, int splits, int runs, int small_rows);
 /* cs1_gemm with the K-split path switched off for this call. */
 int s1_gemm_unsplit(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream);
 /* gemm: a cs1_gemm_create handle whose workspace the K-split path may use, or null (no split). */
 int s1_gemm_tcgen05(void* gemm, const void* x, const void* w, void* y, int M, int N, int K, int ldy, void* stream);
 /* act [M, I] (rows of ld) = silu(x w[0:I]^T) * (x w[I:2I]^T) in one kernel, bit-identical to cs1_gemm
  * into [M, 2 I] followed by cs1_silu_mul (the reference's MLP sequence, model.rs:1301-1316).
- * CS1_ERR_UNSUPPORTED when the tcgen05 engine cannot take the problem (M <= 128, K % 8 != 0, other
- * engine selected): run the two operators then. */
+ * CS1_ERR_UNSUPPORTED when the pair kernel cannot take the problem (M <= 128, K % 8 != 0): run the
+ * two operators then. */
 int s1_gemm_swiglu(void* gemm, const void* x, const void* w, void* act, int M, int I, int K, int ld, void* stream);
 /* Waits for the device, returns in *code the error word of the tcgen05 GEMM (0 = no bounded
  * wait gave up) and clears it. */
@@ -137,13 +143,15 @@ void* s1_model_stream(void* model);
  * second time (the pass is recorded and the recording launched, with no wait for the stream):
  * ragged request sets rarely repeat a vector, and a first sight then costs one eager pass only. */
 int s1_model_enable_graphs(void* model, int on);
-/* Exact packing (off by default): a prompt's hidden states come out bit-identical whether it
+/* Exact packing (on by default): a prompt's hidden states come out bit-identical whether it
  * runs alone, inside a pack, or as a continuation of a captured prefix. Every GEMM then runs on
  * whole tiles (no K range shared between blocks), which makes a row's result independent of the
- * call's row count; a shape this library's engine does not take (cuBLASLt) runs per sequence,
- * as the reference does for its out/down projections (model.rs:723-739). With it off the
- * planner may share K by the row count: faster on a few shapes, and equal to single execution
- * within rounding (the reference's gate is 0.01 on the logits). */
+ * call's row count, so the out/down projections need not run per sequence as they do in the
+ * reference (model.rs:723-739). Off: the planner may share K between blocks by the row count,
+ * which is faster with few rows (2-3x on the narrow projections at 32-128 tokens) but changes the
+ * summation order with the row count: measured on a 4-layer 9B-width decoder with random weights,
+ * packed and alone logits then differ by up to 0.02, twice the reference's gate of 0.01
+ * (tests/open_jev/prefill_batch.rs:57-64) - hence the default. */
 int s1_model_set_exact_packing(void* model, int on);
 /* The executor's fused kernels, on by default, each with the same bits as the operators it
  * replaces: the MLP's gate/up projection and SiLU-multiply as one kernel (s1_gemm_swiglu), and the
@@ -153,7 +161,7 @@ int s1_model_set_fused_mlp(void* model, int on);
 /* Forward passes of at most `tokens` tokens that are issued eagerly launch every kernel as a
  * programmatic dependent of the one before it (s1_set_dependent_launch mode 1); longer ones, and
  * every pass recorded into a CUDA graph, only the GEMMs and norms (mode 2); tokens < 0: plain stream order
- * always. Default 128 (S1_PDL_TOKENS in the environment at s1_model_create). With few tokens and
+ * always. Default 128. With few tokens and
  * eager issue the gaps between launches are what there is to hide; otherwise short kernels' blocks
  * that only wait take room from the running GEMM, while a GEMM's early blocks fetch their first
  * weight tiles under the short kernel ahead. The result's bits do not depend on it. */
@@ -235,9 +243,10 @@ int s1_model_unfilled(void* model, char* name_out, size_t cap);
 int s1_model_profile(void* model, int on);
 /* Waits for the stream, then returns and resets: device milliseconds per family since the
  * last read (profile mode only; ms nullable), kernels of this library launched per family
- * (nullable, a graph replay counts the kernels it holds) and launches handed to cuBLASLt (nullable). */
+ * (nullable, a graph replay counts the kernels it holds); *library_launches (nullable) is always 0:
+ * no vendor library is linked. */
 int s1_model_profile_read(void* model, float* ms, long long* launches, long long* library_launches);
-/* 1 if cs1_gemm would run this problem on the tcgen05 kernel of this library, 0 if on cuBLASLt. */
+/* 1 if cs1_gemm would run this problem on the tcgen05 kernels, 0 if on the plain kernel. */
 int s1_gemm_engine(void* gemm, const void* x, const void* w, int M, int N, int K);
 
 /* DecisionHead::score (open_jev executor.rs:56-68) and letter_logits (cua_s1 executor.rs:61-78):

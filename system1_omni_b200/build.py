@@ -51,9 +51,21 @@ def build(verbose=False, force=False, ptxas_info=False):
         raise RuntimeError("nvcc failed")
     if force or procs or _stale(OUT, objs):
         lib64 = os.path.join(CUDA_HOME, "lib64")
-        cmd = [NVCC, "-shared", "-o", OUT] + objs + ["-L" + lib64, "-lcublasLt", "-Xlinker", "-rpath", "-Xlinker", lib64]
+        cmd = [NVCC, "-shared", "-o", OUT] + objs + ["-L" + lib64, "-ldl", "-Xlinker", "-rpath", "-Xlinker", lib64]
         subprocess.run(cmd, check=True)
+    build_compare()
     return OUT
+
+
+def build_compare():
+    """The microbenchmark's comparison arm (the vendor library's GEMM) as a library of its own."""
+    src = os.path.join(PKG, "compare", "library_gemm.cpp")
+    out = os.path.join(PKG, "compare", "libs1_compare.so")
+    if _stale(out, [src]):
+        lib64 = os.path.join(CUDA_HOME, "lib64")
+        subprocess.run([NVCC, "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-o", out, src, "-L" + lib64,
+                        "-lcublasLt", "-Xlinker", "-rpath", "-Xlinker", lib64], check=True)
+    return out
 
 
 if __name__ == "__main__":

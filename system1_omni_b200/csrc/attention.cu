@@ -1,21 +1,16 @@
 // Full-attention layers: q/k preparation (per-head RMSNorm, partial rotary embedding, gate
-// split) and causal grouped-query flash attention with the sigmoid output gate fused into
-// the epilogue, for head dims 128 and 256.
-//
-// The attention kernel keeps the online softmax and the output tile in registers
-// (FlashAttention-2 schedule on mma.sync m16n8k16): one block takes 64 queries of one head,
-// four warps of 16 rows, and walks the keys in double-buffered cp.async tiles. Probabilities
-// are rounded to bf16 for P*V while the running sums stay float32, and the gated epilogue
-// rounds both factors to bf16 before multiplying, which makes the fused result equal to
-// attention followed by a separate gate pass bit for bit, and a windowed launch equal to
-// the rows of a full launch (reference contract: src/backends/cuda/qwen3_5/attention.cu:84-233,
+// split) and the entry points of causal grouped-query attention with the sigmoid output gate,
+// for head dims 128 and 256. The attention itself is the tcgen05 kernel of attention_tc5.cu:
+// probabilities are rounded to bf16 for P*V while the running sums stay float32, and the gated
+// epilogue rounds both factors to bf16 before multiplying, which makes the fused result equal
+// to attention followed by a separate gate pass bit for bit, and a windowed launch equal to the
+// rows of a full launch (reference contract: src/backends/cuda/qwen3_5/attention.cu:84-233,
 // tests/qwen3_5/kernels.rs:273-474,852-929).
 #include <math.h>
 
 #include "attention_tc5.h"
 #include "common.cuh"
 #include "cs1_ops.h"
-#include "mma.cuh"
 
 namespace s1 {
 namespace {
@@ -80,202 +75,7 @@ __global__ void __launch_bounds__(256)
     }
 }
 
-// ---- flash attention ----
-constexpr int BM = 64, FA_THREADS = 128;
-
-template <int DH, int BN>
-struct FaSmem {
-    static constexpr int LDS = DH + 8;  // row stride in elements; 16 extra bytes keep ldmatrix conflict-free
-    static constexpr int BYTES = (BM + 4 * BN) * LDS * 2;
-};
-
-template <int DH, int BN, bool GATED>
-__global__ void __launch_bounds__(FA_THREADS)
-    flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v, int ldv,
-                 const bf16* __restrict__ gate, bf16* __restrict__ out, int T, int Hq, int Hk, float scale_log2,
-                 int q_base, const bf16* __restrict__ kpre, const bf16* __restrict__ vpre, int ldvpre, int own_base) {
-    // Rows are absolute positions. Keys and values of positions below own_base come from the
-    // shared prefix buffers (kpre, vpre); q, gate, out, k and v hold the positions from own_base
-    // on, indexed from zero. own_base = 0: everything in q, k, v (the plain and q_base entries).
-    constexpr int LDS = FaSmem<DH, BN>::LDS;
-    constexpr int NT = BN / 8;   // score tiles per warp row block
-    constexpr int DT = DH / 8;   // output tiles
-    extern __shared__ __align__(16) unsigned char smem[];
-    bf16* qs = reinterpret_cast<bf16*>(smem);
-    bf16* ks = qs + BM * LDS;           // [2][BN][LDS]
-    bf16* vs = ks + 2 * BN * LDS;       // [2][BN][LDS]
-    const int h = blockIdx.y, hk = h / (Hq / Hk);
-    const int q0 = q_base + (gridDim.x - 1 - blockIdx.x) * BM;  // longest blocks first
-    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-    const int g = lane / 4, t = lane % 4;
-    const int row0 = q0 + warp * 16;
-
-    constexpr int CPR = DH / 8;  // 16-byte chunks per row
-    for (int c = tid; c < BM * CPR; c += FA_THREADS) {
-        const int r = c / CPR, col = (c % CPR) * 8, row = q0 + r;
-        cp_async16(qs + r * LDS + col, q + ((size_t)(min(row, T - 1) - own_base) * Hq + h) * DH + col, row < T);
-    }
-    const int kv_end = min(T, q0 + BM);
-    const int ntiles = (kv_end + BN - 1) / BN;
-    auto load_kv = [&](int tile, int stage) {
-        const int k0 = tile * BN;
-        bf16* kd = ks + stage * BN * LDS;
-        bf16* vd = vs + stage * BN * LDS;
-        for (int c = tid; c < BN * CPR; c += FA_THREADS) {
-            const int r = c / CPR, col = (c % CPR) * 8, row = k0 + r;
-            const bool ok = row < kv_end;
-            const int rr = min(row, T - 1);
-            if (rr < own_base) {
-                cp_async16(kd + r * LDS + col, kpre + ((size_t)rr * Hk + hk) * DH + col, ok);
-                cp_async16(vd + r * LDS + col, vpre + (size_t)rr * ldvpre + (size_t)hk * DH + col, ok);
-            } else {
-                cp_async16(kd + r * LDS + col, k + ((size_t)(rr - own_base) * Hk + hk) * DH + col, ok);
-                cp_async16(vd + r * LDS + col, v + (size_t)(rr - own_base) * ldv + (size_t)hk * DH + col, ok);
-            }
-        }
-    };
-    load_kv(0, 0);
-    cp_async_commit();
-
-    float o[DT][4];
-#pragma unroll
-    for (int n = 0; n < DT; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-
-    for (int j = 0; j < ntiles; j++) {
-        if (j + 1 < ntiles) {
-            load_kv(j + 1, (j + 1) & 1);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
-        const bf16* kt = ks + (j & 1) * BN * LDS;
-        const bf16* vt = vs + (j & 1) * BN * LDS;
-        const int k0 = j * BN;
-
-        float s[NT][4];
-#pragma unroll
-        for (int n = 0; n < NT; n++) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
-#pragma unroll
-        for (int kk = 0; kk < DH / 16; kk++) {
-            uint32_t a[4];
-            load_a_rm(a, qs, LDS, warp * 16, kk * 16, lane);
-#pragma unroll
-            for (int np = 0; np < NT / 2; np++) {
-                uint32_t b[4];
-                load_b_nk(b, kt, LDS, np * 16, kk * 16, lane);
-                mma_bf16(s[2 * np], a, b[0], b[1]);
-                mma_bf16(s[2 * np + 1], a, b[2], b[3]);
-            }
-        }
-        // causal mask on tiles that reach past this warp's first row
-        if (k0 + BN - 1 > row0) {
-#pragma unroll
-            for (int n = 0; n < NT; n++) {
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const int key = k0 + n * 8 + 2 * t + (e & 1);
-                    const int row = row0 + g + (e >> 1) * 8;
-                    if (key > row) s[n][e] = -INFINITY;
-                }
-            }
-        }
-        float alpha[2];
-#pragma unroll
-        for (int r = 0; r < 2; r++) {
-            float mx = -INFINITY;
-#pragma unroll
-            for (int n = 0; n < NT; n++) mx = fmaxf(mx, fmaxf(s[n][2 * r], s[n][2 * r + 1]));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float mn = fmaxf(m[r], mx * scale_log2);
-            alpha[r] = exp2f(m[r] - mn);
-            m[r] = mn;
-            float sum = 0.f;
-#pragma unroll
-            for (int n = 0; n < NT; n++) {
-                const float p0 = exp2f(s[n][2 * r] * scale_log2 - mn);
-                const float p1 = exp2f(s[n][2 * r + 1] * scale_log2 - mn);
-                s[n][2 * r] = p0;
-                s[n][2 * r + 1] = p1;
-                sum += p0 + p1;
-            }
-            l[r] = l[r] * alpha[r] + sum;
-        }
-#pragma unroll
-        for (int n = 0; n < DT; n++) {
-            o[n][0] *= alpha[0];
-            o[n][1] *= alpha[0];
-            o[n][2] *= alpha[1];
-            o[n][3] *= alpha[1];
-        }
-#pragma unroll
-        for (int kt2 = 0; kt2 < BN / 16; kt2++) {
-            uint32_t a[4];
-            a[0] = pack2(s[2 * kt2][0], s[2 * kt2][1]);
-            a[1] = pack2(s[2 * kt2][2], s[2 * kt2][3]);
-            a[2] = pack2(s[2 * kt2 + 1][0], s[2 * kt2 + 1][1]);
-            a[3] = pack2(s[2 * kt2 + 1][2], s[2 * kt2 + 1][3]);
-#pragma unroll
-            for (int dp = 0; dp < DT / 2; dp++) {
-                uint32_t b[4];
-                load_b_kn(b, vt, LDS, kt2 * 16, dp * 16, lane);
-                mma_bf16(o[2 * dp], a, b[0], b[1]);
-                mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
-            }
-        }
-        __syncthreads();  // every warp is done with this stage before it is refilled
-    }
-
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-    }
-    const float inv[2] = {1.f / l[0], 1.f / l[1]};
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-        const int row = row0 + g + r * 8;
-        if (row >= T) continue;
-        const size_t base = ((size_t)(row - own_base) * Hq + h) * DH + 2 * t;
-#pragma unroll
-        for (int n = 0; n < DT; n++) {
-            float a = o[n][2 * r] * inv[r], b = o[n][2 * r + 1] * inv[r];
-            if constexpr (GATED) {
-                const uint32_t gw = *reinterpret_cast<const uint32_t*>(gate + base + n * 8);
-                // attention -> bf16 store -> bf16 sigmoid -> multiply, without the store
-                a = rbf(a) * rbf(sigmoid(__uint_as_float(gw << 16)));
-                b = rbf(b) * rbf(sigmoid(__uint_as_float(gw & 0xffff0000u)));
-            }
-            *reinterpret_cast<uint32_t*>(out + base + n * 8) = pack2(a, b);
-        }
-    }
-}
-
-template <int DH, int BN, bool GATED>
-int launch_flash(const bf16* q, const bf16* k, const bf16* v, int ldv, const bf16* gate, bf16* out, int T, int Hq,
-                 int Hk, float scale, int q_base, cudaStream_t st, const bf16* kpre = nullptr,
-                 const bf16* vpre = nullptr, int ldvpre = 0, int own_base = 0) {
-    constexpr int BYTES = FaSmem<DH, BN>::BYTES;
-    // Raise the dynamic shared memory limit once per device.
-    static bool configured[64] = {};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return e;
-    if (dev >= 64) return cudaErrorInvalidDevice;
-    if (!configured[dev]) {
-        e = cudaFuncSetAttribute(flash_kernel<DH, BN, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, BYTES);
-        if (e != cudaSuccess) return e;
-        configured[dev] = true;
-    }
-    constexpr float LOG2E = 1.4426950408889634f;
-    const dim3 grid((T - q_base + BM - 1) / BM, Hq);
-    flash_kernel<DH, BN, GATED><<<grid, FA_THREADS, BYTES, st>>>(q, k, v, ldv, gate, out, T, Hq, Hk, scale * LOG2E,
-                                                                q_base, kpre, vpre, ldvpre, own_base);
-    return cudaGetLastError();
-}
+constexpr int BM = 64;  // a window starts on a multiple of 64 rows (the delta rule's chunk, model.rs:955-958)
 
 template <bool GATED>
 int attention_entry(const void* q, const void* k, const void* v, int ldv, const void* gate, void* out, int T, int Hq,
@@ -292,11 +92,8 @@ int attention_entry(const void* q, const void* k, const void* v, int ldv, const 
     const bf16* gp = static_cast<const bf16*>(gate);
     bf16* op = static_cast<bf16*>(out);
     // one kernel for every size, so that a window and the one-shot pass round alike
-    if (s1_attn_tc5_enabled())
-        return s1_attn_tc5(qp, kp, vp, ldv, GATED ? gp : nullptr, op, T, Hq, Hk, Dh, scale, q_base, nullptr, nullptr, 0, 0,
-                           as_stream(stream));
-    if (Dh == 256) return launch_flash<256, 32, GATED>(qp, kp, vp, ldv, gp, op, T, Hq, Hk, scale, q_base, as_stream(stream));
-    return launch_flash<128, 64, GATED>(qp, kp, vp, ldv, gp, op, T, Hq, Hk, scale, q_base, as_stream(stream));
+    return s1_attn_tc5(qp, kp, vp, ldv, GATED ? gp : nullptr, op, T, Hq, Hk, Dh, scale, q_base, nullptr, nullptr, 0, 0,
+                       as_stream(stream));
 }
 
 }  // namespace
@@ -365,14 +162,8 @@ extern "C" int s1_attention_gated_shared_prefix(const void* q, const void* k, co
     const bf16* gp = static_cast<const bf16*>(gate);
     bf16* op = static_cast<bf16*>(out);
     const int T = prefix_len + rows;
-    if (s1_attn_tc5_enabled())
-        return s1_attn_tc5(qp, kp, vp, ldv, gp, op, T, Hq, Hk, Dh, scale, prefix_len, kpre, vpre, ldv_prefix, prefix_len,
-                           as_stream(stream));
-    if (Dh == 256)
-        return launch_flash<256, 32, true>(qp, kp, vp, ldv, gp, op, T, Hq, Hk, scale, prefix_len, as_stream(stream), kpre,
-                                           vpre, ldv_prefix, prefix_len);
-    return launch_flash<128, 64, true>(qp, kp, vp, ldv, gp, op, T, Hq, Hk, scale, prefix_len, as_stream(stream), kpre, vpre,
-                                       ldv_prefix, prefix_len);
+    return s1_attn_tc5(qp, kp, vp, ldv, gp, op, T, Hq, Hk, Dh, scale, prefix_len, kpre, vpre, ldv_prefix, prefix_len,
+                       as_stream(stream));
 }
 
 extern "C" int cs1_attention_gated_prefix(const void* q, const void* k, const void* v, int ldv, const void* gate,

@@ -436,14 +436,6 @@ int launch_attn(const AttnMaps& maps, const bf16* gate, bf16* out, int T, int Hq
 
 using namespace s1;
 
-bool s1_attn_tc5_enabled() {
-    static const bool on = [] {
-        const char* v = getenv("S1_ATTN");
-        return !(v && strcmp(v, "mma") == 0);
-    }();
-    return on;
-}
-
 int s1_attn_tc5(const bf16* q, const bf16* k, const bf16* v, int ldv, const bf16* gate, bf16* out, int T, int Hq, int Hk,
                 int Dh, float scale, int q_base, const bf16* kpre, const bf16* vpre, int ldvpre, int own_base,
                 cudaStream_t st) {

@@ -3,8 +3,6 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
-// False when S1_ATTN=mma is in the environment (the mma.sync kernel then serves every call).
-bool s1_attn_tc5_enabled();
 // Causal GQA attention of positions [q_base, T) over keys [0, T). q, gate, out, k and v hold the
 // positions from own_base on (indexed from zero); keys and values of positions below own_base are
 // read from kpre / vpre (row stride ldvpre). gate null = ungated. Dh 128 or 256; q, k, v, kpre, vpre

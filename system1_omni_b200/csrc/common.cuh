@@ -1,8 +1,6 @@
 // Device helpers shared by the sm_100a kernels: bf16 conversion, 128-bit packs, warp and
 // block reductions, and the launch-argument checks every entry point performs.
 #pragma once
-#include <stdlib.h>
-
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -108,8 +106,7 @@ inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 // trip to HBM are a large part of every kernel), the GEMMs and the norms after them (its choice
 // otherwise: measured at 1024 tokens +3 %, where making every kernel a dependent costs 1 %: blocks
 // that only wait take room from the running kernel, while a GEMM's blocks that arrive early fetch
-// their first ring of weight tiles under the short kernel ahead), or none. S1_PDL=1 / 2 / 0 in the
-// environment force one.
+// their first ring of weight tiles under the short kernel ahead), or none.
 // Both instructions are no-ops in a kernel launched the ordinary way.
 __device__ __forceinline__ void grid_dep_sync() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -120,30 +117,15 @@ inline int& dep_launch_switch() {
     return mode;
 }
 
-inline int dep_launch_mode() {
-    static const int forced = [] {
-        const char* e = getenv("S1_PDL");
-        return !e ? -1 : (e[0] == '1' ? 1 : e[0] == '2' ? 2 : 0);
-    }();
-    return forced >= 0 ? forced : dep_launch_switch();
-}
+inline int dep_launch_mode() { return dep_launch_switch(); }
 // Kernel families, for the choice of which launches become dependents.
 enum DepFamily { DEP_GEMM = 1, DEP_GDN = 2, DEP_ATTENTION = 4, DEP_NORM = 8, DEP_OTHER = 16 };
 // What the two modes cover, from measurements on the 4B-shaped decoder: the delta-rule kernels are
-// never launched as dependents (their blocks take nearly all of an SM's shared memory while they
-// wait: -4 % at 1024 tokens, and short passes are faster without them too); mode 1 takes everything
-// else, mode 2 the GEMMs and the norms that follow them. S1_PDL_MASK1 / S1_PDL_MASK override, for
-// experiments.
+// never launched as dependents (their blocks take most of an SM's shared memory while they wait:
+// -4 % at 1024 tokens, and short passes are faster without them too); mode 1 takes everything
+// else, mode 2 the GEMMs and the norms that follow them.
 inline int dep_launch_mask(int mode) {
-    static const int mask1 = [] {
-        const char* e = getenv("S1_PDL_MASK1");
-        return e ? atoi(e) : (int)(DEP_GEMM | DEP_ATTENTION | DEP_NORM | DEP_OTHER);
-    }();
-    static const int mask2 = [] {
-        const char* e = getenv("S1_PDL_MASK");
-        return e ? atoi(e) : (int)(DEP_GEMM | DEP_NORM);
-    }();
-    return mode == 1 ? mask1 : mode == 2 ? mask2 : 0;
+    return mode == 1 ? (int)(DEP_GEMM | DEP_ATTENTION | DEP_NORM | DEP_OTHER) : mode == 2 ? (int)(DEP_GEMM | DEP_NORM) : 0;
 }
 inline bool dep_launch_family(int family) { return (dep_launch_mask(dep_launch_mode()) & family) != 0; }
 inline bool dep_launch_enabled() { return dep_launch_family(DEP_OTHER); }

@@ -80,7 +80,7 @@ struct Model {
     void* gemm = nullptr;
     Scratch s;
     bool graph_enabled = false;
-    bool exact_packing = false;
+    bool exact_packing = true;  // whole-tile GEMMs: a prompt's bits do not depend on what it is packed with
     bool fuse_swiglu = true;  // gate/up GEMM and SiLU-multiply as one kernel where the engine supports it
     int overlap_tokens = 128;  // eager passes of at most this many tokens launch every kernel as a programmatic dependent
     bool capturing = false;    // the pass being issued is recorded into a graph
@@ -319,9 +319,7 @@ int op(Model* m, int family, int kernels, F&& call) {
 #define S1_OP(family, kernels, expr) S1_TRY(op(m, family, kernels, [&] { return (expr); }))
 
 int gemm(Model* m, size_t x, const Tensor& w, size_t y, int rows, int n, int k) {
-    const bool own = s1_gemm_engine(m->gemm, m->s.at(x), m->w(w), rows, n, k) == 1;
-    if (!own) m->library_launches++;
-    return op(m, S1_FAMILY_GEMM, own ? 1 : 0, [&] {
+    return op(m, S1_FAMILY_GEMM, 1, [&] {
         // exact packing: whole tiles only, so a row's sum over K runs in one fixed order
         // whatever the row count of the call (packed, alone, or continuing a prefix)
         if (m->exact_packing)
@@ -332,19 +330,13 @@ int gemm(Model* m, size_t x, const Tensor& w, size_t y, int rows, int n, int k) 
 
 // The projections back to the hidden size (out / o / down). The reference runs them per
 // sequence (gemm_sequences, model.rs:723-739) so that a prompt sees the same GEMM shape, hence
-// the same library plan, packed or alone. Under exact packing this library's own engine needs
-// no such split (whole tiles make rows independent of the row count); only a shape that goes
-// to cuBLASLt is still run per sequence. Without exact packing: once over the pack.
+// the same library plan, packed or alone. Here a row's result does not depend on the call's row
+// count once the tiles are whole (exact packing; the plain kernel always sums k in order), so
+// the projection runs once over the pack in every mode.
 int gemm_rows(Model* m, size_t x, const Tensor& w, size_t y, const int* lengths, int nseq, int n, int k) {
     int t = 0;
     for (int i = 0; i < nseq; i++) t += lengths[i];
-    if (!m->exact_packing || s1_gemm_engine(m->gemm, m->s.at(x), m->w(w), t, n, k) == 1) return gemm(m, x, w, y, t, n, k);
-    size_t off = 0;
-    for (int i = 0; i < nseq; i++) {
-        S1_TRY(gemm(m, x + off * k * BF16, w, y + off * n * BF16, lengths[i], n, k));
-        off += lengths[i];
-    }
-    return 0;
+    return gemm(m, x, w, y, t, n, k);
 }
 
 // Second half of a layer (model.rs:1287-1336): residual add + post norm, SwiGLU MLP, residual
@@ -747,7 +739,6 @@ int s1_model_create(const S1Config* cfg, int device, void** out) {
     }
     const char* flag = getenv("CUA_S1_GRAPH");
     m->graph_enabled = flag && strcmp(flag, "1") == 0;
-    if (const char* n = getenv("S1_PDL_TOKENS")) m->overlap_tokens = atoi(n) >= 0 ? atoi(n) : -1;
     *out = m;
     return 0;
 }

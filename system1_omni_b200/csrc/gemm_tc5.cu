@@ -56,7 +56,8 @@ __device__ int g_gemm_error = 0;
 template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_tc5_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
-                    bf16* __restrict__ y, int M, int N, int K, int ldy, int vec_ok, int splits) {
+                    bf16* __restrict__ y, int M, int N, int K, int ldy, int vec_ok, int splits,
+                    const bf16* __restrict__ bias) {
     using namespace tc5;
     using G = Cfg<BN>;
     grid_dep_trigger();
@@ -221,6 +222,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     }
                 } else if (row < M && col0 < N) {
                     bf16* dst = y + (size_t)row * ldy + col0;
+                    if (bias) {  // joins the float32 sum before the one rounding (whole tiles only: splits == 1)
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (col0 + j < N) v[j] = __float_as_uint(__uint_as_float(v[j]) + f32(bias[col0 + j]));
+                    }
                     if (vec_ok && col0 + 32 <= N) {
                         uint4 o[4];
 #pragma unroll
@@ -936,7 +942,7 @@ int cluster_room(DeviceInfo* info, int slot, int c) {
 
 template <int BN>
 int launch(const void* x, const void* w, void* y, int M, int N, int K, int ldy, DeviceInfo* info, int slot, int splits,
-           cudaStream_t st) {
+           cudaStream_t st, const bf16* bias = nullptr) {
     using G = Cfg<BN>;
     const cudaError_t e = prepare<BN>(info, slot);
     if (e != cudaSuccess) return e;
@@ -965,7 +971,7 @@ int launch(const void* x, const void* w, void* y, int M, int N, int K, int ldy, 
     }
     cfg.attrs = attr;
     cfg.numAttrs = n;
-    return cudaLaunchKernelEx(&cfg, gemm_tc5_kernel<BN>, mx, mw, static_cast<bf16*>(y), M, N, K, ldy, vec_ok, splits);
+    return cudaLaunchKernelEx(&cfg, gemm_tc5_kernel<BN>, mx, mw, static_cast<bf16*>(y), M, N, K, ldy, vec_ok, splits, bias);
 }
 
 // Plan for at most 128 rows: the column-block width and over how many blocks of a cluster a
@@ -980,15 +986,21 @@ struct SmallPlan {
     int bn, splits;
     double us;  // the estimate it was chosen by
 };
+// Planner overrides for the schedule tests and for tuning runs (s1_gemm_plan_override); 0 = the
+// planners decide. Process-wide, plain reads on the launch path.
+struct PlanOverride {
+    int bn = 0, splits = 0;
+    int runs = 2;        // contiguous runs in the pair kernel: 0 never, 1 always, 2 by the estimate
+    int small_rows = 0;  // up to this many rows the single-block kernel, above it the pair kernel
+};
+PlanOverride g_override;
 constexpr double SMALL_KB_US[3] = {0.38, 0.31, 0.30};  // widths 256, 128, 64
 constexpr double SMALL_W_BYTES_PER_US = 4.5e6;
 
 SmallPlan small_plan(int M, int N, int K, DeviceInfo* info, bool may_split) {
     const int kblocks = (K + BK - 1) / BK;
     const int rows = M < BM ? M : BM;
-    int force_bn = 0, force_s = 0;
-    if (const char* f = getenv("S1_GEMM_BN")) force_bn = atoi(f);
-    if (const char* f = getenv("S1_GEMM_SPLITS")) force_s = atoi(f);
+    const int force_bn = g_override.bn, force_s = g_override.splits;
     const int widths[3] = {256, 128, 64};
     SmallPlan best{64, 1, 1e30};
     double best_cost = 1e30;
@@ -1040,11 +1052,7 @@ constexpr double RUN_KB_COST = 1.3;
 PairPlan pair_plan(int M, int N, int K, int pairs, size_t partial_bytes, int counter_slots) {
     const long num_m = (M + 2 * BM - 1) / (2 * BM);
     const int kblocks = (K + BK - 1) / BK;
-    // tuning knobs (S1_GEMM_RUNS: 0 never, 1 always, otherwise by the estimate)
-    int force_bn = 0, force_s = 0, force_run = 2;
-    if (const char* f = getenv("S1_GEMM_BN")) force_bn = atoi(f);
-    if (const char* f = getenv("S1_GEMM_SPLITS")) force_s = atoi(f);
-    if (const char* f = getenv("S1_GEMM_RUNS")) force_run = atoi(f);
+    const int force_bn = g_override.bn, force_s = g_override.splits, force_run = g_override.runs;
     PairPlan best{256, 1, 0, 1e30};
     for (int bn = 256; bn >= 64; bn -= 32) {
         if (force_bn && bn != force_bn) continue;
@@ -1138,22 +1146,12 @@ int launch_pair_swiglu(const void* x, const void* w, void* act, int M, int I, in
 // Which kernel takes a problem of more than 128 rows: the pair kernel, or the single-block kernel
 // whose clusters share K. By the two planners' estimates; with few rows and a narrow result
 // (N = 2560 ... 5120 at up to some 700 rows) the pair kernel has too few 256-row tiles to fill the
-// GPU and its shared-tile schedules pay for partial tiles in global memory. S1_GEMM_SMALL_ROWS=n
-// The single-block estimate runs up to 20 % low with several row blocks (measured against both
-// kernels on the projections of the three model sizes at 192 to 1024 rows), so it has to win by
-// 15 %. S1_GEMM_SMALL_ROWS=n overrides: up to n rows the single-block kernel, above it the pair kernel.
+// GPU and its shared-tile schedules pay for partial tiles in global memory. The single-block
+// estimate runs up to 20 % low with several row blocks (measured against both kernels on the
+// projections of the three model sizes at 192 to 1024 rows), so it has to win by 15 %.
 bool single_block_wins(double single_us, double pair_us, int M) {
-    if (const char* v = getenv("S1_GEMM_SMALL_ROWS"))
-        if (atoi(v) > 0) return M <= atoi(v);
+    if (g_override.small_rows > 0) return M <= g_override.small_rows;
     return single_us < 0.85 * pair_us;
-}
-
-bool pair_enabled() {
-    static const bool on = [] {
-        const char* v = getenv("S1_GEMM_PAIR");
-        return !(v && v[0] == '0');
-    }();
-    return on;
 }
 
 }  // namespace
@@ -1176,8 +1174,7 @@ int s1_gemm_tc5(const void* x, const void* w, void* y, int M, int N, int K, int 
     // rows, so the k-blocks of a tile stay in one block.
     const SmallPlan plan = small_plan(M, N, K, info, scratch != nullptr);
     // More than one row block: the CTA-pair kernel unless the single-block one is estimated faster
-    // (S1_GEMM_PAIR=0 keeps the single-block one, for A/B runs).
-    if (M > BM && pair_enabled()) {
+    if (M > BM) {
         const bool fix = scratch && scratch->partials && scratch->counters;
         const PairPlan pair = pair_plan(M, N, K, info->sms / 2, fix ? scratch->partial_bytes : 0, fix ? scratch->counter_slots : 0);
         if (!single_block_wins(plan.us, pair.us, M))
@@ -1191,7 +1188,7 @@ int s1_gemm_tc5(const void* x, const void* w, void* y, int M, int N, int K, int 
 }
 
 bool s1_gemm_tc5_swiglu_supported(const void* x, const void* w, int M, int I, int K) {
-    if (!(M > BM && I > 0 && K >= 64 && K % 8 == 0 && aligned16(x) && aligned16(w) && pair_enabled())) return false;
+    if (!(M > BM && I > 0 && K >= 64 && K % 8 == 0 && aligned16(x) && aligned16(w))) return false;
     cudaError_t err;
     DeviceInfo* info = device_info(&err);
     if (!info) return false;
@@ -1206,6 +1203,32 @@ int s1_gemm_tc5_swiglu(const void* x, const void* w, void* act, int M, int I, in
     DeviceInfo* info = device_info(&err);
     if (!info) return err;
     return launch_pair_swiglu(x, w, act, M, I, K, ld, info, st);
+}
+
+// y = bf16(x w^T + bias) on the single-block kernel with whole tiles (the bias joins the float32
+// sum in the epilogue), for any number of rows.
+int s1_gemm_tc5_bias(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int ldy, cudaStream_t st) {
+    cudaError_t err;
+    DeviceInfo* info = device_info(&err);
+    if (!info) return err;
+    const bf16* b = static_cast<const bf16*>(bias);
+    const long t256 = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
+    if (t256 >= info->sms || N % 256 == 0) return launch<256>(x, w, y, M, N, K, ldy, info, 0, 1, st, b);
+    const long t128 = (long)((M + BM - 1) / BM) * ((N + 127) / 128);
+    if (t128 >= info->sms) return launch<128>(x, w, y, M, N, K, ldy, info, 1, 1, st, b);
+    return launch<64>(x, w, y, M, N, K, ldy, info, 2, 1, st, b);
+}
+
+// Planner overrides for the schedule tests and for tuning runs: tile width (0 = planner's
+// choice), K shares per tile (0 = planner's), contiguous runs in the pair kernel (0 never, 1
+// always, 2 by the estimate), and the row count up to which the single-block kernel takes
+// problems of more than 128 rows (0 = by the estimates). Process-wide.
+extern "C" int s1_gemm_plan_override(int bn, int splits, int runs, int small_rows) {
+    g_override.bn = bn > 0 ? bn : 0;
+    g_override.splits = splits > 0 ? splits : 0;
+    g_override.runs = runs == 0 || runs == 1 ? runs : 2;
+    g_override.small_rows = small_rows > 0 ? small_rows : 0;
+    return 0;
 }
 
 // Diagnostics: how many clusters of c blocks of the single-block kernel of width bn the current

@@ -22,6 +22,11 @@ bool s1_gemm_tc5_supported(const void* x, const void* w, const void* y, int M, i
 int s1_gemm_tc5(const void* x, const void* w, void* y, int M, int N, int K, int ldy, const S1GemmScratch* scratch,
                 cudaStream_t stream);
 
+// y [M, N] (rows of ldy) = bf16(x w^T + bias), bias [N] bf16 added to the float32 sum before the one
+// rounding; whole tiles on the single-block kernel, any M. Same support rule and return codes.
+int s1_gemm_tc5_bias(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int ldy,
+                     cudaStream_t stream);
+
 // The MLP's first half in one kernel: act [M, I] (rows of ld) = silu(x w[0:I]^T) * (x w[I:2I]^T),
 // each projection rounded to bf16 before the activation (bit-identical to the GEMM followed
 // by the SiLU-multiply operator). Needs more than 128 rows (the pair kernel).

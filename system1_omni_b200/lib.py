@@ -88,7 +88,8 @@ SIGNATURES = {
     "s1_memset_async": (i32, [vp, i32, sz, vp]),
     "s1_device_sync": (i32, []),
     "s1_mem_info": (i32, [C.POINTER(sz), C.POINTER(sz)]),
-    "s1_gemm_cublaslt": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+    "s1_gemm_plain": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+    "s1_gemm_plan_override": (i32, [i32, i32, i32, i32]),
     "s1_gemm_tcgen05": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "s1_gemm_tc5_status": (i32, [ip]),
     "s1_gemm_tc5_cluster_room": (i32, [i32, i32]),

@@ -145,10 +145,22 @@ MODEL_SHAPES = {
 }
 
 
+def compare_library():
+    """The vendor library's GEMM as a comparison arm, from its own shared object; None if it was not built."""
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "compare", "libs1_compare.so")
+    if not os.path.exists(path):
+        return None
+    lib = C.CDLL(path)
+    lib.s1_compare_library_gemm.restype = C.c_int
+    lib.s1_compare_library_gemm.argtypes = [C.c_void_p] * 3 + [C.c_int] * 3 + [C.c_void_p]
+    return lib
+
+
 def gemm(b, out):
     lib, st = b.lib, b.stream.handle
     _, tf, src = peaks()
     handle = lib.cs1_gemm_create(32 << 20)
+    compare = compare_library()
     shapes = []
     for name, (h, I, gdn_in, vd, attn_in, attn_out) in MODEL_SHAPES.items():
         for M in ((64, 128, 1024, 4096) if name == "4B" else (1024,)):
@@ -166,14 +178,16 @@ def gemm(b, out):
         x = b.bf16(M * K)
         y = L.DeviceBuffer(M * N * 2)
         row = {"model": model, "proj": proj, "M": M, "N": N, "K": K, "flops": 2.0 * M * N * K, "weight_copies": n}
-        for engine, call in (("tcgen05", lambda i: lib.s1_gemm_tcgen05(handle, x.at(), ws[i].at(), y.at(), M, N, K, N, st)),
-                             ("cublaslt", lambda i: lib.s1_gemm_cublaslt(handle, x.at(), ws[i].at(), y.at(), M, N, K,
-                                                                         N, st))):
+        arms = [("tcgen05", lambda i: lib.s1_gemm_tcgen05(handle, x.at(), ws[i].at(), y.at(), M, N, K, N, st))]
+        if compare is not None:
+            arms.append(("cublaslt", lambda i: compare.s1_compare_library_gemm(x.at(), ws[i].at(), y.at(), M, N, K, st)))
+        for engine, call in arms:
             us = b.time(call, n)
             row[engine + "_us"] = us
             row[engine + "_TFLOP/s"] = row["flops"] / us / 1e6
         row["tcgen05_frac_of_peak"] = row["tcgen05_TFLOP/s"] / tf
-        row["tcgen05_vs_cublaslt"] = row["cublaslt_us"] / row["tcgen05_us"]
+        if compare is not None:
+            row["tcgen05_vs_cublaslt"] = row["cublaslt_us"] / row["tcgen05_us"]
         row["peak_TFLOP/s"] = tf
         row["peak_source"] = src
         out(row)

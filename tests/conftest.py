@@ -26,3 +26,13 @@ def stream(cs1):
     from system1_omni_b200 import lib
     lib.set_device(0)
     return lib.Stream()
+
+
+@pytest.fixture
+def plan_override(cs1):
+    """Forces the tcgen05 GEMM planners (tile width, K shares, contiguous runs, single-block row
+    limit) for one test and puts the automatic choice back afterwards."""
+    def force(bn=0, splits=0, runs=2, small_rows=0):
+        assert cs1.s1_gemm_plan_override(bn, splits, runs, small_rows) == 0
+    yield force
+    cs1.s1_gemm_plan_override(0, 0, 2, 0)

@@ -321,10 +321,12 @@ def test_attn_prep_matches_reference(cs1, stream, dh):
 
 
 @pytest.mark.parametrize("dh", [256, 128])
-@pytest.mark.parametrize("t,amp", [(1, 8.0), (63, 8.0), (65, 0.5), (139, 2.0), (700, 8.0), (2048, 0.5)])
-def test_flash_attention_matches_float64_reference(cs1, stream, dh, t, amp):
-    # kernels.rs:393-474: V read in place from a 10240-wide projection row; gate < 1.6e-2
-    hq, hk = 16, 4
+@pytest.mark.parametrize("t,amp,hq,hk", [(1, 8.0, 16, 4), (63, 8.0, 16, 4), (65, 0.5, 16, 4), (139, 2.0, 16, 4),
+                                         (700, 8.0, 16, 4), (2048, 0.5, 16, 4), (16384, 2.0, 2, 1)])
+def test_flash_attention_matches_float64_reference(cs1, stream, dh, t, amp, hq, hk):
+    # kernels.rs:393-474: V read in place from a 10240-wide projection row; gate < 1.6e-2.
+    # The last case is the prompt cap: 128 key tiles per query tile, the approximated exponentials
+    # and the skipped rescales of a long softmax, on about 64 sampled rows and the last one.
     ldv, v_at = 10240, (hq * 2 + hk) * dh if dh == 256 else (hq * 2 + hk) * dh
     ldv = max(ldv, v_at + hk * dh)
     q, k, qkv, _ = attn_inputs(t, hq, hk, dh, amp, ldv)
@@ -429,6 +431,20 @@ def test_gated_delta_rule_matches_recurrent_reference(cs1, stream, t, h, hk, dec
     assert np.abs(got - chunked).max() <= 4 * 2.0 ** -8 * scale + 1e-38      # a few bf16 steps of the largest value
 
 
+def test_gated_delta_rule_at_the_longest_prompt(cs1, stream):
+    """16384 tokens (the prompt cap; 256 serial chunk steps) against the float64 token
+    recurrence, same gate as the short shapes: the error does not build up along the chain."""
+    t, h, hk = 16384, 2, 1
+    q, k, v, g, beta = gdn_inputs(t, h, hk, 0.01, 1.0)
+    got = f32(run_gdn(cs1, stream, q, k, v, g, beta, t, h, hk)).astype(np.float64)
+    assert np.all(np.isfinite(got))
+    want = O.gdn_recurrent_f64(q, k, v, g, beta, t, h, hk)
+    assert np.abs(got - want).max() <= 2e-2 * np.abs(want).max()
+    # the last chunk alone is as close as the whole
+    assert np.abs(got[-64:] - want[-64:]).max() <= 2e-2 * np.abs(want).max()
+    assert L.gdn_status() == 0
+
+
 @pytest.mark.parametrize("h,hk", [(16, 16), (32, 16), (48, 16), (24, 8)])
 def test_gated_delta_rule_model_head_counts(cs1, stream, h, hk):
     t = 200
@@ -507,13 +523,15 @@ def check_gemm(got, x, w, N):
 
 
 @pytest.mark.parametrize("M,N,K,pad", GEMM_SHAPES)
-def test_gemm_cublaslt_matches_reference(cs1, stream, M, N, K, pad):
+def test_gemm_plain_kernel_matches_reference(cs1, stream, M, N, K, pad):
+    """The CUDA-core kernel behind cs1_gemm for what TMA cannot address (ragged K, unaligned
+    views), on every shape of the list."""
     x, w, ldy = gemm_case(M, N, K, pad)
     handle = cs1.cs1_gemm_create(32 << 20)
     assert handle
     xd, wd = dev(x, stream), dev(w, stream)
     y = dev(np.full((M, ldy), 0x7FC0, np.uint16), stream)
-    L.check(cs1.s1_gemm_cublaslt(handle, xd.at(), wd.at(), y.at(), M, N, K, ldy, stream.handle), "gemm")
+    L.check(cs1.s1_gemm_plain(handle, xd.at(), wd.at(), y.at(), M, N, K, ldy, stream.handle), "gemm")
     got = host(y, (M, ldy), stream)
     check_gemm(got, x, w, N)
     assert np.all(got[:, N:] == 0x7FC0)           # the padding of a strided output is not touched
@@ -557,14 +575,12 @@ def test_gemm_k_split_is_deterministic(cs1, stream, M, N, K):
 
 @pytest.mark.parametrize("M,N,K,pad", [(1024, 2560, 9728, 0), (1024, 2560, 4096, 8), (1000, 2500, 2048, 4),
                                        (300, 5120, 2560, 0), (257, 96, 64 * 150, 0), (4096, 2560, 2048, 0)])
-@pytest.mark.parametrize("knobs", [{"S1_GEMM_RUNS": "1"}, {"S1_GEMM_RUNS": "1", "S1_GEMM_BN": "160"},
-                                   {"S1_GEMM_RUNS": "0", "S1_GEMM_SPLITS": "3"}])
-def test_gemm_shared_tile_schedules(cs1, stream, M, N, K, pad, knobs, monkeypatch):
+@pytest.mark.parametrize("knobs", [{"runs": 1}, {"runs": 1, "bn": 160}, {"runs": 0, "splits": 3}])
+def test_gemm_shared_tile_schedules(cs1, stream, M, N, K, pad, knobs, plan_override):
     """The pair kernel's two ways of sharing a tile's K range between block pairs - contiguous
     runs over all tiles' k-blocks, and equal splits - forced through the tuning knobs: same
     result as the oracle, repeatable bit for bit, padding untouched, counters back at zero."""
-    for k, v in knobs.items():
-        monkeypatch.setenv(k, v)
+    plan_override(**knobs)
     x, w, ldy = gemm_case(M, N, K, pad, seed=7)
     xd, wd = dev(x, stream), dev(w, stream)
     handle = cs1.cs1_gemm_create(32 << 20)
@@ -583,17 +599,14 @@ def test_gemm_shared_tile_schedules(cs1, stream, M, N, K, pad, knobs, monkeypatc
 @pytest.mark.parametrize("M,N,K,pad", [(64, 2560, 9728, 0), (128, 2560, 4096, 0), (1, 2560, 4096, 8), (77, 1000, 2048, 3),
                                        (128, 12352, 2560, 0), (33, 515, 1024, 0), (200, 2560, 4096, 0), (300, 1000, 2048, 3),
                                        (520, 2560, 9728, 8)])
-@pytest.mark.parametrize("knobs", [{}, {"S1_GEMM_SPLITS": "2", "S1_GEMM_BN": "256"}, {"S1_GEMM_SPLITS": "3", "S1_GEMM_BN": "64"},
-                                   {"S1_GEMM_SPLITS": "4"}, {"S1_GEMM_SPLITS": "5", "S1_GEMM_BN": "128"},
-                                   {"S1_GEMM_SPLITS": "8", "S1_GEMM_BN": "128"}])
-def test_gemm_few_rows_share_k_over_a_cluster(cs1, stream, M, N, K, pad, knobs, monkeypatch):
+@pytest.mark.parametrize("knobs", [{}, {"splits": 2, "bn": 256}, {"splits": 3, "bn": 64}, {"splits": 4},
+                                   {"splits": 5, "bn": 128}, {"splits": 8, "bn": 128}])
+def test_gemm_few_rows_share_k_over_a_cluster(cs1, stream, M, N, K, pad, knobs, plan_override):
     """The single-block kernel (up to 128 rows always, more where it is estimated faster than the
     pair kernel): the blocks of a cluster share a tile's k-blocks and add their float32 tiles
     through distributed shared memory in rank order - as planned and with cluster sizes and
     widths forced: the oracle's result, repeatable bit for bit, padding untouched."""
-    for k, v in knobs.items():
-        monkeypatch.setenv(k, v)
-    monkeypatch.setenv("S1_GEMM_SMALL_ROWS", "4096")        # several row blocks too go to the single-block kernel
+    plan_override(small_rows=4096, **knobs)       # several row blocks too go to the single-block kernel
     x, w, ldy = gemm_case(M, N, K, pad, seed=11)
     xd, wd = dev(x, stream), dev(w, stream)
     handle = cs1.cs1_gemm_create(32 << 20)
@@ -611,12 +624,12 @@ def test_gemm_few_rows_share_k_over_a_cluster(cs1, stream, M, N, K, pad, knobs, 
 
 @pytest.mark.parametrize("M,I,K,pad", [(1024, 9728, 2560, 0), (300, 1000, 512, 8), (129, 96, 64, 0), (700, 17408, 1024, 0),
                                        (257, 40, 128, 3)])
-def test_gemm_swiglu_equals_the_two_operators(cs1, stream, M, I, K, pad, monkeypatch):
+def test_gemm_swiglu_equals_the_two_operators(cs1, stream, M, I, K, pad, plan_override):
     """gate/up projection + SiLU-multiply in one kernel against cs1_gemm then cs1_silu_mul
     (model.rs:1301-1316 runs them as two operators): the same bits, padding untouched. (The kernel
     choice is pinned to the pair kernel above 128 rows: for some of these shapes the planner would
     take the single-block kernel and leave the activation to cs1_silu_mul.)"""
-    monkeypatch.setenv("S1_GEMM_SMALL_ROWS", "128")
+    plan_override(small_rows=128)
     x = O.random_bf16(M * K, 31, 1.0).reshape(M, K)
     w = O.random_bf16(2 * I * K, 32, 0.08).reshape(2 * I, K)
     xd, wd = dev(x, stream), dev(w, stream)

@@ -78,7 +78,7 @@ def test_continuation_equals_the_one_shot_pass(setup, plen):
         finally:
             prefix.close()
     finally:
-        model.set_exact_packing(False)
+        model.set_exact_packing(True)      # the default
     assert np.all(np.isfinite(packed))
     assert np.array_equal(packed, one_shot)
     assert np.array_equal(again, packed)
@@ -90,12 +90,16 @@ def test_continuation_without_exact_packing_is_within_rounding(setup):
     rng = np.random.default_rng(9)
     prefix_ids = rng.integers(0, cfg.vocab, 128).tolist()
     candidates = [rng.integers(0, cfg.vocab, n).tolist() for n in (40, 77, 12)]
-    one_shot = model.forward_batch([prefix_ids + c for c in candidates])
-    prefix = model.capture_prefix(prefix_ids)
+    model.set_exact_packing(False)
     try:
-        packed = model.forward_continue(prefix, candidates)
+        one_shot = model.forward_batch([prefix_ids + c for c in candidates])
+        prefix = model.capture_prefix(prefix_ids)
+        try:
+            packed = model.forward_continue(prefix, candidates)
+        finally:
+            prefix.close()
     finally:
-        prefix.close()
+        model.set_exact_packing(True)
     # prefill_batch.rs:57-64 allows 0.01 on scores between two ways of running the same prompt
     assert np.abs(packed - one_shot).max() <= 0.02 * max(1.0, np.abs(one_shot).max())
 

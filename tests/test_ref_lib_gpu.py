@@ -40,7 +40,37 @@ def test_symbols_and_abi_match(ref, cs1):
         assert cs1.cs1_gdn_workspace_floats(t, h) <= ref.cs1_gdn_workspace_floats(t, h)
 
 
-def test_elementwise_ops_agree_bit_for_bit(ref, cs1, stream):
+def test_silu_kernels_are_within_one_step_of_the_reference_over_many_seeds(ref, cs1, stream):
+    """The convolution and SiLU-multiply here compute SiLU with the hardware's exp2 and reciprocal
+    approximations where the reference divides exactly; the rounded bf16 results may then differ
+    in rare ties. The contract is one bf16 step at most; the observed rate of differing elements
+    over 100 seeds is printed (and must stay rare)."""
+    st = stream.handle
+    T, kd, vd = 67, 256, 512
+    ch, I = 2 * kd + vd, 1536
+    ld = ch + 64
+    differing = total = 0
+    for seed in range(100):
+        x, w = O.random_bf16(T * ld, 1000 + seed, 2.0), O.random_bf16(ch * 4, 2000 + seed, 0.7)
+        xd, wd = dev(x, stream), dev(w, stream)
+        gu = dev(O.random_bf16(T * 2 * I, 3000 + seed, 12.0), stream)
+        outs = []
+        for lib in (ref, cs1):
+            q, k, v, o = (L.DeviceBuffer(T * kd * 2), L.DeviceBuffer(T * kd * 2), L.DeviceBuffer(T * vd * 2),
+                          L.DeviceBuffer(T * I * 2))
+            L.check(lib.cs1_gdn_conv(xd.at(), ld, wd.at(), q.at(), k.at(), v.at(), T, kd, vd, st), "conv")
+            L.check(lib.cs1_silu_mul(gu.at(), 2 * I, o.at(), T, I, st), "silu")
+            outs.append(np.concatenate([host(q, T * kd, stream), host(k, T * kd, stream), host(v, T * vd, stream),
+                                        host(o, T * I, stream)]))
+        d = ulp_diff(*outs)
+        assert d.max() <= 1, (seed, int(d.max()))
+        differing += int((d != 0).sum())
+        total += d.size
+    print(f"SiLU kernels against the reference library: {differing} of {total} elements differ by one bf16 step")
+    assert differing <= 1e-3 * total
+
+
+def test_elementwise_ops_agree_with_the_reference_library(ref, cs1, stream):
     st = stream.handle
     T, kd, vd, hv = 131, 2048, 4096, 32
     ch = 2 * kd + vd
@@ -53,7 +83,7 @@ def test_elementwise_ops_agree_bit_for_bit(ref, cs1, stream):
         L.check(lib.cs1_gdn_conv(xd.at(), ld, wd.at(), q.at(), k.at(), v.at(), T, kd, vd, st), "conv")
         outs.append([host(q, T * kd, stream), host(k, T * kd, stream), host(v, T * vd, stream)])
     for a, b in zip(*outs):
-        assert np.array_equal(a, b)
+        assert ulp_diff(a, b).max() <= 1          # SiLU by approximated exp2 / reciprocal: one step at most
     # gates
     A_log, dt = bf(np.linspace(0, 2.7, hv).astype(np.float32)), bf(np.linspace(-0.2, 0.2, hv).astype(np.float32))
     Ad, dd = dev(A_log, stream), dev(dt, stream)
@@ -72,7 +102,7 @@ def test_elementwise_ops_agree_bit_for_bit(ref, cs1, stream):
         o = L.DeviceBuffer(T * I * 2)
         L.check(lib.cs1_silu_mul(gu.at(), 2 * I, o.at(), T, I, st), "silu")
         outs.append(host(o, T * I, stream))
-    assert np.array_equal(*outs)
+    assert ulp_diff(*outs).max() <= 1
     # gated norm: one warp per row there, 16 lanes here -> the sums may differ in the last bit
     xn, wn = dev(O.random_bf16(T * vd, 4, 2.0), stream), dev(bf(1 + 0.1 * f32(O.random_bf16(128, 5, 1.0))), stream)
     outs = []

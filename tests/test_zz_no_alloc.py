@@ -60,8 +60,8 @@ def test_static_scratch_limits(cs1, stream):
     assert cs1.cs1_gdn_workspace_floats(16384, 48) * 4 > STATIC_BYTES
     assert cs1.cs1_gdn_prefill_static(None, None, None, None, None, None, 16384, 48, 16, 1.0, st) == ERR_STATIC_SCRATCH
     assert b"fixed scratch" in cs1.cs1_error_string(ERR_STATIC_SCRATCH)
-    # the largest windows that fit, as documented: 1600 tokens at 32 heads, 1088 at 48, 3072 at 16
-    for t, h in [(1600, 32), (1088, 48), (3072, 16)]:
+    # the largest windows that fit, as documented: 1792 tokens at 32 heads, 1152 at 48, 3584 at 16
+    for t, h in [(1792, 32), (1152, 48), (3584, 16)]:
         assert cs1.cs1_gdn_workspace_floats(t, h) * 4 <= STATIC_BYTES
         assert cs1.cs1_gdn_workspace_floats(t + 64, h) * 4 > STATIC_BYTES
     # no tokens is a no-op; bad head grouping is an argument error, as for the other entry points
