@@ -169,39 +169,38 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
 
     grid_dep_sync();
     // ---- q and k rows are requested first of all: 16 lanes per row, 16 rows per pass; a lane owns
-    //      dims [4 sub, 4 sub + 4) and [64 + 4 sub, 64 + 4 sub + 4) ----
-    const int sub = tid & 15, rsel = tid >> 4, d0 = sub * 4;
-    uint2 raws[2][4][2];
+    //      the 8 dims [8 sub, 8 sub + 8), one 16-byte piece of the row ----
+    const int sub = tid & 15, rsel = tid >> 4;
+    uint4 raws[2][4];
 #pragma unroll
     for (int which = 0; which < 2; which++) {
         const bf16* src0 = which == 0 ? k : q;
 #pragma unroll
         for (int pass = 0; pass < 4; pass++) {
             const int r = pass * 16 + rsel;
-            raws[which][pass][0] = raws[which][pass][1] = make_uint2(0, 0);
-            if (r0 + r < T) {
-                const bf16* src = src0 + ((size_t)(r0 + r) * HK + hk) * D + d0;
-                raws[which][pass][0] = *reinterpret_cast<const uint2*>(src);
-                raws[which][pass][1] = *reinterpret_cast<const uint2*>(src + 64);
-            }
+            raws[which][pass] = make_uint4(0, 0, 0, 0);
+            if (r0 + r < T) raws[which][pass] = ld16(src0 + ((size_t)(r0 + r) * HK + hk) * D + sub * 8);
         }
     }
-    // ---- log-decays: a sequential float32 prefix sum, rows past the end have g = beta = 0 ----
+    // ---- log-decays: float32 prefix sums over the chunk (a shuffle scan in each of the two warps,
+    //      the second adding the first one's total), rows past the end have g = beta = 0 ----
     if (tid < C) {
         const int row = r0 + tid;
-        cum[tid] = row < T ? g[(size_t)row * H + h] : 0.f;
+        float x = row < T ? g[(size_t)row * H + h] : 0.f;
         bt[tid] = row < T ? f32(beta[(size_t)row * H + h]) : 0.f;
+#pragma unroll
+        for (int o2 = 1; o2 < 32; o2 <<= 1) {
+            const float y = __shfl_up_sync(0xffffffffu, x, o2);
+            if (lane >= o2) x += y;
+        }
+        cum[tid] = x;
     }
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t t_lanes = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    if (tid == 0) {
-        float run = 0.f;
-#pragma unroll 8
-        for (int i = 0; i < C; i++) cum[i] = (run += cum[i]);
-    }
+    if (tid >= 32 && tid < C) cum[tid] += cum[31];
     __syncthreads();
     if (tid < C) {
         const float last = cum[C - 1];
@@ -216,18 +215,11 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
 #pragma unroll
     for (int which = 0; which < 2; which++) {  // 0: k, 1: q
         const bool is_k = which == 0;
-        const uint2 (&raw)[4][2] = raws[which];
 #pragma unroll
         for (int pass = 0; pass < 4; pass++) {
             const int i = pass * 16 + rsel, r = is_k ? i : C + i;
             float x[8];
-#pragma unroll
-            for (int half = 0; half < 2; half++) {
-                x[4 * half + 0] = __uint_as_float(raw[pass][half].x << 16);
-                x[4 * half + 1] = __uint_as_float(raw[pass][half].x & 0xffff0000u);
-                x[4 * half + 2] = __uint_as_float(raw[pass][half].y << 16);
-                x[4 * half + 3] = __uint_as_float(raw[pass][half].y & 0xffff0000u);
-            }
+            unpack8(raws[which][pass], x);
             float ss = 0.f;
 #pragma unroll
             for (int e = 0; e < 8; e++) ss += x[e] * x[e];
@@ -236,34 +228,29 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
             if (!is_k) inv *= scale;
             const float mult = is_k ? erem[i] : ecum[i];
             const float ec = ecum[i];
+            float nrm[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) nrm[e] = x[e] * inv;
+            // float columns [8 sub, 8 sub + 8): box sub / 4, 16-byte pieces 2 (sub % 4) and the next
+            unsigned char* tf = smem + T_KQ + (sub >> 2) * KQ_BOX;
+            *reinterpret_cast<float4*>(tf + swz(r, 2 * (sub & 3))) =
+                make_float4(__uint_as_float(to_tf32(nrm[0])), __uint_as_float(to_tf32(nrm[1])), __uint_as_float(to_tf32(nrm[2])),
+                            __uint_as_float(to_tf32(nrm[3])));
+            *reinterpret_cast<float4*>(tf + swz(r, 2 * (sub & 3) + 1)) =
+                make_float4(__uint_as_float(to_tf32(nrm[4])), __uint_as_float(to_tf32(nrm[5])), __uint_as_float(to_tf32(nrm[6])),
+                            __uint_as_float(to_tf32(nrm[7])));
             // kd: token row i of the two [64 tokens x 64 dims] boxes; qd: row 64 + i of the two
-            // [128 rows x 64 dims] boxes it shares with w
-            unsigned char* dout = is_k ? ws.kd + tile * KD_BYTES + swz(i, sub >> 1) + (sub & 1) * 8
-                                       : ws.wq + tile * WQ_BYTES + swz(C + i, sub >> 1) + (sub & 1) * 8;
-            const int dbox = is_k ? KD_BYTES / 2 : WQ_BYTES / 2;
+            // [128 rows x 64 dims] boxes it shares with w. bf16 columns [8 sub, +8): box sub / 8, piece sub % 8
+            float scaled[8];
 #pragma unroll
-            for (int half = 0; half < 2; half++) {
-                float nrm[4];
+            for (int e = 0; e < 8; e++) scaled[e] = nrm[e] * mult;
+            unsigned char* dout = is_k ? ws.kd + tile * KD_BYTES + (sub >> 3) * (KD_BYTES / 2) + swz(i, sub & 7)
+                                       : ws.wq + tile * WQ_BYTES + (sub >> 3) * (WQ_BYTES / 2) + swz(C + i, sub & 7);
+            st16(dout, pack8(scaled));
+            if (is_k) {  // k exp(cum), the MN-major operand half of [v | k exp(cum)]
 #pragma unroll
-                for (int e = 0; e < 4; e++) nrm[e] = x[4 * half + e] * inv;
-                float4 t;
-                t.x = __uint_as_float(to_tf32(nrm[0]));
-                t.y = __uint_as_float(to_tf32(nrm[1]));
-                t.z = __uint_as_float(to_tf32(nrm[2]));
-                t.w = __uint_as_float(to_tf32(nrm[3]));
-                // column 64 half + 4 sub of a float row: box (2 half + sub / 8), 16-byte piece sub % 8
-                *reinterpret_cast<float4*>(smem + T_KQ + (2 * half + (sub >> 3)) * KQ_BOX + swz(r, sub & 7)) = t;
-                uint2 o;
-                o.x = pack2(nrm[0] * mult, nrm[1] * mult);
-                o.y = pack2(nrm[2] * mult, nrm[3] * mult);
-                *reinterpret_cast<uint2*>(dout + half * dbox) = o;
-                if (is_k) {
-                    // k exp(cum), bf16: box `half` of 64 columns, piece (4 sub) / 8, 8 bytes at (sub & 1) * 8
-                    uint2 e2;
-                    e2.x = pack2(nrm[0] * ec, nrm[1] * ec);
-                    e2.y = pack2(nrm[2] * ec, nrm[3] * ec);
-                    *reinterpret_cast<uint2*>(smem + T_KE + half * U_BYTES + swz(i, sub >> 1) + (sub & 1) * 8) = e2;
-                }
+                for (int e = 0; e < 8; e++) scaled[e] = nrm[e] * ec;
+                st16(smem + T_KE + (sub >> 3) * U_BYTES + swz(i, sub & 7), pack8(scaled));
             }
         }
     }
@@ -377,35 +364,53 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
             *reinterpret_cast<float2*>(a21 + i * LDA + j0) = make_float2(y0, y1);
             __syncthreads();
         }
-        {   // 32 -> 64: 32 x 32 outputs as 2 x 2 register tiles on all 256 threads
-            const int ib = (t >> 4) * 2, j0 = (t & 15) * 2;
+        {   // 32 -> 64: 32 x 32 outputs as 4 x 2 register tiles on 128 threads, four steps of the sum
+            // per pass so that the left factor's rows come in as float4
+            const int ib = (t >> 4) * 4, j0 = (t & 15) * 2;
             float* a21 = A + 32 * LDA;
             const float* t22 = a21 + 32;
-            float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-#pragma unroll 8
-            for (int m = 0; m < 32; m++) {
-                const float2 tt = *reinterpret_cast<const float2*>(A + m * LDA + j0);
+            float acc[4][2];
+            if (t < 128) {
 #pragma unroll
-                for (int rr = 0; rr < 2; rr++) {
-                    const float a = a21[(ib + rr) * LDA + m];
-                    acc[rr][0] += a * tt.x, acc[rr][1] += a * tt.y;
+                for (int rr = 0; rr < 4; rr++) acc[rr][0] = acc[rr][1] = 0.f;
+#pragma unroll 2
+                for (int m = 0; m < 32; m += 4) {
+                    float2 tt[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) tt[e] = *reinterpret_cast<const float2*>(A + (m + e) * LDA + j0);
+#pragma unroll
+                    for (int rr = 0; rr < 4; rr++) {
+                        const float4 a = *reinterpret_cast<const float4*>(a21 + (ib + rr) * LDA + m);
+                        acc[rr][0] += a.x * tt[0].x, acc[rr][1] += a.x * tt[0].y;
+                        acc[rr][0] += a.y * tt[1].x, acc[rr][1] += a.y * tt[1].y;
+                        acc[rr][0] += a.z * tt[2].x, acc[rr][1] += a.z * tt[2].y;
+                        acc[rr][0] += a.w * tt[3].x, acc[rr][1] += a.w * tt[3].y;
+                    }
                 }
-            }
 #pragma unroll
-            for (int rr = 0; rr < 2; rr++) *reinterpret_cast<float2*>(X + (ib + rr) * LDX + j0) = make_float2(acc[rr][0], acc[rr][1]);
+                for (int rr = 0; rr < 4; rr++) *reinterpret_cast<float2*>(X + (ib + rr) * LDX + j0) = make_float2(acc[rr][0], acc[rr][1]);
+            }
             __syncthreads();
-            acc[0][0] = acc[0][1] = acc[1][0] = acc[1][1] = 0.f;
-#pragma unroll 8
-            for (int m = 0; m < 32; m++) {
-                const float2 tt = *reinterpret_cast<const float2*>(X + m * LDX + j0);
+            if (t < 128) {
 #pragma unroll
-                for (int rr = 0; rr < 2; rr++) {
-                    const float a = t22[(ib + rr) * LDA + m];
-                    acc[rr][0] -= a * tt.x, acc[rr][1] -= a * tt.y;
+                for (int rr = 0; rr < 4; rr++) acc[rr][0] = acc[rr][1] = 0.f;
+#pragma unroll 2
+                for (int m = 0; m < 32; m += 4) {
+                    float2 tt[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) tt[e] = *reinterpret_cast<const float2*>(X + (m + e) * LDX + j0);
+#pragma unroll
+                    for (int rr = 0; rr < 4; rr++) {
+                        const float4 a = *reinterpret_cast<const float4*>(t22 + (ib + rr) * LDA + m);
+                        acc[rr][0] -= a.x * tt[0].x, acc[rr][1] -= a.x * tt[0].y;
+                        acc[rr][0] -= a.y * tt[1].x, acc[rr][1] -= a.y * tt[1].y;
+                        acc[rr][0] -= a.z * tt[2].x, acc[rr][1] -= a.z * tt[2].y;
+                        acc[rr][0] -= a.w * tt[3].x, acc[rr][1] -= a.w * tt[3].y;
+                    }
                 }
-            }
 #pragma unroll
-            for (int rr = 0; rr < 2; rr++) *reinterpret_cast<float2*>(a21 + (ib + rr) * LDA + j0) = make_float2(acc[rr][0], acc[rr][1]);
+                for (int rr = 0; rr < 4; rr++) *reinterpret_cast<float2*>(a21 + (ib + rr) * LDA + j0) = make_float2(acc[rr][0], acc[rr][1]);
+            }
             __syncthreads();
         }
     }
@@ -477,7 +482,7 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
 // gdn_scan_tc5: the serial half. One block per (value head, 64 value columns); per chunk
 //   D [128 x 64]  = [w ; qd] Sb            one M = 128 product: rows 0-63 w Sb, rows 64-127 qd Sb
 //   v_new         = bf16(u - D[0:64])      by threads, straight into the next products' operand
-//   D            += [0 ; P] v_new          rows 64-127 become o = qd Sb + P v_new
+//   D            += [. ; P] v_new          rows 64-127 become o = qd Sb + P v_new (rows 0-63 are dead by then)
 //   S             = decay S + kd^T v_new   accumulated onto the float32 state in tensor memory,
 //                                          which its threads scaled by decay beforehand
 // Sb is the bf16 copy of the chunk-entry state, written by the state's threads into the swizzled
@@ -486,23 +491,29 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
 // lanes of its quarter): warps 0-7 own the state (a row of S and half of its columns per
 // thread), warps 8-9 and 12-13 make v_new, warps 10-11 and 14-15 read o out of the accumulator
 // (two of them, used in turn, so that a chunk's output is stored while the next chunk's first
-// product runs) and store it, warp 16 feeds the copy engine (two stages of tiles) and issues
+// product runs) and store it, warp 16 feeds the copy engine (three stages of tiles) and issues
 // the MMAs. The scaling of S is off the chain: the first product needs only Sb. Every wait is
 // on an mbarrier and bounded.
 // ---------------------------------------------------------------------------------------
 constexpr int SCAN_THREADS = 17 * 32;
+constexpr int STAGES = 3;                             // a chunk's tiles are requested two chunks ahead
 constexpr int S_WQ = 0;                               // per stage: [w ; qd], two boxes of 128 rows
 constexpr int S_KD = S_WQ + WQ_BYTES;                 // kd, two boxes of 64 token rows
-constexpr int S_PZ = S_KD + KD_BYTES;                 // one box of 128 rows: 64 zero rows, then P
-constexpr int S_U = S_PZ + 2 * P_BYTES;               // this block's box of u
+constexpr int S_P = S_KD + KD_BYTES;                  // P, one box of 64 rows
+// The product [.. ; P] v_new has M = 128: its A operand is the box of 128 rows that ends with P,
+// i.e. it begins with the second box of kd. What those 64 rows contribute lands in rows 0-63 of
+// D, which nobody reads after v_new has been taken from them.
+constexpr int S_PA = S_P - P_BYTES;
+constexpr int S_U = S_P + P_BYTES;                    // this block's box of u
 constexpr int S_STAGE = S_U + U_BYTES;
-constexpr int S_SB = 2 * S_STAGE;                     // bf16 state, one box of [128 k rows x 64 columns]
+constexpr int S_SB = STAGES * S_STAGE;                // bf16 state, one box of [128 k rows x 64 columns]
 constexpr int S_VN = S_SB + D * 128;                  // v_new, one box of [64 tokens x 64 columns]
 constexpr int S_BAR = S_VN + C * 128;                 // barriers, the tensor-memory address, a flag
 constexpr int SCAN_SMEM = S_BAR + 128 + 1024;         // + slack to align the base to 1024
 constexpr uint32_t STAGE_TX = WQ_BYTES + KD_BYTES + P_BYTES + U_BYTES;
 constexpr int SCAN_TMEM_COLS = 256;                   // S in columns [0, 64), the two D in [64, 128) and [128, 192)
-static_assert(S_STAGE % 1024 == 0 && S_KD % 1024 == 0 && S_PZ % 1024 == 0 && S_U % 1024 == 0, "boxes are 1024-byte aligned");
+static_assert(S_STAGE % 1024 == 0 && S_KD % 1024 == 0 && S_PA % 1024 == 0 && S_U % 1024 == 0, "boxes are 1024-byte aligned");
+static_assert(SCAN_SMEM <= 227 * 1024, "the stages fit an SM");
 
 __global__ void __launch_bounds__(SCAN_THREADS, 1)
     gdn_scan_tc5(Work ws, bf16* __restrict__ o, int T, int H, int NC, const float* __restrict__ s_in,
@@ -511,14 +522,15 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1)
     grid_dep_trigger();
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + S_BAR);  // [2] a stage's tiles have landed
-    uint64_t* sb_ready = full + 2;   // 256 arrivals: Sb written
-    uint64_t* s_scaled = full + 3;   // 256 arrivals: decay S is back in tensor memory
-    uint64_t* d1_done = full + 4;    // the first product is complete
-    uint64_t* vn_ready = full + 5;   // 128 arrivals: v_new written
-    uint64_t* d2_done = full + 6;    // [2], by chunk parity: the second and third products are complete
-    uint64_t* d_free = full + 8;     // [2] 128 arrivals: that D has been read out
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(full + 10);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + S_BAR);  // [STAGES] a stage's tiles have landed
+    uint64_t* sb_ready = full + 3;   // 256 arrivals: Sb written
+    uint64_t* s_scaled = full + 4;   // 256 arrivals: decay S is back in tensor memory
+    uint64_t* d1_done = full + 5;    // the first product is complete
+    uint64_t* vn_ready = full + 6;   // 128 arrivals: v_new written
+    uint64_t* s_done = full + 7;     // the state's product (the third) is complete
+    uint64_t* d2_done = full + 8;    // [2], by chunk parity: every product of the chunk is complete
+    uint64_t* d_free = full + 10;    // [2] 128 arrivals: that D has been read out
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(full + 12);
     volatile int* gave_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int h = blockIdx.x, slice = blockIdx.y, v0 = slice * VS;
@@ -527,12 +539,12 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1)
     const size_t tile0 = (size_t)h * NC;
 
     if (tid == 0) {
-        mbar_init(&full[0], 1);
-        mbar_init(&full[1], 1);
+        for (int i = 0; i < STAGES; i++) mbar_init(&full[i], 1);
         mbar_init(sb_ready, 256);
         mbar_init(s_scaled, 256);
         mbar_init(d1_done, 1);
         mbar_init(vn_ready, 128);
+        mbar_init(s_done, 1);
         mbar_init(&d2_done[0], 1);
         mbar_init(&d2_done[1], 1);
         mbar_init(&d_free[0], 128);
@@ -544,11 +556,6 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1)
         tmem_alloc(tmem_slot, SCAN_TMEM_COLS);
         tmem_relinquish();
     }
-    // the upper half of each stage's P box stays zero for the whole kernel
-    for (int i = tid; i < 2 * (P_BYTES / 16); i += SCAN_THREADS)
-        *reinterpret_cast<uint4*>(smem + (i / (P_BYTES / 16)) * S_STAGE + S_PZ + (i % (P_BYTES / 16)) * 16) =
-            make_uint4(0, 0, 0, 0);
-    fence_proxy_async();
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
@@ -600,7 +607,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1)
             fence_before_sync();
             mbar_arrive(s_scaled);
             if (c + 1 < NC) decay = ws.decay[tile0 + c + 1];
-            if (!mbar_wait(&d2_done[c & 1], (c >> 1) & 1, gave_up)) {
+            if (!mbar_wait(s_done, c & 1, gave_up)) {
                 fail(44);
                 ok = false;
                 break;
@@ -620,6 +627,15 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1)
         // ---- v_new: thread (i, hh) owns v_new[i][32 hh .. + 32) of the chunk ----
         const int hh = (warp - 8) >> 2, i = quarter * 32 + lane;
         for (int c = 0; c < NC; c++) {
+            // this thread's 32 values of u wait in registers for the product they are subtracted from
+            if (!mbar_wait(&full[c % STAGES], (c / STAGES) & 1, gave_up)) {
+                fail(53);
+                break;
+            }
+            const unsigned char* u_box = smem + (c % STAGES) * S_STAGE + S_U;
+            uint4 u_pieces[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) u_pieces[j] = *reinterpret_cast<const uint4*>(u_box + swz(i, hh * 4 + j));
             if (!mbar_wait(d1_done, c & 1, gave_up)) {
                 fail(45);
                 break;
@@ -628,12 +644,10 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1)
             uint32_t acc[32];
             tmem_ld_32x32(t_lanes + VS + (c & 1) * VS + hh * 32, acc);
             tmem_ld_wait();
-            const unsigned char* u_box = smem + (c & 1) * S_STAGE + S_U;
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                const uint4 u8 = *reinterpret_cast<const uint4*>(u_box + swz(i, hh * 4 + j));
                 float uf[8];
-                unpack8(u8, uf);
+                unpack8(u_pieces[j], uf);
                 uint4 piece;
                 piece.x = pack2(uf[0] - __uint_as_float(acc[8 * j + 0]), uf[1] - __uint_as_float(acc[8 * j + 1]));
                 piece.y = pack2(uf[2] - __uint_as_float(acc[8 * j + 2]), uf[3] - __uint_as_float(acc[8 * j + 3]));
@@ -682,23 +696,38 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1)
         const unsigned char* u_g = ws.u + tile0 * (2 * U_BYTES) + slice * U_BYTES;
         auto load = [&](int c) {
             if (!issuer) return;
-            unsigned char* st = smem + (c & 1) * S_STAGE;
-            uint64_t* bar = &full[c & 1];
+            unsigned char* st = smem + (c % STAGES) * S_STAGE;
+            uint64_t* bar = &full[c % STAGES];
             mbar_expect_tx(bar, STAGE_TX);
             bulk_load(st + S_WQ, wq_g + (size_t)c * WQ_BYTES, WQ_BYTES, bar);
             bulk_load(st + S_KD, kd_g + (size_t)c * KD_BYTES, KD_BYTES, bar);
-            bulk_load(st + S_PZ + P_BYTES, p_g + (size_t)c * P_BYTES, P_BYTES, bar);
+            bulk_load(st + S_P, p_g + (size_t)c * P_BYTES, P_BYTES, bar);
             bulk_load(st + S_U, u_g + (size_t)c * (2 * U_BYTES), U_BYTES, bar);
         };
-        load(0);
-        if (NC > 1) load(1);
+        for (int c = 0; c < STAGES - 1 && c < NC; c++) load(c);
+        // The tiles of chunk c + 2 are requested during chunk c, into the stage chunk c - 1 has left
+        // (its last product, the one that reads P, must have completed). When in the chunk matters: a
+        // proxy fence issued by a thread while a bulk copy is still writing this block's shared
+        // memory was measured to wait for the copy (500 cycles and more), and both the state's and
+        // the v_new threads fence once per chunk - behind the first product's issue the copy has the
+        // longest stretch without one of those fences to land in (10 % faster than behind the
+        // v_new threads' fence).
+        auto next_tiles = [&](int c) {
+            if (c + STAGES - 1 >= NC) return true;
+            if (c >= 1 && !mbar_wait(&d2_done[(c - 1) & 1], ((c - 1) >> 1) & 1, gave_up)) {
+                fail(50);
+                return false;
+            }
+            load(c + STAGES - 1);
+            return true;
+        };
         constexpr uint32_t idesc_b = instr_desc_b_mn(1, 128, VS);                // A K-major, B MN-major
         constexpr uint32_t idesc_ab = instr_desc_b_mn(1, 128, VS) | (1u << 15);  // both MN-major
         const uint32_t sb = smem_addr(smem + S_SB), vn = smem_addr(smem + S_VN);
         for (int c = 0; c < NC; c++) {
-            const uint32_t st = smem_addr(smem + (c & 1) * S_STAGE);
+            const uint32_t st = smem_addr(smem + (c % STAGES) * S_STAGE);
             const uint32_t d = tmem_base + VS + (c & 1) * VS;
-            if (!mbar_wait(&full[c & 1], (c >> 1) & 1, gave_up)) {
+            if (!mbar_wait(&full[c % STAGES], (c / STAGES) & 1, gave_up)) {
                 fail(47);
                 break;
             }
@@ -719,6 +748,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1)
                 mma_commit(d1_done);
             }
             __syncwarp();
+            if (!next_tiles(c)) break;
             if (!mbar_wait(vn_ready, c & 1, gave_up)) {
                 fail(49);
                 break;
@@ -730,20 +760,16 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1)
             fence_after_sync();
             if (issuer) {
 #pragma unroll
-                for (int ks = 0; ks < C / 16; ks++) {
-                    const uint64_t b = smem_desc_mn_sw128(vn + ks * 2048, C * 128, 1024);
-                    mma_bf16_ss(tmem_base, smem_desc_mn_sw128(st + S_KD + ks * 2048, KD_BYTES / 2, 1024), b, idesc_ab, 1u);
-                    mma_bf16_ss(d, smem_desc_sw128(st + S_PZ + ks * 32), b, idesc_b, 1u);
-                }
+                for (int ks = 0; ks < C / 16; ks++)  // the state first: the next chunk waits for it alone
+                    mma_bf16_ss(tmem_base, smem_desc_mn_sw128(st + S_KD + ks * 2048, KD_BYTES / 2, 1024),
+                                smem_desc_mn_sw128(vn + ks * 2048, C * 128, 1024), idesc_ab, 1u);
+                mma_commit(s_done);
+#pragma unroll
+                for (int ks = 0; ks < C / 16; ks++)
+                    mma_bf16_ss(d, smem_desc_sw128(st + S_PA + ks * 32), smem_desc_mn_sw128(vn + ks * 2048, C * 128, 1024), idesc_b, 1u);
                 mma_commit(&d2_done[c & 1]);
             }
             __syncwarp();
-            // this stage is free once those products have read it
-            if (!mbar_wait(&d2_done[c & 1], (c >> 1) & 1, gave_up)) {
-                fail(50);
-                break;
-            }
-            if (c + 2 < NC) load(c + 2);
         }
         __syncwarp();
     }
