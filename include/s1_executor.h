@@ -125,6 +125,9 @@ int s1_model_create(const S1Config* cfg, int device, void** model);
 void s1_model_destroy(void* model);
 int s1_model_set_tensor(void* model, const char* name, const void* host_bf16, size_t bytes);
 int s1_model_tensor(void* model, const char* name, void** device_ptr, size_t* bytes);
+/* The shape a checkpoint must give that tensor (Weights::get, model.rs:306-320): rank and up to
+ * 8 extents, each nullable. */
+int s1_model_tensor_shape(void* model, const char* name, int* rank, uint64_t* shape8);
 /* Random weights of the shape, generated on the device: matrices and zero-centred norm
  * weights N(0, std), the gated norm weight 1 + N(0, std), A_log U(0, ln 16), dt_bias N(0, 0.1). */
 int s1_model_init_random(void* model, uint64_t seed, float std);
@@ -231,11 +234,22 @@ enum {
 int s1_checkpoint_inspect(const char* dir, char* prefix_out, size_t prefix_cap, int* n_tensors, int index,
                           char* name_out, size_t name_cap, char* dtype_out, size_t dtype_cap, int* rank,
                           uint64_t* shape8, uint64_t* bytes);
-/* Upload every tensor of the decoder from the checkpoint into the model's arena (tensors the
- * decoder has no place for - lm_head, vision tower, MTP - are skipped). All must be bfloat16 and
- * of the planned byte size; all planned tensors must be present. offender (nullable) receives the
- * name of the tensor an error is about. */
+/* Upload every tensor of the decoder from the checkpoint into the model's arena (tensors under
+ * the prefix that the decoder has no place for - lm_head, MTP - are skipped). Every tensor under
+ * the prefix must be bfloat16 (model.rs:291-295), every tensor of the decoder must have exactly
+ * the planned shape (model.rs:306-320: a transposed matrix has the same bytes), and all planned
+ * tensors must be present. offender (nullable) receives the name of the tensor an error is about. */
 int s1_model_load_checkpoint(void* model, const char* dir, char* offender, size_t offender_cap);
+/* open_jev_export.json of a merged Open-Jev export (recipe/open_jev/export_merged.py:82-90,
+ * engine.rs:21-46, executor.rs:21-54), host only: format tag "open-jev-text-merged/1",
+ * temperature (finite, > 0), max_length (1..=16384), chat_prefix / chat_suffix (strings) and
+ * the trained scalar head: `hidden` finite weights into head_weight and a finite bias, rounded
+ * from the file's float64 to float32. With s1_head_logits (n_classes = 1) and s1_decide they
+ * give a request's scores and decision as the worker computes them. Every out pointer but
+ * head_weight is nullable. S1_ERR_CHECKPOINT_IO / _FORMAT, or S1_ERR_EXPORT_FIELD for a missing
+ * or invalid field. */
+int s1_export_read(const char* dir, int hidden, float* head_weight, float* head_bias, double* temperature,
+                   int* max_length, char* model_id, size_t model_id_cap);
 /* Number of planned tensors not yet given a value; the first one's name in name_out (nullable). */
 int s1_model_unfilled(void* model, char* name_out, size_t cap);
 
@@ -273,6 +287,7 @@ int s1_assign_requests(const int* lengths, int n, int n_ranks, double a, double 
 #define S1_ERR_CHECKPOINT_FORMAT 3005  /* not a safetensors file / index */
 #define S1_ERR_CHECKPOINT_DTYPE 3006   /* a language-model tensor is not bfloat16 (model.rs:291-295) */
 #define S1_ERR_CHECKPOINT_MISSING 3007 /* no embed_tokens.weight, or a tensor of the decoder is absent */
+#define S1_ERR_EXPORT_FIELD 3008       /* open_jev_export.json lacks a field or holds an invalid value */
 
 #ifdef __cplusplus
 }

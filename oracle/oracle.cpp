@@ -20,7 +20,7 @@
 // tests/test_oracle_kat.py replays against this file, and (2) tolerance contracts between
 // its kernels and the float64 oracles restated here; on a GPU box the reference's own CUDA
 // library (built from its sources into oracle/_ref/) is run beside this oracle on the same
-// seeded inputs (tests/test_ref_lib.py).
+// seeded inputs (tests/test_ref_lib_gpu.py).
 //
 // bf16 values travel as uint16_t bit patterns.
 #include <math.h>

@@ -5,8 +5,11 @@
 // every one of them required to be bfloat16; uploaded into the model's arena by name.
 // The file format: 8 bytes little-endian header length, a JSON object
 // {name: {"dtype", "shape", "data_offsets": [begin, end]}, "__metadata__": {...}}, then the data.
+#include <errno.h>
 #include <fcntl.h>
+#include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
@@ -27,13 +30,27 @@ struct Json {
     enum Kind { Null, Bool, Number, String, Array, Object } kind = Null;
     bool b = false;
     double num = 0;
-    std::string str;
+    std::string str;  // a string's text, or a number's digits as written
+
     std::vector<Json> items;
     std::vector<std::pair<std::string, Json>> fields;
     const Json* get(const char* key) const {
         for (const auto& f : fields)
             if (f.first == key) return &f.second;
         return nullptr;
+    }
+    // A non-negative integer written without fraction or exponent (offsets and extents: exact
+    // beyond 2^53, where a double is not).
+    bool as_u64(uint64_t* out) const {
+        if (kind != Number || str.empty()) return false;
+        for (char ch : str)
+            if (ch < '0' || ch > '9') return false;
+        errno = 0;
+        char* stop = nullptr;
+        const unsigned long long v = strtoull(str.c_str(), &stop, 10);
+        if (errno != 0 || *stop != 0) return false;
+        *out = v;
+        return true;
     }
 };
 
@@ -68,8 +85,28 @@ struct Parser {
                     case 'r': out += '\r'; break;
                     case 'b': out += '\b'; break;
                     case 'f': out += '\f'; break;
-                    case 'u': {  // keep the escape as text: tensor and file names are ASCII
-                        out += "\\u";
+                    case 'u': {  // four hex digits; code points up to 0x7ff become UTF-8, others stay escaped text
+                        unsigned code = 0;
+                        bool hex = end - p > 4;
+                        for (int i = 1; hex && i <= 4; i++) {
+                            const char ch = p[i];
+                            const int d = ch >= '0' && ch <= '9' ? ch - '0' : ch >= 'a' && ch <= 'f' ? ch - 'a' + 10 : ch >= 'A' && ch <= 'F' ? ch - 'A' + 10 : -1;
+                            if (d < 0) hex = false;
+                            code = code * 16 + (unsigned)(d < 0 ? 0 : d);
+                        }
+                        if (!hex) {
+                            ok = false;
+                            return out;
+                        }
+                        if (code < 0x80) {
+                            out += (char)code;
+                        } else if (code < 0x800) {
+                            out += (char)(0xc0 | (code >> 6));
+                            out += (char)(0x80 | (code & 0x3f));
+                        } else {
+                            out.append(p - 1, 6);
+                        }
+                        p += 4;
                         break;
                     }
                     default: out += *p;
@@ -79,9 +116,19 @@ struct Parser {
                 out += *p++;
             }
         }
-        if (p >= end) ok = false;
+        if (p >= end) {
+            ok = false;
+            return out;
+        }
         p++;
         return out;
+    }
+    // A literal, whole: a header cut off inside one is malformed.
+    bool literal(const char* word) {
+        const size_t n = strlen(word);
+        if ((size_t)(end - p) < n || strncmp(p, word, n) != 0) return false;
+        p += n;
+        return true;
     }
     Json value() {
         Json v;
@@ -117,18 +164,18 @@ struct Parser {
         } else if (*p == '"') {
             v.kind = Json::String;
             v.str = string();
-        } else if (!strncmp(p, "true", std::min<size_t>(4, end - p))) {
-            v.kind = Json::Bool, v.b = true, p += 4;
-        } else if (!strncmp(p, "false", std::min<size_t>(5, end - p))) {
-            v.kind = Json::Bool, p += 5;
-        } else if (!strncmp(p, "null", std::min<size_t>(4, end - p))) {
-            p += 4;
+        } else if (literal("true")) {
+            v.kind = Json::Bool, v.b = true;
+        } else if (literal("false")) {
+            v.kind = Json::Bool;
+        } else if (literal("null")) {
         } else {
             char* stop = nullptr;
             std::string text(p, std::min<size_t>(64, end - p));
             v.kind = Json::Number;
             v.num = strtod(text.c_str(), &stop);
             if (stop == text.c_str()) ok = false;
+            v.str.assign(text.c_str(), stop - text.c_str());
             p += stop - text.c_str();
         }
         depth--;
@@ -180,6 +227,7 @@ int open_file(const std::string& path, File* f) {
     if (!parse_json(reinterpret_cast<const char*>(base + 8), header, &root) || root.kind != Json::Object)
         return S1_ERR_CHECKPOINT_FORMAT;
     const uint64_t data_bytes = f->size - 8 - header;
+    std::vector<std::pair<uint64_t, uint64_t>> spans;
     for (const auto& field : root.fields) {
         if (field.first == "__metadata__") continue;
         const Json *dtype = field.second.get("dtype"), *shape = field.second.get("shape"),
@@ -189,13 +237,23 @@ int open_file(const std::string& path, File* f) {
             return S1_ERR_CHECKPOINT_FORMAT;
         View v;
         v.dtype = dtype->str;
-        for (const Json& d : shape->items) v.shape.push_back((uint64_t)d.num);
-        const uint64_t begin = (uint64_t)offs->items[0].num, stop = (uint64_t)offs->items[1].num;
+        for (const Json& d : shape->items) {
+            uint64_t extent = 0;
+            if (!d.as_u64(&extent)) return S1_ERR_CHECKPOINT_FORMAT;
+            v.shape.push_back(extent);
+        }
+        uint64_t begin = 0, stop = 0;
+        if (!offs->items[0].as_u64(&begin) || !offs->items[1].as_u64(&stop)) return S1_ERR_CHECKPOINT_FORMAT;
         if (begin > stop || stop > data_bytes) return S1_ERR_CHECKPOINT_FORMAT;
         v.data = base + 8 + header + begin;
         v.bytes = stop - begin;
         f->tensors[field.first] = v;
+        if (stop > begin) spans.emplace_back(begin, stop);
     }
+    // two tensors may not share bytes
+    std::sort(spans.begin(), spans.end());
+    for (size_t i = 1; i < spans.size(); i++)
+        if (spans[i].first < spans[i - 1].second) return S1_ERR_CHECKPOINT_FORMAT;
     return 0;
 }
 
@@ -295,7 +353,7 @@ int s1_checkpoint_inspect(const char* dir, char* prefix_out, size_t prefix_cap, 
 
 // Model::load's weight half (model.rs:239-315, 622-705): every language-model tensor of the
 // checkpoint that the model has a place for is checked (bfloat16, byte size of the planned
-// tensor) and uploaded; tensors the decoder does not use (lm_head, vision tower, MTP) are
+// tensor's shape) and uploaded; tensors the decoder does not use (lm_head, MTP) are
 // skipped. Fails with S1_ERR_CHECKPOINT_DTYPE / S1_ERR_TENSOR_SIZE at the first offender
 // and S1_ERR_CHECKPOINT_MISSING when a planned tensor is absent; `offender` (nullable) receives
 // the tensor's name.
@@ -306,11 +364,25 @@ int s1_model_load_checkpoint(void* model, const char* dir, char* offender, size_
     int rc = open_checkpoint(dir, &ck);
     if (rc != 0) return rc;
     for (const auto& t : ck.ours) {
-        size_t planned = 0;
-        if (s1_model_tensor(model, t.first.c_str(), nullptr, &planned) != 0) continue;  // not part of the decoder
+        // every tensor under the prefix must be bfloat16, used or not (model.rs:291-295)
         if (t.second->dtype != "BF16") {
             copy_name(t.first, offender, offender_cap);
             return S1_ERR_CHECKPOINT_DTYPE;
+        }
+        int rank = 0;
+        uint64_t want[8] = {};
+        if (s1_model_tensor_shape(model, t.first.c_str(), &rank, want) != 0) continue;  // not part of the decoder
+        // the shape the decoder expects, not merely its byte count (model.rs:306-320): a transposed
+        // matrix has the same bytes
+        uint64_t elems = 1;
+        bool same = (size_t)rank == t.second->shape.size();
+        for (int i = 0; same && i < rank; i++) {
+            same = want[i] == t.second->shape[i];
+            elems *= want[i];
+        }
+        if (!same || elems * 2 != t.second->bytes) {
+            copy_name(t.first, offender, offender_cap);
+            return S1_ERR_TENSOR_SIZE;
         }
         rc = s1_model_set_tensor(model, t.first.c_str(), t.second->data, (size_t)t.second->bytes);
         if (rc != 0) {
@@ -323,6 +395,46 @@ int s1_model_load_checkpoint(void* model, const char* dir, char* offender, size_
         copy_name(missing, offender, offender_cap);
         return S1_ERR_CHECKPOINT_MISSING;
     }
+    return 0;
+}
+
+// The export manifest of a merged Open-Jev checkpoint, open_jev_export.json (written last by
+// recipe/open_jev/export_merged.py:82-90; read by Engine::load, engine.rs:21-46, and
+// DecisionHead::load, executor.rs:21-54): format tag, calibration temperature (finite, > 0),
+// max_length (1..=16384), chat prefix and suffix (strings; the processor's business), and the
+// trained scalar head - `hidden` finite weights and a finite bias, float64 in the file, rounded
+// to float32 as the reference does. Host only. Every out pointer but head_weight is nullable.
+int s1_export_read(const char* dir, int hidden, float* head_weight, float* head_bias, double* temperature,
+                   int* max_length, char* model_id, size_t model_id_cap) {
+    if (!dir || hidden <= 0 || !head_weight) return S1_ERR_ARGUMENT;
+    std::string text;
+    if (!read_text(std::string(dir) + "/open_jev_export.json", &text)) return S1_ERR_CHECKPOINT_IO;
+    Json root;
+    if (!parse_json(text.data(), text.size(), &root) || root.kind != Json::Object) return S1_ERR_CHECKPOINT_FORMAT;
+    const Json* format = root.get("format");
+    if (!format || format->kind != Json::String || format->str != "open-jev-text-merged/1") return S1_ERR_CHECKPOINT_FORMAT;
+    const Json *temp = root.get("temperature"), *len = root.get("max_length"), *w = root.get("head_weight"),
+               *b = root.get("head_bias"), *pre = root.get("chat_prefix"), *suf = root.get("chat_suffix"),
+               *id = root.get("model_id");
+    if (!temp || temp->kind != Json::Number || !isfinite(temp->num) || !(temp->num > 0.0)) return S1_ERR_EXPORT_FIELD;
+    uint64_t max_len = 0;
+    if (!len || !len->as_u64(&max_len) || max_len < 1 || max_len > 16384) return S1_ERR_EXPORT_FIELD;
+    if (!pre || pre->kind != Json::String || !suf || suf->kind != Json::String) return S1_ERR_EXPORT_FIELD;
+    if (!w || w->kind != Json::Array || (int)w->items.size() != hidden || !b || b->kind != Json::Number)
+        return S1_ERR_EXPORT_FIELD;
+    const float bias = (float)b->num;
+    if (!isfinite(bias)) return S1_ERR_EXPORT_FIELD;
+    for (int i = 0; i < hidden; i++) {
+        const Json& x = w->items[i];
+        if (x.kind != Json::Number) return S1_ERR_EXPORT_FIELD;
+        const float v = (float)x.num;
+        if (!isfinite(v)) return S1_ERR_EXPORT_FIELD;
+        head_weight[i] = v;
+    }
+    if (head_bias) *head_bias = bias;
+    if (temperature) *temperature = temp->num;
+    if (max_length) *max_length = (int)max_len;
+    if (model_id && model_id_cap) copy_name(id && id->kind == Json::String ? id->str : std::string(), model_id, model_id_cap);
     return 0;
 }
 

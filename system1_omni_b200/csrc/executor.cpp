@@ -10,6 +10,7 @@
 
 #include <algorithm>
 #include <deque>
+#include <initializer_list>
 #include <numeric>
 #include <string>
 #include <unordered_map>
@@ -37,6 +38,8 @@ constexpr int ENDS_RING = 16;
 struct Tensor {
     size_t offset = 0, bytes = 0;
     bool filled = false;
+    int rank = 0;
+    uint64_t shape[3] = {};  // the checkpoint tensor's shape (Weights::get, model.rs:306-320)
 };
 
 // Byte offsets into one scratch allocation for up to `cap` tokens (model.rs:415-555).
@@ -133,9 +136,14 @@ int validate(const S1Config& c) {
 void plan_arena(Model* m) {
     const S1Config& c = m->cfg;
     size_t at = 0;
-    auto place = [&](const std::string& name, size_t elems, bool aligned) {
+    auto place = [&](const std::string& name, std::initializer_list<size_t> shape, bool aligned) {
         if (aligned) at = (at + ALIGN - 1) / ALIGN * ALIGN;
         Tensor t;
+        size_t elems = 1;
+        for (size_t extent : shape) {
+            t.shape[t.rank++] = extent;
+            elems *= extent;
+        }
         t.offset = at;
         t.bytes = elems * BF16;
         at += t.bytes;
@@ -151,43 +159,43 @@ void plan_arena(Model* m) {
     };
     const size_t h = c.hidden, I = c.intermediate, kd = m->key_dim(), vd = m->value_dim(), hv = c.lin_v_heads;
     const size_t hq = c.heads, hk = c.kv_heads, hd = c.head_dim;
-    m->embed = place("embed_tokens.weight", (size_t)c.vocab * h, true);
-    m->final_norm = place("norm.weight", h, true);
+    m->embed = place("embed_tokens.weight", {(size_t)c.vocab, h}, true);
+    m->final_norm = place("norm.weight", {h}, true);
     m->layers.resize(c.n_layers);
     for (int i = 0; i < c.n_layers; i++) {
         const std::string p = "layers." + std::to_string(i) + ".";
         Layer& ly = m->layers[i];
         ly.full = m->full[i] != 0;
         if (!ly.full) {
-            const Tensor a = place(p + "linear_attn.in_proj_qkv.weight", (2 * kd + vd) * h, true);
-            place(p + "linear_attn.in_proj_z.weight", vd * h, false);
-            place(p + "linear_attn.in_proj_b.weight", hv * h, false);
-            const Tensor d = place(p + "linear_attn.in_proj_a.weight", hv * h, false);
+            const Tensor a = place(p + "linear_attn.in_proj_qkv.weight", {2 * kd + vd, h}, true);
+            place(p + "linear_attn.in_proj_z.weight", {vd, h}, false);
+            place(p + "linear_attn.in_proj_b.weight", {hv, h}, false);
+            const Tensor d = place(p + "linear_attn.in_proj_a.weight", {hv, h}, false);
             ly.in_proj = join(a, d);
         } else {
-            const Tensor a = place(p + "self_attn.q_proj.weight", hq * hd * 2 * h, true);
-            place(p + "self_attn.k_proj.weight", hk * hd * h, false);
-            const Tensor d = place(p + "self_attn.v_proj.weight", hk * hd * h, false);
+            const Tensor a = place(p + "self_attn.q_proj.weight", {hq * hd * 2, h}, true);
+            place(p + "self_attn.k_proj.weight", {hk * hd, h}, false);
+            const Tensor d = place(p + "self_attn.v_proj.weight", {hk * hd, h}, false);
             ly.qkv = join(a, d);
         }
         {
-            const Tensor a = place(p + "mlp.gate_proj.weight", I * h, true);
-            const Tensor d = place(p + "mlp.up_proj.weight", I * h, false);
+            const Tensor a = place(p + "mlp.gate_proj.weight", {I, h}, true);
+            const Tensor d = place(p + "mlp.up_proj.weight", {I, h}, false);
             ly.gate_up = join(a, d);
         }
-        ly.down = place(p + "mlp.down_proj.weight", h * I, true);
-        ly.input_norm = place(p + "input_layernorm.weight", h, true);
-        ly.post_norm = place(p + "post_attention_layernorm.weight", h, true);
+        ly.down = place(p + "mlp.down_proj.weight", {h, I}, true);
+        ly.input_norm = place(p + "input_layernorm.weight", {h}, true);
+        ly.post_norm = place(p + "post_attention_layernorm.weight", {h}, true);
         if (!ly.full) {
-            ly.conv = place(p + "linear_attn.conv1d.weight", (2 * kd + vd) * 4, true);
-            ly.a_log = place(p + "linear_attn.A_log", hv, true);
-            ly.dt_bias = place(p + "linear_attn.dt_bias", hv, true);
-            ly.norm = place(p + "linear_attn.norm.weight", 128, true);
-            ly.out = place(p + "linear_attn.out_proj.weight", h * vd, true);
+            ly.conv = place(p + "linear_attn.conv1d.weight", {2 * kd + vd, 1, 4}, true);
+            ly.a_log = place(p + "linear_attn.A_log", {hv}, true);
+            ly.dt_bias = place(p + "linear_attn.dt_bias", {hv}, true);
+            ly.norm = place(p + "linear_attn.norm.weight", {128}, true);
+            ly.out = place(p + "linear_attn.out_proj.weight", {h, vd}, true);
         } else {
-            ly.o = place(p + "self_attn.o_proj.weight", h * hq * hd, true);
-            ly.q_norm = place(p + "self_attn.q_norm.weight", hd, true);
-            ly.k_norm = place(p + "self_attn.k_norm.weight", hd, true);
+            ly.o = place(p + "self_attn.o_proj.weight", {h, hq * hd}, true);
+            ly.q_norm = place(p + "self_attn.q_norm.weight", {hd}, true);
+            ly.k_norm = place(p + "self_attn.k_norm.weight", {hd}, true);
         }
     }
     m->arena_bytes = (at + ALIGN - 1) / ALIGN * ALIGN;
@@ -781,6 +789,16 @@ int s1_model_tensor(void* model, const char* name, void** device_ptr, size_t* by
     if (it == m->named.end()) return S1_ERR_UNKNOWN_TENSOR;
     if (device_ptr) *device_ptr = m->w(it->second);
     if (bytes) *bytes = it->second.bytes;
+    return 0;
+}
+
+int s1_model_tensor_shape(void* model, const char* name, int* rank, uint64_t* shape8) {
+    Model* m = static_cast<Model*>(model);
+    if (!m || !name) return S1_ERR_ARGUMENT;
+    auto it = m->named.find(name);
+    if (it == m->named.end()) return S1_ERR_UNKNOWN_TENSOR;
+    if (rank) *rank = it->second.rank;
+    for (int i = 0; shape8 && i < it->second.rank; i++) shape8[i] = it->second.shape[i];
     return 0;
 }
 

@@ -102,6 +102,8 @@ SIGNATURES = {
                                     C.c_size_t, ip, vp, vp]),
     "s1_model_load_checkpoint": (i32, [vp, C.c_char_p, C.c_char_p, C.c_size_t]),
     "s1_model_unfilled": (i32, [vp, C.c_char_p, C.c_size_t]),
+    "s1_model_tensor_shape": (i32, [vp, C.c_char_p, ip, vp]),
+    "s1_export_read": (i32, [C.c_char_p, i32, vp, C.POINTER(f32), C.POINTER(f64), ip, C.c_char_p, C.c_size_t]),
     "s1_gemm_swiglu": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "s1_model_set_exact_packing": (i32, [vp, i32]),
     "s1_model_set_overlap_tokens": (i32, [vp, i32]),

@@ -2,7 +2,7 @@
 
     python -m system1_omni_b200.microbench --what elementwise|gemm|gdn|attention|all [--out file.jsonl]
 
-elementwise  the sweep of BASELINE.json's fifth config: bf16 N(0,1)-like activations with
+elementwise  the elementwise / reduction sweep: bf16 N(0,1)-like activations with
              tokens in {1k, 4k, 16k, 64k} x channels in {2048, 4096, 8192} for causal
              conv1d(k=4)+SiLU, softplus/exp decay gates, gated RMSNorm, residual add + RMSNorm,
              RMSNorm and SiLU*up; achieved GB/s = algorithmic bytes / device time.

@@ -341,6 +341,29 @@ class DecisionHead:
         return head_logits(self.weights, last, self.bias)[0]
 
 
+@dataclass
+class Export:
+    """A merged Open-Jev export's manifest, open_jev_export.json (engine.rs:21-46): the trained
+    scalar head, the calibration temperature of contract::answer and the prompt length cap."""
+    head: DecisionHead
+    temperature: float
+    max_length: int
+    model_id: str
+
+    @classmethod
+    def load(cls, directory, hidden):
+        w = np.zeros(hidden, np.float32)
+        bias, temp, length, mid = C.c_float(), C.c_double(), C.c_int(), C.create_string_buffer(128)
+        L.check(L.load().s1_export_read(os.fsencode(directory), hidden, w.ctypes.data_as(C.c_void_p), C.byref(bias),
+                                        C.byref(temp), C.byref(length), mid, 128), "export manifest")
+        return cls(DecisionHead(w, bias.value), temp.value, length.value, mid.value.decode())
+
+    def decide(self, last_rows):
+        """(index of the chosen candidate, probabilities) from the candidates' last-token rows."""
+        scores = np.array([self.head.score(row) for row in last_rows], np.float32)
+        return answer(scores, self.temperature)
+
+
 def letter_logits(letters, last, n_options):
     last = np.asarray(last, np.float32)
     letters = np.asarray(letters, np.float32).reshape(-1, last.size)[:n_options]

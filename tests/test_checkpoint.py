@@ -97,6 +97,78 @@ def test_malformed_checkpoints_are_refused(tmp_path, cs1):
     assert inspect(tmp_path)[0] == 3007                                   # no embed_tokens.weight under any prefix
 
 
+def test_malformed_headers_are_refused(tmp_path, cs1):
+    def header(obj_text, data=b""):
+        raw = obj_text if isinstance(obj_text, bytes) else obj_text.encode()
+        (tmp_path / "model.safetensors").write_bytes(struct.pack("<Q", len(raw)) + raw + data)
+        return inspect(tmp_path)[0]
+
+    good = {"model.embed_tokens.weight": {"dtype": "BF16", "shape": [4, 8], "data_offsets": [0, 64]}}
+    assert header(json.dumps(good), b"\0" * 64) == 0
+    # a header that ends inside a literal, or inside a string
+    assert header('{"a": t') == 3005
+    assert header('{"a": nul') == 3005
+    assert header('{"a": "xy') == 3005
+    assert header('{"a": "\\u00') == 3005
+    # begin past end, a fractional offset, a negative extent
+    bad = json.loads(json.dumps(good))
+    bad["model.embed_tokens.weight"]["data_offsets"] = [64, 0]
+    assert header(json.dumps(bad), b"\0" * 64) == 3005
+    assert header(json.dumps(good).replace("[0, 64]", "[0, 64.5]"), b"\0" * 64) == 3005
+    assert header(json.dumps(good).replace("[4, 8]", "[-4, 8]"), b"\0" * 64) == 3005
+    # two tensors that share bytes
+    two = dict(good)
+    two["model.norm.weight"] = {"dtype": "BF16", "shape": [8], "data_offsets": [56, 72]}
+    assert header(json.dumps(two), b"\0" * 72) == 3005
+    two["model.norm.weight"]["data_offsets"] = [64, 80]
+    assert header(json.dumps(two), b"\0" * 80) == 0
+    # an escaped name is decoded: "model.embed_tokens.w\u0065ight"
+    esc = json.dumps(good).replace("weight", "w\\u0065ight")
+    assert "\\u0065" in esc
+    assert header(esc, b"\0" * 64) == 0
+
+
+def export_manifest(hidden, **over):
+    m = {"format": "open-jev-text-merged/1", "model_id": "open-jev-9b", "base_revision": "r1", "checkpoint_revision": "r2",
+         "temperature": 1.7, "max_length": 4096, "chat_prefix": "<|im_start|>user\n", "chat_suffix": "<|im_end|>\n",
+         "head_weight": [0.25 * i - 1.0 for i in range(hidden)], "head_bias": -0.125}
+    m.update(over)
+    return m
+
+
+def read_export(directory, hidden):
+    lib = L.load()
+    w = np.zeros(hidden, np.float32)
+    bias, temp, length, mid = C.c_float(), C.c_double(), C.c_int(), C.create_string_buffer(64)
+    code = lib.s1_export_read(os.fsencode(directory), hidden, w.ctypes.data_as(C.c_void_p), C.byref(bias), C.byref(temp),
+                              C.byref(length), mid, 64)
+    return code, w, bias.value, temp.value, length.value, mid.value.decode()
+
+
+def test_export_manifest(tmp_path, cs1):
+    """open_jev_export.json as Engine::load and DecisionHead::load read it (engine.rs:21-46,
+    executor.rs:21-54): head, bias, temperature, length cap; the reference's refusals."""
+    from system1_omni_b200 import model as M
+    hidden = 12
+    assert read_export(tmp_path, hidden)[0] == 3004                      # no manifest: not an export
+    path = tmp_path / "open_jev_export.json"
+    path.write_text(json.dumps(export_manifest(hidden)) + "\n")
+    code, w, bias, temp, length, mid = read_export(tmp_path, hidden)
+    assert (code, bias, temp, length, mid) == (0, -0.125, 1.7, 4096, "open-jev-9b")
+    assert np.array_equal(w, np.array([0.25 * i - 1.0 for i in range(hidden)], np.float32))
+    # the head as the worker applies it: float64 accumulation, float32 result, bias added in float32
+    last = np.linspace(-1, 1, hidden).astype(np.float32)
+    score = M.DecisionHead(w, bias).score(last)
+    assert score == np.float32(np.float32(np.dot(w.astype(np.float64), last.astype(np.float64))) + np.float32(bias))
+    for over in ({"format": "something-else/1"}, {"temperature": 0.0}, {"temperature": "hot"}, {"max_length": 0},
+                 {"max_length": 16385}, {"head_weight": [1.0] * (hidden - 1)}, {"head_weight": [1.0] * (hidden - 1) + ["x"]},
+                 {"head_bias": None}, {"chat_prefix": 3}, {"head_weight": [1e39] + [0.0] * (hidden - 1)}):
+        path.write_text(json.dumps(export_manifest(hidden, **over)))
+        assert read_export(tmp_path, hidden)[0] in (3005, 3008), over
+    path.write_text("{")
+    assert read_export(tmp_path, hidden)[0] == 3005
+
+
 @pytest.mark.gpu
 def test_model_from_checkpoint_matches_set_tensors(tmp_path, cs1):
     from system1_omni_b200 import model as M
@@ -143,3 +215,10 @@ def test_model_from_checkpoint_matches_set_tensors(tmp_path, cs1):
     assert "3007" in msg and names[0] in msg
     msg = attempt(lambda b: b["a"].update({victim: np.zeros(3, np.uint16)}))
     assert "3003" in msg and names[0] in msg
+    # a matrix of the right byte count but transposed is refused too (the reference compares shapes)
+    matrix = "model.layers.0.mlp.down_proj.weight"
+    key = "a" if matrix in shards[0] else "b"
+    msg = attempt(lambda b: b[key].update({matrix: np.ascontiguousarray(b[key][matrix].T)}))
+    assert "3003" in msg and "down_proj" in msg
+    # a tensor under the prefix that the decoder does not use must still be bfloat16
+    assert "3006" in attempt(lambda b: b["b"].update({"model.mtp.fc.weight": np.zeros((8, 8), np.float32)}))

@@ -1,4 +1,4 @@
-"""BASELINE.json's first configuration: one Gated DeltaNet layer prefill, seed 0, batch 1,
+"""The single-layer configuration: one Gated DeltaNet layer prefill, seed 0, batch 1,
 T = 2048, hidden 2048, 16 q/k and 16 v heads of 128, chunk 64, conv kernel 4, x ~ N(0,1),
 weights ~ N(0, 0.02), A_log ~ U(0, ln 16), dt_bias ~ N(0, 0.1). The device layer is compared
 with the CPU oracle composed operator by operator (same rounding points) and with a variant
