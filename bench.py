@@ -26,6 +26,8 @@ One JSON line on rank 0:
              the logits bit for bit with what the gather delivered
   cpu_baseline  the CPU oracle (a port of the reference's arithmetic, OpenMP) on a bounded
              sample of the same workload, N = 1 only
+  roofline.library_ms_per_step  the vendor library's GEMM on the same packs and shapes, timed after
+             everything else from a comparison library of its own (N = 1 only)
 --impl reference times that CPU oracle as the reference arm (the reference has no CPU forward
 pass of its own: its CPU code for this path is the float64 test oracles the port restates).
 """
@@ -229,6 +231,77 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def library_gemm_ms(cfg, model, pack_rows, stream):
+    """The vendor library's GEMM (cuBLASLt, from the comparison arm's own shared object, which the
+    product neither links nor loads) on every projection shape of one step, after the timed
+    regions, and this library's kernel under the same protocol: each (pack, projection) timed alone
+    (a warm-up launch, then 3 launches between events), milliseconds x the layers that run it,
+    summed over the step. Operands are the model's own random weights (w: the projection of the
+    first layer of its kind, x: rows of the embedding table), so that neither arm computes on
+    constant data."""
+    from system1_omni_b200 import lib as L
+    from system1_omni_b200.microbench import compare_library
+    compare = compare_library()
+    if compare is None:
+        return None
+    lib = L.load()
+    h, I = cfg.hidden, cfg.intermediate
+    gdn_in = 2 * cfg.key_dim + 2 * cfg.value_dim + 2 * cfg.lin_v_heads
+    attn_in = cfg.heads * cfg.head_dim * 2 + 2 * cfg.kv_heads * cfg.head_dim
+    full = cfg.full_attention
+    n_full = sum(full)
+    n_lin = cfg.n_layers - n_full
+    lin, att = full.index(False) if n_lin else None, full.index(True) if n_full else None
+
+    def tensor(name):
+        ptr, nbytes = C.c_void_p(), C.c_size_t()
+        L.check(lib.s1_model_tensor(model.handle, name.encode(), C.byref(ptr), C.byref(nbytes)), name)
+        return ptr
+
+    shapes = [(2 * I, h, cfg.n_layers, tensor("layers.0.mlp.gate_proj.weight")),
+              (h, I, cfg.n_layers, tensor("layers.0.mlp.down_proj.weight"))]
+    if n_lin:
+        shapes += [(gdn_in, h, n_lin, tensor(f"layers.{lin}.linear_attn.in_proj_qkv.weight")),
+                   (h, cfg.value_dim, n_lin, tensor(f"layers.{lin}.linear_attn.out_proj.weight"))]
+    if n_full:
+        shapes += [(attn_in, h, n_full, tensor(f"layers.{att}.self_attn.q_proj.weight")),
+                   (h, cfg.heads * cfg.head_dim, n_full, tensor(f"layers.{att}.self_attn.o_proj.weight"))]
+    x = tensor("embed_tokens.weight")
+    rows = max(pack_rows)
+    if rows * max(k for _, k, _, _ in shapes) > cfg.vocab * h:
+        return None
+    y = L.DeviceBuffer(rows * max(n for n, _, _, _ in shapes) * 2)
+    handle = lib.cs1_gemm_create(0)
+    e0, e1 = L.Event(), L.Event()
+
+    def timed(call):
+        if call() != 0:
+            return None
+        e0.record(stream)
+        for _ in range(3):
+            call()
+        e1.record(stream)
+        e1.sync()
+        return e0.elapsed_ms(e1) / 3
+
+    ours = theirs = 0.0
+    for m in pack_rows:
+        for n, k, count, w in shapes:
+            a = timed(lambda: lib.s1_gemm_unsplit(handle, x, w, y.at(), m, n, k, n, stream))
+            b = timed(lambda: compare.s1_compare_library_gemm(x, w, y.at(), m, n, k, stream))
+            if a is None or b is None:
+                lib.cs1_gemm_destroy(handle)
+                return None
+            ours += a * count
+            theirs += b * count
+    lib.cs1_gemm_destroy(handle)
+    return {"library_ms": theirs, "own_ms": ours,
+            "note": "cuBLASLt and this library's whole-tile GEMM on the same packs, projection shapes and operands, each "
+                    "launch shape timed alone (short bursts at high clocks, unlike the seconds-long step) x its layers; "
+                    "the gate/up product here writes [rows, 2 I] in both arms (in the step this library's epilogue "
+                    "applies the SiLU-multiply and writes half of it)"}
+
+
 def fit_cost(samples):
     """Least squares of pack milliseconds on (sum T, sum T^2) over every rank's packs; a, b >= 0."""
     s = np.asarray([r for r in samples if r[2] > 0], np.float64)
@@ -250,6 +323,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=64, help="fewer layers for a quick functional check only")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-library-arm", action="store_true", help="skip the vendor library's GEMM comparison (N = 1 only)")
     ap.add_argument("--graphs", type=int, default=1, help="CUDA-graph replay of repeated packs (0 = eager)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -304,6 +378,7 @@ def main():
         disp.stage(ids_all)
         disp.upload()
         cost = {"a_ms_per_token": a, "b_ms_per_token2": b, "source": "least squares over this run's pack times"}
+    edges = list(disp.pack_start) + [len(disp.local)]      # of the plan the timed steps run
     local_tokens = disp.local_tokens
     total_tokens = int(lengths.sum())
 
@@ -389,6 +464,9 @@ def main():
         model.close()
         return
 
+    library = library_gemm_ms(cfg, model, [int(lengths[disp.local[edges[p]:edges[p + 1]]].sum()) for p in range(disp.n_packs)],
+                              stream) if world == 1 and not args.no_library_arm else None
+
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         secs, layers, threads = cpu_sample(1)
@@ -418,7 +496,10 @@ def main():
                      "frac": achieved / pk["tflops"], "traffic": GEMM_TRAFFIC["bytes"], "traffic_of": GEMM_TRAFFIC["of"],
                      "kernel": "bf16 GEMM family, tcgen05 (this library), rank 0's share",
                      "launches_per_step": int(fam_launch[0]), "flops_per_step": flops, "ms_per_step": gemm_ms,
-                     "peak_source": pk["source"] + " (sustained cuBLAS bf16)"},
+                     "peak_source": pk["source"] + " (sustained cuBLAS bf16)",
+                     "library_ms_per_step": library["library_ms"] if library else None,
+                     "own_ms_per_step_same_protocol": library["own_ms"] if library else None,
+                     "library_note": library["note"] if library else "comparison arm not run (N > 1, switched off, or not built)"},
         "per_family": per_family,
         "balance": {"tokens_by_rank": tokens_by_rank, "busy_ms_by_rank": busy_by_rank,
                     "packs_by_rank": [int(r[2]) for r in per_rank], "requests_by_rank": [int(r[3]) for r in per_rank],

@@ -70,6 +70,24 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// 2^x for x <= 0 (and a little above) without the special-function unit, which the softmax
+// otherwise saturates (16 results per clock and SM against 128 FMAs): the integer below x taken
+// from the low mantissa bits of x + 1.5 * 2^23 rounded down, a cubic for 2^fraction (relative
+// error 8.6e-5, far below the bf16 step P is rounded to), the exponent put in by an integer add.
+// Arguments below -127, -inf included, give exactly 0.
+__device__ __forceinline__ float poly_exp2(float x) {
+    x = fmaxf(x, -127.f);
+    const float t = __fadd_rd(x, 12582912.f);
+    const float f = x - (t - 12582912.f);
+    float p = fmaf(0.07706612f, f, 0.22764599f);
+    p = fmaf(p, f, 0.69511658f);
+    p = fmaf(p, f, 1.f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+#ifndef ATTN_POLY_EVERY
+#define ATTN_POLY_EVERY 4  // every n-th exponential of a row goes to the FMA pipe; 0 = none
+#endif
+
 // The eight softmax warps. Warp 2 + i and warp 6 + i (i = 0..3) own the 32 query rows of tensor
 // memory lanes [32 ((2 + i) & 3), +32); the first takes the lower half of the score and output
 // columns, the second the upper half.
@@ -139,7 +157,8 @@ __device__ __forceinline__ void softmax_rows(unsigned char* smem, uint64_t* bars
         float sum = 0.f;
 #pragma unroll
         for (int i = 0; i < HN; i++) {
-            const float p = fast_exp2(__uint_as_float(sv[i]) * scale_log2 - mn);
+            const float arg = __uint_as_float(sv[i]) * scale_log2 - mn;
+            const float p = ATTN_POLY_EVERY > 0 && i % ATTN_POLY_EVERY == ATTN_POLY_EVERY - 1 ? poly_exp2(arg) : fast_exp2(arg);
             sv[i] = __float_as_uint(p);
             sum += p;
         }
