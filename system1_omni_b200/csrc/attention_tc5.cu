@@ -39,22 +39,30 @@ namespace {
 constexpr int ABM = 128;       // query rows per block
 constexpr int ATHREADS = 320;  // producer warp, MMA warp, eight softmax warps
 
+#ifndef ATTN_TWO_PER_SM
+#define ATTN_TWO_PER_SM 1  // head dim 128: key tiles of 64 and two blocks to an SM
+#endif
+
 template <int DH>
 struct ACfg {
-    static constexpr int BN = DH == 256 ? 64 : 128;   // keys per tile
+    // Head dim 128 runs with key tiles of 64 so that two blocks fit an SM (99 KB of shared memory
+    // and 256 tensor-memory columns each): one block's MMAs and copies then run under the other's
+    // softmax, which is what bounds a block.
+    static constexpr bool TWO = DH == 128 && ATTN_TWO_PER_SM;
+    static constexpr int BN = DH == 256 || TWO ? 64 : 128;   // keys per tile
     static constexpr int Q_BYTES = ABM * DH * 2;       // DH / 64 boxes of [128 rows, 64 columns]
     static constexpr int KV_BYTES = BN * DH * 2;       // one K or V tile: DH / 64 column boxes of [BN rows, 64]
-    static constexpr int P_BYTES = ABM * BN * 2;       // BN / 64 boxes of [128 rows, 64 keys]
     static constexpr int OFF_K = Q_BYTES;
     static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;
-    static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
-    static constexpr int OFF_BAR = OFF_P + P_BYTES;
+    static constexpr int OFF_BAR = OFF_V + 2 * KV_BYTES;   // P has no tile here: it goes back into tensor memory
     static constexpr int OFF_X = OFF_BAR + 256;        // float [2][2][128]: row maxima (and sums) of the two halves
-    // 195 KB (Dh 128), 211 KB (Dh 256); Dh 64 needs 116 KB and asks for 120 so that two blocks never share
+    // 99 KB (Dh 128), 195 KB (Dh 256); Dh 64 needs 83 KB and asks for 120 so that two blocks never share
     // an SM (each allocates all 512 tensor-memory columns)
-    static constexpr int SMEM = (OFF_X + 2048 + 1024) > 120 * 1024 ? (OFF_X + 2048 + 1024) : 120 * 1024;
+    static constexpr int SMEM = TWO ? OFF_X + 2048 + 1024 : (OFF_X + 2048 + 1024) > 120 * 1024 ? (OFF_X + 2048 + 1024) : 120 * 1024;
     static constexpr int O_COL = 2 * BN;               // tensor memory: two score buffers, then the output
-    static constexpr int TMEM_COLS = 512;
+    static constexpr int TMEM_COLS = TWO ? 256 : 512;
+    static constexpr int BLOCKS_PER_SM = TWO ? 2 : 1;
+    static_assert(!TWO || (2 * (SMEM + 1024) <= 227 * 1024 && O_COL + DH <= TMEM_COLS), "two blocks share an SM");
 };
 
 __device__ int g_attn_error = 0;
@@ -107,10 +115,6 @@ __device__ __forceinline__ void softmax_rows(unsigned char* smem, uint64_t* bars
     const int r = quarter * 32 + lane;
     const int row = q0 + r;
     const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    // P: boxes of 64 keys, 128 bytes per row, 16-byte chunks swizzled by the row
-    unsigned char* p_row = smem + G::OFF_P + r * 128 + (BN == 128 ? hf * (ABM * 128) : 0);
-    const int chunk0 = BN == 128 ? 0 : hf * 4;
-    const int sw = r & 7;
     auto fail = [&](int code) {
         atomicCAS(&g_attn_error, 0, code);
         *abort_flag = 1;
@@ -185,17 +189,20 @@ __device__ __forceinline__ void softmax_rows(unsigned char* smem, uint64_t* bars
                 tmem_st_wait();
             }
         }
+        // P goes back into tensor memory as bf16, two keys to a column, over the first half of the
+        // score buffer it came from (every thread of the block has taken its scores out of it: the
+        // exchange of the row maxima lies in between); the P V product reads it from there as its A
+        // operand. The next scores for this buffer are issued behind that product.
+        {
+            uint32_t pk[HN / 2];
 #pragma unroll
-        for (int ch = 0; ch < HN / 8; ch++) {
-            const uint32_t* v = &sv[ch * 8];
-            uint4 w;
-            w.x = pack2(__uint_as_float(v[0]), __uint_as_float(v[1]));
-            w.y = pack2(__uint_as_float(v[2]), __uint_as_float(v[3]));
-            w.z = pack2(__uint_as_float(v[4]), __uint_as_float(v[5]));
-            w.w = pack2(__uint_as_float(v[6]), __uint_as_float(v[7]));
-            *reinterpret_cast<uint4*>(p_row + (((chunk0 + ch) ^ sw) * 16)) = w;
+            for (int i = 0; i < HN / 2; i++) pk[i] = pack2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1]));
+            if constexpr (HN == 64)
+                tmem_st_32x32(t_row + b * BN + hf * (HN / 2), pk);
+            else
+                tmem_st_32x16(t_row + b * BN + hf * (HN / 2), pk);
+            tmem_st_wait();
         }
-        fence_proxy_async();
         fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(p_full);
@@ -250,7 +257,7 @@ __device__ __forceinline__ void softmax_rows(unsigned char* smem, uint64_t* bars
 }
 
 template <int DH, bool GATED, bool CAUSAL>
-__global__ void __launch_bounds__(ATHREADS, 1)
+__global__ void __launch_bounds__(ATHREADS, ACfg<DH>::BLOCKS_PER_SM)
     attn_tc5_kernel(const __grid_constant__ AttnMaps maps, const bf16* __restrict__ gate, bf16* __restrict__ out, int T,
                     int Hq, int Hk, float scale_log2, int q_base, int own_base, int vec_ok) {
     using namespace tc5;
@@ -358,10 +365,10 @@ __global__ void __launch_bounds__(ATHREADS, 1)
             const bool issuer = elect_one();
             constexpr uint32_t idesc_s = instr_desc(1, ABM, BN);
             constexpr uint32_t idesc_o = instr_desc_b_mn(1, ABM, DH);
-            const uint32_t q_addr = smem_addr(smem), p_addr = smem_addr(smem + G::OFF_P);
+            const uint32_t q_addr = smem_addr(smem);
             bool ok = mbar_wait(q_full, 0, abort_flag);
             if (!ok) fail(23);
-            // P V of tile t: A = P (K-major over keys), B = V tile read MN-major
+            // P V of tile t: A = P in tensor memory (K-major over keys, where the scores were), B = V tile read MN-major
             auto issue_pv = [&](int t) {
                 const int stage = t & 1;
                 if (!mbar_wait(p_full, t & 1, abort_flag)) {
@@ -377,9 +384,8 @@ __global__ void __launch_bounds__(ATHREADS, 1)
                 if (issuer) {
 #pragma unroll
                     for (int kk = 0; kk < BN / 16; kk++) {
-                        const uint64_t a = smem_desc_sw128(p_addr + (kk / 4) * (ABM * 128) + (kk % 4) * 32);
                         const uint64_t b = smem_desc_mn_sw128(v_addr + kk * 2048, BN * 128, 1024);
-                        mma_bf16_ss(tmem_base + G::O_COL, a, b, idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
+                        mma_bf16_ts(tmem_base + G::O_COL, tmem_base + stage * BN + kk * 8, b, idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
                     }
                     mma_commit(&v_empty[stage]);
                     mma_commit(o_done);
