@@ -147,26 +147,36 @@ __device__ __forceinline__ void softmax_rows(unsigned char* smem, uint64_t* bars
                 for (int i = 0; i < HN; i++)
                     if (CAUSAL ? k0 + i > row : k0 + i >= T) sv[i] = 0xff800000u;  // -inf
             }
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four short chains instead of one long one
 #pragma unroll
-            for (int i = 0; i < HN; i++) mx = fmaxf(mx, __uint_as_float(sv[i]));
+            for (int i = 0; i < HN; i++) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sv[i]));
+            mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         }
         // the row maximum over both halves; the buffers alternate, so one barrier per tile is enough
         xchg[(b * 2 + hf) * ABM + r] = mx;
         asm volatile("bar.sync 1, 256;" ::: "memory");
         if (!ok) continue;
         mx = fmaxf(mx, xchg[(b * 2 + (hf ^ 1)) * ABM + r]);
-        const float mn = fmaxf(m, mx * scale_log2);
-        const float alpha = fast_exp2(m - mn);
+        // m is the offset the exponentials are taken against, not necessarily the running maximum: it
+        // moves only when the maximum has grown by more than 8 (in log2 units) past it. Until then the
+        // exponentials stay below 2^8 - nothing for float32 sums or bf16 P - and the accumulator and the
+        // row sum need no rescaling, which saves a round trip of O through the registers on most tiles
+        // (with the exact maximum nearly every tile of the first few thousand keys moves some row's).
+        // Both threads of a row see the same m and mx, so they decide alike.
+        const float top = fmaxf(m, mx * scale_log2);
+        const bool move = top > m + 8.f;
+        const float mn = move ? top : m;
+        const float alpha = move ? fast_exp2(m - mn) : 1.f;
         m = mn;
-        float sum = 0.f;
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < HN; i++) {
             const float arg = __uint_as_float(sv[i]) * scale_log2 - mn;
             const float p = ATTN_POLY_EVERY > 0 && i % ATTN_POLY_EVERY == ATTN_POLY_EVERY - 1 ? poly_exp2(arg) : fast_exp2(arg);
             sv[i] = __float_as_uint(p);
-            sum += p;
+            s4[i & 3] += p;
         }
-        l = l * alpha + sum;
+        l = l * alpha + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
 
         if (j > 0) {
             // P V of the previous tile is complete: the accumulator may be rescaled and P overwritten

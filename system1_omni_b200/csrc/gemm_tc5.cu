@@ -325,11 +325,12 @@ constexpr int PAIR_ACC_STRIDE = 256;
 
 // Tile index -> (row block, column block) for the pair kernel. Blocks that run at the same time
 // take consecutive indices and fetch the same k-block at the same time; requests for one
-// x or w tile then coincide in L2. Walking 8 row blocks per column block (instead of all of
+// x or w tile then coincide in L2. Walking GM = 8 row blocks per column block (instead of all of
 // them) makes the 74 tiles in flight an 8 x 9 patch: 17 distinct operand tiles per k-block
-// rather than num_m + 74 / num_m.
-__device__ __forceinline__ void pair_tile_coords(int tile, int num_m, int num_n, int& m, int& n) {
-    constexpr int GM = 8;
+// rather than num_m + 74 / num_m. The host widens the walk to 16 row blocks where their rows of x
+// stay in L2 from one column block to the next (pair_walk): w then streams from HBM once per 16
+// row blocks instead of once per 8.
+__device__ __forceinline__ void pair_tile_coords(int tile, int num_m, int num_n, int GM, int& m, int& n) {
     const int per_group = GM * num_n;
     const int group = tile / per_group, in = tile - group * per_group;
     const int first = group * GM;
@@ -403,7 +404,7 @@ struct PieceIter {
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
                          bf16* __restrict__ y, int M, int N, int K, int ldy, int vec_ok, int BN, int splits, int mode,
-                         float* __restrict__ partials, int* __restrict__ counters, int swiglu) {
+                         float* __restrict__ partials, int* __restrict__ counters, int swiglu, int walk) {
     using namespace tc5;
     grid_dep_trigger();
     extern __shared__ unsigned char smem_raw[];
@@ -472,7 +473,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
             int ahead = 0;
             if (more) {
                 int m_idx, n_idx;
-                pair_tile_coords(pc.tile, num_m, num_n, m_idx, n_idx);
+                pair_tile_coords(pc.tile, num_m, num_n, walk, m_idx, n_idx);
                 const int n0 = swiglu ? n_idx * half_n + (int)rank * N : n_idx * BN + (int)rank * half_n;
                 ahead = min(pc.kb1 - pc.kb0, (int)nstages);
                 for (int i = 0; i < ahead && issuer; i++) {
@@ -483,7 +484,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
             grid_dep_sync();
             for (bool first_piece = true; ok && more; first_piece = false, more = pieces.next(pc)) {
                 int m_idx, n_idx;
-                pair_tile_coords(pc.tile, num_m, num_n, m_idx, n_idx);
+                pair_tile_coords(pc.tile, num_m, num_n, walk, m_idx, n_idx);
                 const int m0 = m_idx * 2 * BM + (int)rank * BM;
                 const int n0 = swiglu ? n_idx * half_n + (int)rank * N : n_idx * BN + (int)rank * half_n;
                 for (int kb = pc.kb0; kb < pc.kb1; kb++) {
@@ -558,7 +559,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
             const int tile = pc.tile;
             const bool shared_tile = pc.nparts > 1;
             int m_idx, n_idx;
-            pair_tile_coords(tile, num_m, num_n, m_idx, n_idx);
+            pair_tile_coords(tile, num_m, num_n, walk, m_idx, n_idx);
             const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
             if (!mbar_wait_idle(&tfull[acc], acc_phase, abort_flag)) {
                 fail(14);
@@ -1088,6 +1089,18 @@ PairPlan pair_plan(int M, int N, int K, int pairs, size_t partial_bytes, int cou
     return best;
 }
 
+// Row blocks walked per column block. 16 where that many blocks' rows of x (16 x 256 x K bf16) fit
+// in a good third of the 126 MB L2 beside the w and y streams, else 8: the energy of the second
+// HBM pass over w is what the wider walk saves (the kernel is tensor-bound either way, and runs
+// under the board's power limit in long steps).
+#ifndef PAIR_WALK_WIDE
+#define PAIR_WALK_WIDE 1
+#endif
+int pair_walk(int M, int K) {
+    const long num_m = (M + 2 * BM - 1) / (2 * BM);
+    return PAIR_WALK_WIDE && num_m > 8 && (size_t)16 * 2 * BM * K * 2 <= ((size_t)48 << 20) ? 16 : 8;
+}
+
 int launch_pair(const void* x, const void* w, void* y, int M, int N, int K, int ldy, DeviceInfo* info,
                 void* partials, size_t partial_bytes, int* counters, int counter_slots, cudaStream_t st) {
     if (!info->pair_smem_set) {
@@ -1105,7 +1118,7 @@ int launch_pair(const void* x, const void* w, void* y, int M, int N, int K, int 
     const int grid = plan.mode == 1 ? 2 * pairs : 2 * (units < pairs ? units : pairs);
     const int vec_ok = store_width(y, ldy);
     return launch_dep_gemm(gemm_tc5_pair_kernel, grid, GEMM_THREADS, PAIR_SMEM, st, mx, mw, static_cast<bf16*>(y), M, N, K, ldy,
-                      vec_ok, bn, plan.splits, plan.mode, static_cast<float*>(partials), counters, 0);
+                      vec_ok, bn, plan.splits, plan.mode, static_cast<float*>(partials), counters, 0, pair_walk(M, K));
 }
 
 // Width of the gate/up tile (half of it gate columns, half up columns) for the fused kernel.
@@ -1140,7 +1153,7 @@ int launch_pair_swiglu(const void* x, const void* w, void* act, int M, int I, in
     const int grid = 2 * (int)(tiles < pairs ? tiles : pairs);
     const int vec_ok = store_width(act, ld);
     return launch_dep_gemm(gemm_tc5_pair_kernel, grid, GEMM_THREADS, PAIR_SMEM, st, mx, mw, static_cast<bf16*>(act), M, I, K, ld,
-                      vec_ok, bn, 1, 0, static_cast<float*>(nullptr), static_cast<int*>(nullptr), 1);
+                      vec_ok, bn, 1, 0, static_cast<float*>(nullptr), static_cast<int*>(nullptr), 1, pair_walk(M, K));
 }
 
 // Which kernel takes a problem of more than 128 rows: the pair kernel, or the single-block kernel
