@@ -63,9 +63,9 @@ FAMILIES = ["gemm", "gdn_prefill", "attention", "gdn_conv", "gdn_gates", "rms_no
             "attn_prep", "other"]
 # DRAM bytes of one launch of the pair kernel (ncu, dram__bytes_read.sum + dram__bytes_write.sum) on the
 # widest projection of this workload at one full pack; the capture and its command are under profiles/.
-GEMM_TRAFFIC = {"bytes": 1.349e9,
+GEMM_TRAFFIC = {"bytes": 1.02e9,
                 "of": "one launch, y[4096,34816] = x[4096,5120] w^T (gate | up at a full pack): algorithmic 683.6e6 bytes "
-                      "(x 41.9e6 + w 356.5e6 + y 285.2e6); w is fetched twice, in two waves of 8 row blocks"}
+                      "(x 41.9e6 + w 356.5e6 + y 285.2e6); the 16 row blocks of the pack share one fetch of each column block of w"}
 
 
 def cfg4(layers=64):
