@@ -290,8 +290,13 @@ __global__ void __launch_bounds__(ATHREADS, ACfg<DH>::BLOCKS_PER_SM)
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int h = blockIdx.y, hk = h / (Hq / Hk);
-    const int q0 = q_base + (gridDim.x - 1 - blockIdx.x) * ABM;  // longest blocks first
+    // Block index -> (query block, head), the heads of one query block next to each other and the
+    // last query block first: under a causal mask a block's work grows with its position, so the
+    // blocks are handed out longest first over the whole launch and the ragged end of the launch
+    // is made of its shortest blocks (the heads of a query block also share their keys in L2).
+    const int nq = gridDim.x / Hq;
+    const int h = blockIdx.x % Hq, hk = h / (Hq / Hk);
+    const int q0 = q_base + (nq - 1 - blockIdx.x / Hq) * ABM;
     const int kv_end = CAUSAL ? min(T, q0 + ABM) : T;
     const int ntiles = (kv_end + BN - 1) / BN;
 
@@ -460,7 +465,7 @@ int launch_attn(const AttnMaps& maps, const bf16* gate, bf16* out, int T, int Hq
         configured[dev] = true;
     }
     constexpr float LOG2E = 1.4426950408889634f;
-    const dim3 grid((T - q_base + ABM - 1) / ABM, Hq);
+    const dim3 grid(((T - q_base + ABM - 1) / ABM) * Hq);
     const int vec_ok = aligned16(out) && (!GATED || aligned16(gate));
     return launch_dep_family(DEP_ATTENTION, attn_tc5_kernel<DH, GATED, CAUSAL>, grid, ATHREADS, G::SMEM, st, maps, gate, out, T, Hq, Hk, scale * LOG2E,
                       q_base, own_base, vec_ok);
