@@ -383,13 +383,40 @@ def main():
         disp.stage(ids_all)
         disp.upload()
         cost = {"a_ms_per_token": a, "b_ms_per_token2": b, "source": "least squares over this run's pack times"}
-    edges = list(disp.pack_start) + [len(disp.local)]      # of the plan the timed steps run
-    local_tokens = disp.local_tokens
     total_tokens = int(lengths.sum())
 
     for _ in range(args.warmup):
         disp.enqueue(resident=True)
     model.synchronize()
+
+    # ---- the GPUs of a box are not equally fast under the board power limit (a few per cent in
+    # sustained clock): each rank's speed = planned cost of its share / device time of two passes,
+    # and the requests are assigned once more to finish together (s1_dispatch_set_speed) ----
+    speeds = None
+    if world > 1:
+        e0, e1 = L.Event(), L.Event()
+        e0.record(stream)
+        disp.enqueue(resident=True)
+        disp.enqueue(resident=True)
+        e1.record(stream)
+        e1.sync()
+        a, b = disp_cost(cost)
+        t = lengths[disp.local].astype(np.float64)
+        seen = disp.allgather([float((a * t + b * t * t).sum()), e0.elapsed_ms(e1) / 2])
+        rate = seen[:, 0] / seen[:, 1]
+        speeds = rate / rate.mean()
+        if speeds.max() / speeds.min() > 1.005:
+            disp.set_speed(speeds)
+            disp.plan(model, lengths, N_CLASSES)
+            disp.stage(ids_all)
+            disp.upload()
+            for _ in range(3):          # new packs: issued eagerly, recorded, replayed
+                disp.enqueue(resident=True)
+            model.synchronize()
+        else:
+            speeds = None
+    edges = list(disp.pack_start) + [len(disp.local)]      # of the plan the timed steps run
+    local_tokens = disp.local_tokens
     lib.s1_model_profile_read(model.handle, None, None, None)      # reset the launch counters
     sampler = ClockSampler(local)
 
@@ -433,7 +460,7 @@ def main():
     check = None
     if rank == 0:
         other = 1 if world > 1 else 0
-        _, theirs, packs = D.layout(lengths, world, other, disp_cost(cost)[0], disp_cost(cost)[1])
+        _, theirs, packs = D.layout(lengths, world, other, disp_cost(cost)[0], disp_cost(cost)[1], speeds)
         first = np.concatenate([[0], np.cumsum(lengths)])
         picked = [packs[0]] if len(packs) == 1 else [packs[0], packs[len(packs) // 2]]
         equal, compared = True, []
@@ -510,6 +537,9 @@ def main():
                     "packs_by_rank": [int(r[2]) for r in per_rank], "requests_by_rank": [int(r[3]) for r in per_rank],
                     "tokens_max_over_mean": max(tokens_by_rank) / (sum(tokens_by_rank) / world),
                     "busy_max_over_mean": max(busy_by_rank) / (sum(busy_by_rank) / world),
+                    "speed_by_rank": None if speeds is None else [round(float(v), 4) for v in speeds],
+                    "speed_note": "relative GPU speed measured before the timed region (planned cost / device time of two "
+                                  "passes); the assignment weights the ranks by it, so token counts differ on purpose",
                     "gather_us_median": float(np.median(gather_us)),
                     "gather_us_note": "host time of H2D + all-gather + D2H on rank 0, which includes the wait for the slowest rank"},
         "dispatch_check": check,

@@ -36,6 +36,12 @@ void s1_dispatch_destroy(void* dispatch);
  * attention layers' quadratic share on the 27B-shaped decoder). Every rank must set the same. */
 int s1_dispatch_set_cost(void* dispatch, double a, double b);
 
+/* Relative speed of every rank's GPU for the assignment (speed [world], > 0; null puts all back
+ * to equal): requests go where they finish earliest, (load + cost) / speed
+ * (s1_assign_requests_weighted). A host measures it as planned cost / busy time of a few passes.
+ * Every rank must set the same values. Takes effect at the next s1_dispatch_plan. */
+int s1_dispatch_set_speed(void* dispatch, const double* speed, int world);
+
 /* The plan alone, on the host (no GPU, no communicator): rank_of [n] for all requests and, for
  * `rank`, its requests in run order (local_index, up to n entries) with their count in *n_local
  * and the first local request of each pack (pack_start, up to n entries). Returns the number of
@@ -43,7 +49,11 @@ int s1_dispatch_set_cost(void* dispatch, double a, double b);
 int s1_dispatch_layout(const int* lengths, int n, int world, double a, double b, int rank, int* rank_of,
                        int* local_index, int* n_local, int* pack_start);
 
-/* Plans a request set (every rank passes the same lengths): s1_assign_requests over all ranks,
+/* s1_dispatch_layout with per-rank speeds (speed [world] or null), as s1_dispatch_set_speed takes them. */
+int s1_dispatch_layout_weighted(const int* lengths, int n, int world, double a, double b, const double* speed, int rank,
+                                int* rank_of, int* local_index, int* n_local, int* pack_start);
+
+/* Plans a request set (every rank passes the same lengths): s1_assign_requests_weighted over all ranks,
  * each rank's requests ordered by length (so that short prompts share packs), packs by
  * s1_batch_ranges. Allocates the staging buffers for `model` (hidden size, stream) and
  * n_classes logits per request. */

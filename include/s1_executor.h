@@ -278,6 +278,12 @@ int s1_batch_ranges(const int* lengths, int n, int* starts);
 /* Token-balanced assignment of whole requests to n_ranks GPUs: longest processing time
  * first on the cost a*T + b*T^2. rank_of [n]. No counterpart in the reference (single GPU). */
 int s1_assign_requests(const int* lengths, int n, int n_ranks, double a, double b, int* rank_of);
+/* The same with ranks of unequal speed (speed [n_ranks], relative, > 0; null = all equal): each
+ * request, longest first, goes to the rank on which it would finish earliest,
+ * (load + cost) / speed. GPUs of one box differ by a few per cent in sustained clock under the
+ * board power limit, which is more than the residue of the token balance. */
+int s1_assign_requests_weighted(const int* lengths, int n, int n_ranks, double a, double b, const double* speed,
+                                int* rank_of);
 
 #define S1_ERR_ARGUMENT 3000
 #define S1_ERR_NONFINITE 3001

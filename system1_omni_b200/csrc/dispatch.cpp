@@ -9,6 +9,7 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <cmath>
 #include <chrono>
 #include <string>
 #include <thread>
@@ -56,6 +57,7 @@ struct Dispatch {
     double* side_dev = nullptr;   // their device staging
     size_t side_cap = 0;
     double a = 1.0, b = 4e-6;
+    std::vector<double> speed;  // per rank, relative; empty = all equal
 
     // the plan
     void* model = nullptr;
@@ -96,11 +98,11 @@ void release_plan(Dispatch* d) {
 }
 
 // rank_of for all requests and every rank's run order: by length, then by request index.
-int layout(const int* lengths, int n, int world, double a, double b, std::vector<int>& rank_of,
+int layout(const int* lengths, int n, int world, double a, double b, const double* speed, std::vector<int>& rank_of,
            std::vector<std::vector<int>>& members) {
     if (n < 0 || world <= 0 || (n > 0 && !lengths)) return S1_ERR_ARGUMENT;
     rank_of.assign(n, 0);
-    D_TRY(s1_assign_requests(lengths, n, world, a, b, rank_of.data()));
+    D_TRY(s1_assign_requests_weighted(lengths, n, world, a, b, speed, rank_of.data()));
     members.assign(world, {});
     for (int i = 0; i < n; i++) members[rank_of[i]].push_back(i);
     for (auto& m : members)
@@ -146,10 +148,15 @@ extern "C" {
 
 int s1_dispatch_layout(const int* lengths, int n, int world, double a, double b, int rank, int* rank_of,
                        int* local_index, int* n_local, int* pack_start) {
+    return s1_dispatch_layout_weighted(lengths, n, world, a, b, nullptr, rank, rank_of, local_index, n_local, pack_start);
+}
+
+int s1_dispatch_layout_weighted(const int* lengths, int n, int world, double a, double b, const double* speed, int rank,
+                                int* rank_of, int* local_index, int* n_local, int* pack_start) {
     if (rank < 0 || rank >= world) return -S1_ERR_ARGUMENT;
     std::vector<int> ranks;
     std::vector<std::vector<int>> members;
-    const int rc = layout(lengths, n, world, a, b, ranks, members);
+    const int rc = layout(lengths, n, world, a, b, speed, ranks, members);
     if (rc != 0) return -rc;
     if (rank_of) std::copy(ranks.begin(), ranks.end(), rank_of);
     const std::vector<int>& mine = members[rank];
@@ -215,6 +222,18 @@ int s1_dispatch_set_cost(void* dispatch, double a, double b) {
     return 0;
 }
 
+int s1_dispatch_set_speed(void* dispatch, const double* speed, int world) {
+    Dispatch* d = static_cast<Dispatch*>(dispatch);
+    if (!d || (speed && world != d->world)) return S1_ERR_ARGUMENT;
+    for (int r = 0; speed && r < world; r++)
+        if (!(speed[r] > 0.0) || !std::isfinite(speed[r])) return S1_ERR_ARGUMENT;
+    if (speed)
+        d->speed.assign(speed, speed + world);
+    else
+        d->speed.clear();
+    return 0;
+}
+
 int s1_dispatch_plan(void* dispatch, void* model, const int* lengths, int n, int n_classes) {
     Dispatch* d = static_cast<Dispatch*>(dispatch);
     if (!d || !model || n <= 0 || !lengths || n_classes <= 0) return S1_ERR_ARGUMENT;
@@ -228,7 +247,7 @@ int s1_dispatch_plan(void* dispatch, void* model, const int* lengths, int n, int
     d->n_classes = n_classes;
     d->n = n;
     d->lengths.assign(lengths, lengths + n);
-    D_TRY(layout(lengths, n, d->world, d->a, d->b, d->rank_of, d->members));
+    D_TRY(layout(lengths, n, d->world, d->a, d->b, d->speed.empty() ? nullptr : d->speed.data(), d->rank_of, d->members));
     d->most = 0;
     for (const auto& m : d->members) d->most = std::max(d->most, (int)m.size());
     const std::vector<int>& mine = d->members[d->rank];

@@ -9,6 +9,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <cmath>
 #include <deque>
 #include <initializer_list>
 #include <numeric>
@@ -1185,18 +1186,29 @@ int s1_batch_ranges(const int* lengths, int n, int* starts) {
 }
 
 int s1_assign_requests(const int* lengths, int n, int n_ranks, double a, double b, int* rank_of) {
+    return s1_assign_requests_weighted(lengths, n, n_ranks, a, b, nullptr, rank_of);
+}
+
+int s1_assign_requests_weighted(const int* lengths, int n, int n_ranks, double a, double b, const double* speed,
+                                int* rank_of) {
     if (n < 0 || n_ranks <= 0 || (n > 0 && (!lengths || !rank_of))) return S1_ERR_ARGUMENT;
+    for (int r = 0; speed && r < n_ranks; r++)
+        if (!(speed[r] > 0.0) || !std::isfinite(speed[r])) return S1_ERR_ARGUMENT;
     std::vector<int> idx(n);
     std::iota(idx.begin(), idx.end(), 0);
     auto cost = [&](int i) { return a * lengths[i] + b * (double)lengths[i] * (double)lengths[i]; };
     std::stable_sort(idx.begin(), idx.end(), [&](int x, int y) { return cost(x) > cost(y); });
     std::vector<double> load(n_ranks, 0.0);
+    // each request, longest first, goes where it would finish earliest (the first such rank);
+    // with equal speeds that is the rank with the least load
+    auto finish = [&](int r, double c) { return speed ? (load[r] + c) / speed[r] : load[r]; };
     for (int i : idx) {
+        const double c = cost(i);
         int best = 0;
         for (int r = 1; r < n_ranks; r++)
-            if (load[r] < load[best]) best = r;
+            if (finish(r, c) < finish(best, c)) best = r;
         rank_of[i] = best;
-        load[best] += cost(i);
+        load[best] += c;
     }
     return 0;
 }

@@ -18,17 +18,22 @@ from . import lib as L
 from . import model as M
 
 
-def layout(lengths, world, rank, a=1.0, b=4e-6):
-    """(rank_of [n], this rank's request indices in run order, packs as ranges over that order)."""
+def layout(lengths, world, rank, a=1.0, b=4e-6, speed=None):
+    """(rank_of [n], this rank's request indices in run order, packs as ranges over that order).
+    speed: relative speed of every rank's GPU (None = equal)."""
     lengths = np.ascontiguousarray(lengths, dtype=np.int32)
+    sp = None if speed is None else np.ascontiguousarray(speed, dtype=np.float64)
+    if sp is not None and sp.size != world:
+        raise ValueError("one speed per rank")
     n = lengths.size
     rank_of = np.zeros(max(n, 1), np.int32)
     local = np.zeros(max(n, 1), np.int32)
     starts = np.zeros(max(n, 1), np.int32)
     n_local = C.c_int(0)
-    packs = L.load().s1_dispatch_layout(lengths.ctypes.data_as(C.c_void_p), n, world, a, b, rank,
-                                        rank_of.ctypes.data_as(C.c_void_p), local.ctypes.data_as(C.c_void_p),
-                                        C.byref(n_local), starts.ctypes.data_as(C.c_void_p))
+    packs = L.load().s1_dispatch_layout_weighted(lengths.ctypes.data_as(C.c_void_p), n, world, a, b,
+                                                 None if sp is None else sp.ctypes.data_as(C.c_void_p), rank,
+                                                 rank_of.ctypes.data_as(C.c_void_p), local.ctypes.data_as(C.c_void_p),
+                                                 C.byref(n_local), starts.ctypes.data_as(C.c_void_p))
     if packs < 0:
         raise L.CudaError(-packs, "dispatch layout")
     edges = [int(x) for x in starts[:packs]] + [n_local.value]
@@ -72,6 +77,14 @@ class Dispatcher:
 
     def set_cost(self, a, b):
         L.check(L.load().s1_dispatch_set_cost(self.handle, float(a), float(b)), "dispatch cost")
+
+    def set_speed(self, speed):
+        """Relative speed of every rank's GPU (None = equal); used by the next plan."""
+        if speed is None:
+            L.check(L.load().s1_dispatch_set_speed(self.handle, None, self.world), "dispatch speed")
+            return
+        sp = np.ascontiguousarray(speed, dtype=np.float64)
+        L.check(L.load().s1_dispatch_set_speed(self.handle, sp.ctypes.data_as(C.c_void_p), sp.size), "dispatch speed")
 
     def plan(self, model, lengths, n_classes):
         lengths = np.ascontiguousarray(lengths, dtype=np.int32)
@@ -139,7 +152,7 @@ class Dispatcher:
         return out
 
 
-def run_sharded(requests, forward, n_classes, rank, world, gather=None, a=1.0, b=4e-6):
+def run_sharded(requests, forward, n_classes, rank, world, gather=None, a=1.0, b=4e-6, speed=None):
     """The dispatcher's plan with a caller-supplied forward and gather.
 
     forward(list_of_requests) -> float32 [n, n_classes] logits of one pack on this rank.
@@ -148,7 +161,7 @@ def run_sharded(requests, forward, n_classes, rank, world, gather=None, a=1.0, b
     in request order, other ranks get None. With world == 1 no communication happens.
     """
     lengths = np.array([len(r) for r in requests], np.int32)
-    rank_of, mine, packs = layout(lengths, world, rank, a, b)
+    rank_of, mine, packs = layout(lengths, world, rank, a, b, speed)
     local = np.zeros((len(mine), n_classes), np.float32)
     for group in packs:
         idx = list(group)
@@ -165,6 +178,6 @@ def run_sharded(requests, forward, n_classes, rank, world, gather=None, a=1.0, b
         return None
     out = np.zeros((len(requests), n_classes), np.float32)
     for r in range(world):
-        theirs = layout(lengths, world, r, a, b)[1]
+        theirs = layout(lengths, world, r, a, b, speed)[1]
         out[theirs] = np.asarray(gathered[r], np.float32).reshape(most, n_classes)[: len(theirs)]
     return out

@@ -135,6 +135,7 @@ SIGNATURES = {
     "s1_decide": (i32, [vp, i32, f64, vp]),
     "s1_batch_ranges": (i32, [vp, i32, vp]),
     "s1_assign_requests": (i32, [vp, i32, i32, f64, f64, vp]),
+    "s1_assign_requests_weighted": (i32, [vp, i32, i32, f64, f64, vp, vp]),
     "s1_device_status": (i32, [ip, ip, ip]),
     "s1_selftest_wait_runs_out": (i32, [i32, vp]),
     "s1_model_config": (i32, [vp, C.POINTER(S1Config)]),
@@ -146,6 +147,8 @@ SIGNATURES = {
     "s1_dispatch_destroy": (None, [vp]),
     "s1_dispatch_set_cost": (i32, [vp, f64, f64]),
     "s1_dispatch_layout": (i32, [vp, i32, i32, f64, f64, i32, vp, vp, ip, vp]),
+    "s1_dispatch_layout_weighted": (i32, [vp, i32, i32, f64, f64, vp, i32, vp, vp, ip, vp]),
+    "s1_dispatch_set_speed": (i32, [vp, vp, i32]),
     "s1_dispatch_plan": (i32, [vp, vp, vp, i32, i32]),
     "s1_dispatch_info": (i32, [vp, ip, C.POINTER(C.c_longlong), ip, vp]),
     "s1_dispatch_local": (i32, [vp, vp, vp]),

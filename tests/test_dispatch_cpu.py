@@ -1,5 +1,6 @@
 """The multi-GPU host logic on CPU: two gloo ranks shard a ragged request set, run a stand-in
 forward pass, gather the logits, and rank 0 must hold exactly what a single rank computes."""
+import ctypes as C
 import os
 import socket
 import sys
@@ -96,3 +97,31 @@ def test_shards_are_balanced_and_complete():
     groups = M.ranges([4000, 100, 50, 5000] + [10] * 40)
     assert [list(g) for g in groups][:3] == [[0], [1, 2], [3]]
     assert all(len(g) <= 16 for g in groups)
+
+
+def test_unequal_speeds_shift_load_to_the_faster_ranks():
+    """Requests go where they finish earliest: finish times (load / speed) come out balanced, equal
+    speeds reproduce the unweighted assignment, and invalid speeds are refused."""
+    from system1_omni_b200 import dispatch
+    from system1_omni_b200 import lib as L
+    rng = np.random.default_rng(3)
+    lengths = np.exp(rng.uniform(np.log(512), np.log(16384), 64)).astype(np.int32)
+    cost = lengths + 2e-5 * lengths.astype(np.float64) ** 2
+    world = 8
+    plain = dispatch.layout(lengths, world, 0, a=1.0, b=2e-5)[0]
+    assert np.array_equal(plain, dispatch.layout(lengths, world, 0, a=1.0, b=2e-5, speed=np.ones(world))[0])
+    speed = np.array([0.95, 1.0, 1.05, 1.0, 1.0, 1.02, 0.97, 1.0])
+    where = dispatch.layout(lengths, world, 0, a=1.0, b=2e-5, speed=speed)[0]
+    for rank in range(1, world):        # every rank derives the same assignment
+        assert np.array_equal(where, dispatch.layout(lengths, world, rank, a=1.0, b=2e-5, speed=speed)[0])
+    finish = np.array([cost[where == r].sum() for r in range(world)]) / speed
+    unweighted = np.array([cost[plain == r].sum() for r in range(world)]) / speed
+    assert finish.max() / finish.mean() < 1.02
+    assert finish.max() < unweighted.max()
+    load = np.array([cost[where == r].sum() for r in range(world)])
+    assert load[2] > load[0]            # the fastest rank carries more than the slowest
+    bad = np.array([1.0, 0.0] + [1.0] * 6)
+    out = np.zeros(64, np.int32)
+    rc = L.load().s1_assign_requests_weighted(lengths.ctypes.data_as(C.c_void_p), 64, world, 1.0, 2e-5,
+                                              bad.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p))
+    assert rc == 3000
