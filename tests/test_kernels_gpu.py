@@ -346,6 +346,36 @@ def test_flash_attention_matches_float64_reference(cs1, stream, dh, t, amp, hq, 
 
 
 @pytest.mark.parametrize("dh", [256, 128])
+@pytest.mark.parametrize("climb", [0.11, 0.13, 1.5, -0.12])
+def test_flash_attention_with_scores_that_climb_along_the_keys(cs1, stream, dh, climb):
+    """The kernel moves a row's exponent offset only when the maximum has grown by 2^8 since the
+    offset was set. Scores that rise by `climb` (in log2 units) per key make every tile's maximum
+    exceed the last: at 0.11-0.13 per key a 64-key tile stays just under / just over the threshold
+    (and a 128-key tile over it), so offsets go stale by up to 2^8 for tiles on end; at 1.5 every
+    tile moves it; falling scores never do. All against the float64 reference."""
+    t, hq, hk = 1024, 2, 1
+    scale = dh ** -0.5
+    rng = np.random.default_rng(17)
+    # q = e0 in every row, k_j = (j * climb / (scale * log2 e)) e0 + noise: score_j * scale * log2 e = j * climb + noise
+    q = np.zeros((t, hq, dh), np.float32)
+    q[:, :, 0] = 1.0
+    k = rng.normal(0, 0.05, (t, hk, dh)).astype(np.float32)
+    k[:, :, 0] = np.arange(t)[:, None] * climb / (scale * np.log2(np.e))
+    ldv = hk * dh
+    q, k = O.f32_to_bf16(q.ravel()), O.f32_to_bf16(k.ravel())
+    v = O.random_bf16(t * ldv, 3, 1.0)
+    qd, kd, vd = dev(q, stream), dev(k, stream), dev(v, stream)
+    out = L.DeviceBuffer(t * hq * dh * 2)
+    L.check(cs1.cs1_attention(qd.at(), kd.at(), vd.at(), ldv, out.at(), t, hq, hk, dh, scale, stream.handle), "attention")
+    got = f32(host(out, (t, hq, dh), stream)).astype(np.float64)
+    assert np.all(np.isfinite(got))
+    want = O.attention_f64(q, k, v, 0, ldv, t, hq, hk, dh, scale)
+    diff = np.abs(got - want).max(-1)
+    worst = (diff / np.maximum(np.abs(want).max(-1), 1e-3)).max()
+    assert worst < 1.6e-2, worst
+
+
+@pytest.mark.parametrize("dh", [256, 128])
 @pytest.mark.parametrize("hq,hk", [(24, 4), (16, 4), (4, 4), (16, 1)])
 def test_fused_attention_gate_matches_separate_pass(cs1, stream, dh, hq, hk):
     # kernels.rs:273-391
@@ -662,6 +692,24 @@ def test_gemm_rows_do_not_depend_on_the_row_count(cs1, stream):
     L.check(cs1.s1_gemm_tcgen05(None, xd.at(100 * K * 2), wd.at(), part.at(), 37, N, K, N, stream.handle), "gemm")
     assert L.gemm_status() == 0
     assert np.array_equal(host(full, (M, N), stream)[100:137], host(part, (37, N), stream))
+
+
+@pytest.mark.parametrize("M,N,K,pad", [(4200, 700, 256, 8), (2305, 264, 6144, 0), (2400, 520, 6400, 0)])
+def test_gemm_many_row_blocks(cs1, stream, M, N, K, pad):
+    """More than eight row blocks of 256: the tiles are walked 16 row blocks per column block where
+    K <= 6144 (a ragged last group at 4200 and 2305 rows) and 8 otherwise (K = 6400). Against the
+    oracle, and the rows of a window inside equal the same rows computed in a small call of their own."""
+    x, w, ldy = gemm_case(M, N, K, pad, seed=9)
+    xd, wd = dev(x, stream), dev(w, stream)
+    y = dev(np.full((M, ldy), 0x7FC0, np.uint16), stream)
+    L.check(cs1.s1_gemm_tcgen05(None, xd.at(), wd.at(), y.at(), M, N, K, ldy, stream.handle), "gemm")
+    got = host(y, (M, ldy), stream)
+    assert L.gemm_status() == 0
+    check_gemm(got, x, w, N)
+    assert np.all(got[:, N:] == 0x7FC0)
+    part = L.DeviceBuffer(300 * N * 2)
+    L.check(cs1.s1_gemm_tcgen05(None, xd.at(2000 * K * 2), wd.at(), part.at(), 300, N, K, N, stream.handle), "gemm")
+    assert np.array_equal(got[2000:2300, :N], host(part, (300, N), stream))
 
 
 def test_gemm_argument_checks(cs1, stream):
