@@ -88,6 +88,19 @@ int s1_dispatch_collect(void* dispatch, const float* head_weights, const float* 
                         double* gather_us);
 
 /* Small collectives for the harness around it (timing protocol, statistics): all ranks. */
+/* One multi-candidate request over the ranks: n candidates continue one shared prefix that every
+ * rank has captured itself (weights and prefix are replicated: s1_prefix_create +
+ * s1_model_prefix_capture on each rank's model). The candidates are assigned to ranks by length
+ * (s1_assign_requests_weighted with the speeds set), each rank continues its share in packed
+ * passes (s1_model_forward_continue), applies the head, and the logits are gathered to rank 0 in
+ * candidate order: logits [n, n_classes] there, may be null elsewhere. ids: all candidates
+ * concatenated, lengths [n], the same on every rank. rank_of_out (nullable): where each went.
+ * Waits for the device. The single-GPU form of this in the reference is
+ * forward_multimodal_capture / _continue (model.rs:954-1073), one candidate per call. */
+int s1_dispatch_candidates(void* dispatch, void* model, const void* prefix, const int32_t* ids, const int* lengths, int n,
+                           const float* head_weights, const float* head_bias, int n_classes, float* logits,
+                           int* rank_of_out);
+
 int s1_dispatch_barrier(void* dispatch);
 int s1_dispatch_allreduce_max(void* dispatch, double* values, int n);
 int s1_dispatch_allgather(void* dispatch, const double* values, int n, double* all /* [world, n] */);

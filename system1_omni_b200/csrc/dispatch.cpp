@@ -407,6 +407,60 @@ int s1_dispatch_collect(void* dispatch, const float* head_weights, const float* 
     return 0;
 }
 
+int s1_dispatch_candidates(void* dispatch, void* model, const void* prefix, const int32_t* ids, const int* lengths, int n,
+                           const float* head_weights, const float* head_bias, int n_classes, float* logits,
+                           int* rank_of_out) {
+    Dispatch* d = static_cast<Dispatch*>(dispatch);
+    if (!d || !model || !prefix || !ids || !lengths || n <= 0 || n_classes <= 0 || !head_weights ||
+        (d->rank == 0 && !logits))
+        return S1_ERR_ARGUMENT;
+    S1Config cfg;
+    D_TRY(s1_model_config(model, &cfg));
+    D_TRY(cs1_set_device(d->device));
+    // every candidate costs its own tokens (the prefix is there already on every rank)
+    std::vector<int> rank_of;
+    std::vector<std::vector<int>> members;
+    D_TRY(layout(lengths, n, d->world, 1.0, 0.0, d->speed.empty() ? nullptr : d->speed.data(), rank_of, members));
+    if (rank_of_out) std::copy(rank_of.begin(), rank_of.end(), rank_of_out);
+    std::vector<size_t> first(n + 1, 0);
+    for (int i = 0; i < n; i++) {
+        if (lengths[i] <= 0) return S1_ERR_ARGUMENT;
+        first[i + 1] = first[i] + (size_t)lengths[i];
+    }
+    int most = 0;
+    for (const auto& m : members) most = std::max(most, (int)m.size());
+    const std::vector<int>& mine = members[d->rank];
+    // this rank's candidates, packed like requests (at most 16 prompts / 4096 tokens a pass)
+    std::vector<int> len(mine.size()), starts(mine.size() + 1);
+    for (size_t i = 0; i < mine.size(); i++) len[i] = lengths[mine[i]];
+    const int packs = s1_batch_ranges(len.data(), (int)len.size(), starts.data());
+    std::vector<double> block((size_t)most * n_classes, 0.0);
+    std::vector<float> hidden, row(n_classes);
+    std::vector<int32_t> pack_ids;
+    for (int p = 0; p < packs; p++) {
+        const int s0 = starts[p], s1 = p + 1 < packs ? starts[p + 1] : (int)mine.size();
+        pack_ids.clear();
+        for (int i = s0; i < s1; i++) pack_ids.insert(pack_ids.end(), ids + first[mine[i]], ids + first[mine[i] + 1]);
+        hidden.resize((size_t)(s1 - s0) * cfg.hidden);
+        D_TRY(s1_model_forward_continue(model, prefix, pack_ids.data(), len.data() + s0, s1 - s0, hidden.data()));
+        for (int i = s0; i < s1; i++) {
+            D_TRY(s1_head_logits(head_weights, head_bias, hidden.data() + (size_t)(i - s0) * cfg.hidden, cfg.hidden, n_classes,
+                                 row.data()));
+            for (int c = 0; c < n_classes; c++) block[(size_t)i * n_classes + c] = row[c];
+        }
+    }
+    // float32 logits travel as float64 (exact) through the harness all-gather
+    std::vector<double> all(block.size() * d->world);
+    if (block.empty()) return 0;
+    D_TRY(s1_dispatch_allgather(d, block.data(), (int)block.size(), all.data()));
+    if (d->rank == 0)
+        for (int r = 0; r < d->world; r++)
+            for (size_t i = 0; i < members[r].size(); i++)
+                for (int c = 0; c < n_classes; c++)
+                    logits[(size_t)members[r][i] * n_classes + c] = (float)all[((size_t)r * most + i) * n_classes + c];
+    return 0;
+}
+
 int s1_dispatch_barrier(void* dispatch) {
     double x = 0.0;
     return s1_dispatch_allreduce_max(dispatch, &x, 1);

@@ -136,6 +136,24 @@ class Dispatcher:
         self.enqueue(False)
         return self.collect(head, bias)
 
+    def candidates(self, model, prefix, candidates, head, bias=None):
+        """One multi-candidate request: `candidates` (lists of token ids, the same on every rank)
+        continue `prefix` (captured on this rank's model) on the ranks they are assigned to.
+        Rank 0: (float32 [n, n_classes] in candidate order, rank_of [n]); others (None, rank_of)."""
+        head = np.ascontiguousarray(head, dtype=np.float32)
+        b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+        lengths = np.array([len(c) for c in candidates], np.int32)
+        ids = np.ascontiguousarray(np.concatenate([np.asarray(c, np.int32) for c in candidates]), dtype=np.int32)
+        out = np.zeros((len(candidates), head.shape[0]), np.float32) if self.rank == 0 else None
+        rank_of = np.zeros(len(candidates), np.int32)
+        L.check(L.load().s1_dispatch_candidates(self.handle, model.handle, prefix.handle, ids.ctypes.data_as(C.c_void_p),
+                                                lengths.ctypes.data_as(C.c_void_p), len(candidates),
+                                                head.ctypes.data_as(C.c_void_p),
+                                                None if b is None else b.ctypes.data_as(C.c_void_p), head.shape[0],
+                                                None if out is None else out.ctypes.data_as(C.c_void_p),
+                                                rank_of.ctypes.data_as(C.c_void_p)), "dispatch candidates")
+        return out, rank_of
+
     def barrier(self):
         L.check(L.load().s1_dispatch_barrier(self.handle), "dispatch barrier")
 

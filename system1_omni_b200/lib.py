@@ -149,6 +149,7 @@ SIGNATURES = {
     "s1_dispatch_layout": (i32, [vp, i32, i32, f64, f64, i32, vp, vp, ip, vp]),
     "s1_dispatch_layout_weighted": (i32, [vp, i32, i32, f64, f64, vp, i32, vp, vp, ip, vp]),
     "s1_dispatch_set_speed": (i32, [vp, vp, i32]),
+    "s1_dispatch_candidates": (i32, [vp, vp, vp, vp, vp, i32, vp, vp, i32, vp, vp]),
     "s1_dispatch_plan": (i32, [vp, vp, vp, i32, i32]),
     "s1_dispatch_info": (i32, [vp, ip, C.POINTER(C.c_longlong), ip, vp]),
     "s1_dispatch_local": (i32, [vp, vp, vp]),

@@ -311,6 +311,68 @@ def prefix(b, out):
     model.close()
 
 
+def candidates(out):
+    """The shared-prefix request of `prefix` with its candidates shared out over the GPUs of one
+    box: run as `python -m torch.distributed.run --nproc-per-node N -m system1_omni_b200.microbench
+    --what candidates` (or alone for N = 1). Every rank builds the 9B-shaped decoder, captures the
+    1536-token prefix itself, and s1_dispatch_candidates assigns the 8 candidates, continues each
+    rank's share in one packed pass and gathers the logits to rank 0. Rank 0 prints the wall-clock
+    milliseconds (max over ranks) of the capture and of the continuation + gather, and checks two
+    candidates against the whole prompt run in one piece (same bits)."""
+    import os
+    import time
+    from . import dispatch as D
+    from . import model as M
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    L.load()
+    L.set_device(local)
+    types = [("full_attention" if (i + 1) % 4 == 0 else "linear_attention") for i in range(32)]
+    cfg = M.Config(hidden=4096, intermediate=12288, layer_types=types, heads=32, kv_heads=8, head_dim=128,
+                   rotary_half=32, lin_k_heads=16, lin_v_heads=32, vocab=151936, eps=1e-6, rope_theta=1e7,
+                   max_positions=262144)
+    model = M.Model(cfg, device=local)
+    model.init_random(seed=0, std=0.02)
+    rng = np.random.default_rng(0)
+    pre = rng.integers(0, cfg.vocab, 1536).tolist()
+    cands = [rng.integers(0, cfg.vocab, int(n)).tolist() for n in rng.integers(32, 129, 8)]
+    head = np.random.default_rng(7).normal(0, 1.0, (1, cfg.hidden)).astype(np.float32)   # a scalar score per candidate
+    d = D.Dispatcher(rank, world, local)
+
+    def timed(fn, warm=2, n=5):
+        for _ in range(warm):
+            r = fn()
+        d.barrier()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            r = fn()
+        model.synchronize()
+        ms = d.max_over_ranks((time.perf_counter() - t0) / n * 1e3)
+        return ms, r
+
+    def capture():
+        p = model.capture_prefix(pre)
+        p.close()
+
+    capture_ms, _ = timed(capture)
+    prefix_state = model.capture_prefix(pre)
+    continue_ms, (scores, where) = timed(lambda: d.candidates(model, prefix_state, cands, head))
+    if rank == 0:
+        same = True
+        for i in (0, len(cands) - 1):
+            last = model.forward_batch([np.asarray(pre + cands[i], np.int32)])[0]
+            same = same and np.array_equal(M.head_logits(head, last).view(np.uint32), scores[i].view(np.uint32))
+        logical = len(pre) + sum(len(c) for c in cands)
+        out({"op": "shared_prefix_request_sharded", "model": "9B-shaped", "n_gpus": world, "prefix": len(pre),
+             "candidates": [len(c) for c in cands], "candidates_by_rank": np.bincount(where, minlength=world).tolist(),
+             "capture_ms": capture_ms, "continue_and_gather_ms": continue_ms,
+             "logical_tokens_per_s": logical / (capture_ms + continue_ms) * 1e3,
+             "bit_equal_to_whole_prompts": bool(same), "timing": "host wall clock, max over ranks"})
+    prefix_state.close()
+    d.close()
+    model.close()
+
+
 def requests(b, out):
     """One GPU's share of the ragged request set on a 27B-shaped decoder (hidden 5120, 64 layers
     3:1, 16 qk / 48 v GDN heads, 24 q / 4 kv attention heads of 128, MLP 17408; 47 GB of bf16
@@ -417,7 +479,7 @@ def attention(b, out):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", default="all", choices=["elementwise", "gemm", "gdn", "layer", "attention", "prefix", "requests", "latency", "all"])
+    ap.add_argument("--what", default="all", choices=["elementwise", "gemm", "gdn", "layer", "attention", "prefix", "candidates", "requests", "latency", "all"])
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--out", default=None)
@@ -428,6 +490,11 @@ def main():
     ap.add_argument("--gdn-shape", type=int, nargs=3, metavar=("H", "HK", "T"), default=None,
                     help="time this one delta-rule problem only (for a profiler capture)")
     args = ap.parse_args()
+    if args.what == "candidates":  # one process per GPU; sets its own device
+        def emit(row):
+            print(json.dumps({k: (round(v, 4) if isinstance(v, float) else v) for k, v in row.items()}), flush=True)
+        candidates(emit)
+        return 0
     b = Bench(args.warmup, args.iters)
     b.gemm_shape = args.gemm_shape
     b.gdn_shape = args.gdn_shape

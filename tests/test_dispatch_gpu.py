@@ -65,6 +65,36 @@ def test_one_rank_equals_the_public_call(setup):
         d.close()
 
 
+def make_candidates(cfg, seed=12):
+    """A 128-token prefix and nine candidates of 3..70 tokens (the shape of the multi-candidate request)."""
+    rng = np.random.default_rng(seed)
+    prefix = rng.integers(0, cfg.vocab, 128).astype(np.int32)
+    return prefix, [rng.integers(0, cfg.vocab, int(t)).astype(np.int32) for t in rng.integers(3, 71, 9)]
+
+
+def test_candidates_on_one_rank_equal_the_one_shot_prompts(setup):
+    """s1_dispatch_candidates with one rank: every candidate's logits equal, bit for bit, those of
+    the whole prompt (prefix + candidate) run in one piece - whole-tile GEMMs make a row's bits
+    independent of what it is packed with and of where the prefix came from."""
+    from system1_omni_b200 import dispatch as D
+    from system1_omni_b200 import model as M
+    cfg, model = setup
+    prefix_ids, cands = make_candidates(cfg)
+    head = np.random.default_rng(2).normal(0, 1, (N_CLASSES, cfg.hidden)).astype(np.float32)
+    bias = np.linspace(1, -1, N_CLASSES).astype(np.float32)
+    d = D.Dispatcher(0, 1, 0)
+    prefix = model.capture_prefix(prefix_ids.tolist())
+    try:
+        got, rank_of = d.candidates(model, prefix, cands, head, bias)
+        assert np.all(rank_of == 0)
+        for i, c in enumerate(cands):
+            last = model.forward_batch([np.concatenate([prefix_ids, c])])[0]
+            assert np.array_equal(M.head_logits(head, last, bias).view(np.uint32), got[i].view(np.uint32)), i
+    finally:
+        prefix.close()
+        d.close()
+
+
 def test_many_queued_passes_keep_their_own_offsets(setup):
     """More passes than the executor's ring of pinned offset slots, alternating between two length
     vectors, queued without a wait in between: every pass must gather its own last rows."""
@@ -126,7 +156,7 @@ import os, sys
 import numpy as np
 sys.path.insert(0, {root!r}); sys.path.insert(0, os.path.join({root!r}, "tests"))
 from helpers import random_weights, tiny_config
-from test_dispatch_gpu import make_requests, N_CLASSES
+from test_dispatch_gpu import make_candidates, make_requests, N_CLASSES
 from system1_omni_b200 import dispatch as D, lib as L, model as M
 rank, world = int(sys.argv[1]), int(sys.argv[2])
 L.load(); L.set_device(rank)
@@ -142,10 +172,17 @@ for _ in range(3):
     out, us = d.run(head)
 assert d.max_over_ranks(rank) == world - 1
 assert np.array_equal(d.allgather([rank, 2.5]), [[r, 2.5] for r in range(world)])
+# the multi-candidate request: every rank captures the prefix, the candidates are shared out
+prefix_ids, cands = make_candidates(cfg)
+prefix = model.capture_prefix(prefix_ids.tolist())
+d.set_speed([1.0, 1.6][:world] if world == 2 else None)      # unequal on purpose: the faster rank takes more
+scores, where = d.candidates(model, prefix, cands, head)
 d.barrier()
 if rank == 0:
     np.save(sys.argv[4], out)
-d.close(); model.close()
+    np.save(sys.argv[4] + ".cand.npy", scores)
+    np.save(sys.argv[4] + ".where.npy", where)
+prefix.close(); d.close(); model.close()
 """
 
 
@@ -175,3 +212,13 @@ def test_two_ranks_equal_one_rank(setup, tmp_path):
             last = model.forward_batch([prompts[i] for i in reqs])
             for row, i in zip(last, reqs):
                 assert np.array_equal(M.head_logits(head, row).view(np.uint32), got[i].view(np.uint32)), i
+    # the multi-candidate request: both ranks took part (the faster one more), and every candidate's
+    # logits equal those of its whole prompt run on one GPU
+    scores, where = np.load(result + ".cand.npy"), np.load(result + ".where.npy")
+    prefix_ids, cands = make_candidates(cfg)
+    assert set(where.tolist()) == {0, 1}
+    tokens = np.array([len(c) for c in cands])
+    assert tokens[where == 1].sum() > tokens[where == 0].sum()
+    for i, c in enumerate(cands):
+        last = model.forward_batch([np.concatenate([prefix_ids, c])])[0]
+        assert np.array_equal(M.head_logits(head, last).view(np.uint32), scores[i].view(np.uint32)), i
