@@ -60,6 +60,17 @@ int s1_gdn_conv_gates(const void* qkv, int ld, const void* w, void* q, void* k, 
                       int value_dim, const void* b, const void* a, const void* A_log, const void* dt_bias, void* beta,
                       float* g, int H, void* stream);
 
+/* cs1_gdn_prefill_x for the sequences of one pack in one pair of launches (the reference calls it
+ * once per sequence, model.rs:690-712). Sequence i is rows [row0[i], row0[i] + len[i]) of the
+ * packed q, k, v, g, beta and o; nseq <= 16 (the pack limit of s1_batch_ranges), len[i] > 0. All
+ * sequences start from the same state s_in (nullable = zero: the candidates of one captured
+ * prefix share theirs) and sequence i leaves its state in s_out + i * H * 128 * 128 floats
+ * (nullable). The same bits as nseq calls. workspace_floats: what the workspace holds; it must be
+ * at least cs1_gdn_workspace_floats(64 * sum ceil(len[i] / 64), H). */
+int s1_gdn_prefill_batch(const void* q, const void* k, const void* v, const float* g, const void* beta, void* o,
+                         float* workspace, size_t workspace_floats, const int* row0, const int* len, int nseq, int H,
+                         int HK, float scale, const void* s_in, void* s_out, void* stream);
+
 /* The attention kernel's counterpart of s1_gemm_tc5_status: its device error word (0 = no bounded
  * wait ever gave up), read after waiting for all queued work, then cleared. */
 int s1_attn_tc5_status(int* code);

@@ -24,6 +24,9 @@
 
 namespace {
 
+constexpr int PACK_SEQS = 16;  // sequences of one pack (s1_batch_ranges); what the batched operators take per launch
+
+
 constexpr size_t ALIGN = 256;  // model.rs:23
 constexpr size_t BF16 = 2, F32 = 4;
 constexpr size_t GEMM_WORKSPACE = 32u << 20;  // model.rs:26
@@ -47,6 +50,7 @@ struct Tensor {
 struct Scratch {
     size_t cap = 0;
     void* buf = nullptr;
+    size_t ws_floats = 0;  // floats the delta rule's workspace holds
     size_t ids, res, x, delta, gdn_in, beta, g, lq, lk, lv, lo, ln, workspace, attn_in, aq, agate, ak, ao, gate_up,
         act, cos, sin, ends, last, status, total;
     char* at(size_t off) const { return static_cast<char*>(buf) + off; }
@@ -252,7 +256,9 @@ int make_scratch(Model* m, size_t cap) {
         next = (off + bytes + ALIGN - 1) / ALIGN * ALIGN;
         return off;
     };
-    const size_t ws_floats = cs1_gdn_workspace_floats((int)cap, (int)hv);
+    // every sequence of a pack rounds its own last chunk up: at most one more chunk per sequence
+    const size_t ws_floats = cs1_gdn_workspace_floats((int)cap + 64 * PACK_SEQS, (int)hv);
+    s.ws_floats = ws_floats;
     s.ids = take(cap * 4);
     s.res = take(cap * h * BF16);
     s.x = take(cap * h * BF16);
@@ -409,6 +415,31 @@ int conv_gates(Model* m, const Layer& ly, size_t off, int len) {
     return 0;
 }
 
+// The delta rule of every sequence of the pack in one pair of launches (the reference calls its
+// operator once per sequence, model.rs:690-712): sequence q owns lengths[q] packed rows of which
+// the first `lead` are skipped. s_in: the state all of them start from (null = zero); s_out: where
+// the state after the sequence goes (capture; one sequence then).
+int delta_rule(Model* m, const int* lengths, int nseq, int lead, const void* s_in, void* s_out) {
+    const Scratch& s = m->s;
+    const S1Config& c = m->cfg;
+    const int hv = c.lin_v_heads;
+    for (int first = 0, off = 0; first < nseq;) {  // a pack has at most PACK_SEQS sequences; callers of the layer loop may pass more
+        const int n = std::min(nseq - first, PACK_SEQS);
+        int row0[PACK_SEQS], len[PACK_SEQS];
+        for (int i = 0; i < n; i++) {
+            row0[i] = off + lead;
+            len[i] = lengths[first + i] - lead;
+            off += lengths[first + i];
+        }
+        S1_OP(S1_FAMILY_GDN, 2,
+              s1_gdn_prefill_batch(s.at(s.lq), s.at(s.lk), s.at(s.lv), reinterpret_cast<const float*>(s.at(s.g)), s.at(s.beta),
+                                   s.at(s.lo), reinterpret_cast<float*>(s.at(s.workspace)), s.ws_floats, row0, len, n, hv,
+                                   c.lin_k_heads, 1.0f / sqrtf(128.0f), s_in, s_out, m->stream));
+        first += n;
+    }
+    return 0;
+}
+
 // The layer loop (model.rs:1119-1338). Pointwise operators and the input / gate-up GEMMs run
 // once over the packed rows; conv, delta rule, attention prep and attention run per sequence.
 // dump (nullable, host) receives the residual stream after each layer.
@@ -438,7 +469,7 @@ int run(Model* m, const int* lengths, int nseq, char* dump) {
     int t = 0;
     for (int i = 0; i < nseq; i++) t += lengths[i];
     const OverlapScope overlap(m, t);
-    const int h = c.hidden, kd = m->key_dim(), vd = m->value_dim(), hv = c.lin_v_heads;
+    const int h = c.hidden, vd = m->value_dim(), hv = c.lin_v_heads;
     const int hq = c.heads, hk = c.kv_heads, hd = c.head_dim;
     const int gdn_in = m->gdn_in_w(), attn_in = m->attn_in_w(), attn_q = m->attn_q_w(), conv = m->conv_w();
     const float eps = c.eps;
@@ -453,17 +484,7 @@ int run(Model* m, const int* lengths, int nseq, char* dump) {
                 S1_TRY(conv_gates(m, ly, off, lengths[q]));
                 off += lengths[q];
             }
-            off = 0;
-            for (int q = 0; q < nseq; q++) {
-                S1_OP(S1_FAMILY_GDN, 2,
-                      cs1_gdn_prefill(s.at(s.lq + off * kd * BF16), s.at(s.lk + off * kd * BF16),
-                                      s.at(s.lv + off * vd * BF16),
-                                      reinterpret_cast<const float*>(s.at(s.g + off * hv * F32)),
-                                      s.at(s.beta + off * hv * BF16), s.at(s.lo + off * vd * BF16),
-                                      reinterpret_cast<float*>(s.at(s.workspace)), lengths[q], hv, c.lin_k_heads,
-                                      1.0f / sqrtf(128.0f), st));
-                off += lengths[q];
-            }
+            S1_TRY(delta_rule(m, lengths, nseq, 0, nullptr, nullptr));
             S1_OP(S1_FAMILY_GATED_NORM, 1,
                   cs1_gated_rms_norm(s.at(s.lo), s.at(z), gdn_in, m->w(ly.norm), s.at(s.ln), t, hv, 128, eps, st));
             S1_TRY(gemm_rows(m, s.ln, ly.out, s.delta, lengths, nseq, h, vd));
@@ -528,7 +549,7 @@ int run_window(Model* m, const int* lengths, int nseq, Prefix* capture, const Pr
     for (int i = 0; i < nseq; i++) t += lengths[i];
     const OverlapScope overlap(m, t);
     const int lead = prefix ? TAIL_ROWS : 0, qb = prefix ? prefix->len : 0;
-    const int h = c.hidden, kd = m->key_dim(), vd = m->value_dim(), hv = c.lin_v_heads;
+    const int h = c.hidden, vd = m->value_dim(), hv = c.lin_v_heads;
     const int hq = c.heads, hk = c.kv_heads, hd = c.head_dim;
     const int gdn_in = m->gdn_in_w(), attn_in = m->attn_in_w(), attn_q = m->attn_q_w(), conv = m->conv_w();
     const size_t kv_row = (size_t)hk * hd * BF16, tail_bytes = (size_t)TAIL_ROWS * gdn_in * BF16;
@@ -555,19 +576,8 @@ int run_window(Model* m, const int* lengths, int nseq, Prefix* capture, const Pr
             }
             // one convolution over the pack: a continuation's first token row sees its lead rows
             S1_TRY(conv_gates(m, ly, 0, t));
-            off = 0;
-            for (int q = 0; q < nseq; q++) {
-                const size_t r = off + lead;
-                S1_OP(S1_FAMILY_GDN, 2,
-                      cs1_gdn_prefill_x(s.at(s.lq + r * kd * BF16), s.at(s.lk + r * kd * BF16), s.at(s.lv + r * vd * BF16),
-                                        reinterpret_cast<const float*>(s.at(s.g + r * hv * F32)),
-                                        s.at(s.beta + r * hv * BF16), s.at(s.lo + r * vd * BF16),
-                                        reinterpret_cast<float*>(s.at(s.workspace)), lengths[q] - lead, hv,
-                                        c.lin_k_heads, 1.0f / sqrtf(128.0f),
-                                        prefix ? static_cast<const float*>(prefix->state[la]) : nullptr,
-                                        capture ? static_cast<float*>(capture->state[la]) : nullptr, st));
-                off += lengths[q];
-            }
+            S1_TRY(delta_rule(m, lengths, nseq, lead, prefix ? prefix->state[la] : nullptr,
+                              capture ? capture->state[la] : nullptr));
             S1_OP(S1_FAMILY_GATED_NORM, 1,
                   cs1_gated_rms_norm(s.at(s.lo), s.at(z), gdn_in, m->w(ly.norm), s.at(s.ln), t, hv, 128, eps, st));
             S1_TRY(gemm_rows(m, s.ln, ly.out, s.delta, lengths, nseq, h, vd));

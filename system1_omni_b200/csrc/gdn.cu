@@ -88,6 +88,15 @@ Work split(float* workspace, int T, int H) {
     return Work{b + l.wq, b + l.kd, b + l.p, b + l.u, reinterpret_cast<float*>(b + l.decay)};
 }
 
+// The sequences of one launch: a pack holds at most 16 (s1_batch_ranges). A sequence is rows
+// [row0, row0 + len) of the packed operands and chunks [chunk0, chunk0 + ceil(len / 64)) of every
+// head's run of workspace tiles (chunks chunks per head in all).
+constexpr int MAX_SEQS = 16;
+struct Seqs {
+    int n, chunks;
+    int row0[MAX_SEQS], len[MAX_SEQS], chunk0[MAX_SEQS];
+};
+
 __device__ int g_gdn_error = 0;  // a bounded wait gave up (read with s1_gdn_status / s1_device_status)
 
 __device__ __forceinline__ uint32_t to_tf32(float x) {
@@ -125,10 +134,18 @@ constexpr int PREP_TMEM_COLS = 256;              // pair products in columns [0,
 
 __global__ void __launch_bounds__(PREP_THREADS, 2)
     gdn_prep_tc5(const __grid_constant__ CUtensorMap map_v, const bf16* __restrict__ q, const bf16* __restrict__ k,
-                 const float* __restrict__ g, const bf16* __restrict__ beta, Work ws, int T, int H, int HK, int NC,
-                 float scale) {
+                 const float* __restrict__ g, const bf16* __restrict__ beta, Work ws, const __grid_constant__ Seqs seqs,
+                 int H, int HK, float scale) {
     using namespace tc5;
     grid_dep_trigger();
+    // blockIdx.z: the sequence; its rows start at row0 of the packed operands. Chunks past its end
+    // have nothing to do (the grid is as wide as the longest sequence).
+    const int T = seqs.len[blockIdx.z], row0 = seqs.row0[blockIdx.z], NC = seqs.chunks;
+    if ((int)blockIdx.x * C >= T) return;
+    q += (size_t)row0 * HK * D;
+    k += (size_t)row0 * HK * D;
+    g += (size_t)row0 * H;
+    beta += (size_t)row0 * H;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     float* A = reinterpret_cast<float*>(smem + T_A);
@@ -147,7 +164,7 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
     const int r0 = c * C;
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const int quarter = warp & 3;               // the 32 tensor-memory lanes this warp may touch
-    const size_t tile = (size_t)h * NC + c;     // this block's (head, chunk) tile in every workspace array
+    const size_t tile = (size_t)h * NC + seqs.chunk0[blockIdx.z] + c;  // this block's (head, chunk) tile in every workspace array
     if (tid == 0) {
         mbar_init(bar_s, 1);
         mbar_init(bar_v, 1);
@@ -274,7 +291,9 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
     // the operand tile is dead: v comes in over its end, two [64 rows, 64 columns] boxes
     if (tid == 0) {
         mbar_expect_tx(bar_v, 2 * U_BYTES);
-        for (int cb = 0; cb < 2; cb++) tma_load_2d(smem + T_VB + cb * U_BYTES, &map_v, h * D + cb * 64, r0, bar_v);
+        // rows past the sequence's end hold the next sequence's values (or zeros past the end of the
+        // buffer): beta is zero there, so T beta has zero columns for them
+        for (int cb = 0; cb < 2; cb++) tma_load_2d(smem + T_VB + cb * U_BYTES, &map_v, h * D + cb * 64, row0 + r0, bar_v);
     }
 
     // ---- decay masks: the warps of quarters 0-1 read k k^T -> A (float32, shared), those of
@@ -516,10 +535,15 @@ static_assert(S_STAGE % 1024 == 0 && S_KD % 1024 == 0 && S_PA % 1024 == 0 && S_U
 static_assert(SCAN_SMEM <= 227 * 1024, "the stages fit an SM");
 
 __global__ void __launch_bounds__(SCAN_THREADS, 1)
-    gdn_scan_tc5(Work ws, bf16* __restrict__ o, int T, int H, int NC, const float* __restrict__ s_in,
+    gdn_scan_tc5(Work ws, bf16* __restrict__ o, const __grid_constant__ Seqs seqs, int H, const float* __restrict__ s_in,
                  float* __restrict__ s_out) {
     using namespace tc5;
     grid_dep_trigger();
+    // blockIdx.z: the sequence. Every sequence starts from the same s_in (the candidates of one
+    // prefix) and leaves its state in its own slot of s_out.
+    const int T = seqs.len[blockIdx.z], NC = (T + C - 1) / C;
+    o += (size_t)seqs.row0[blockIdx.z] * H * D;
+    if (s_out) s_out += (size_t)blockIdx.z * H * D * D;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + S_BAR);  // [STAGES] a stage's tiles have landed
@@ -536,7 +560,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1)
     const int h = blockIdx.x, slice = blockIdx.y, v0 = slice * VS;
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const int quarter = warp & 3;  // the 32 tensor-memory lanes this warp may touch
-    const size_t tile0 = (size_t)h * NC;
+    const size_t tile0 = (size_t)h * seqs.chunks + seqs.chunk0[blockIdx.z];
 
     if (tid == 0) {
         for (int i = 0; i < STAGES; i++) mbar_init(&full[i], 1);
@@ -794,38 +818,63 @@ cudaError_t set_smem_once(F* kernel, int bytes, bool* done_per_device) {
     return e;
 }
 
-int gdn_run(const void* q, const void* k, const void* v, const float* g, const void* beta, void* o,
-            float* workspace, int T, int H, int HK, float scale, const void* s_in, void* s_out, void* stream) {
-    if (T < 0 || H <= 0 || HK <= 0 || H % HK != 0) return cudaErrorInvalidValue;
+// The sequences row0[i], len[i] (i < nseq <= 16) of the packed operands in one pair of launches.
+// workspace_bytes: what the caller has (0 = not checked: the single-sequence entry points size
+// it by their documented rule).
+int gdn_run_batch(const void* q, const void* k, const void* v, const float* g, const void* beta, void* o,
+                  float* workspace, size_t workspace_bytes, const int* row0, const int* len, int nseq, int H, int HK,
+                  float scale, const void* s_in, void* s_out, void* stream) {
+    if (nseq <= 0 || nseq > MAX_SEQS || !row0 || !len || H <= 0 || HK <= 0 || H % HK != 0) return cudaErrorInvalidValue;
     const float* si = static_cast<const float*>(s_in);
     float* so = static_cast<float*>(s_out);
     cudaStream_t st = as_stream(stream);
-    if (T == 0) {
-        // no tokens: the state passes through unchanged
-        if (so == nullptr) return cudaSuccess;
-        const size_t bytes = (size_t)H * D * D * sizeof(float);
-        return si != nullptr ? cudaMemcpyAsync(so, si, bytes, cudaMemcpyDeviceToDevice, st)
-                             : cudaMemsetAsync(so, 0, bytes, st);
-    }
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(workspace) || !aligned16(o) ||
         (si && !aligned16(si)) || (so && !aligned16(so)))
         return cudaErrorInvalidValue;
+    Seqs seqs{};
+    seqs.n = nseq;
+    int longest = 0;
+    long rows = 0;
+    for (int i = 0; i < nseq; i++) {
+        if (len[i] <= 0 || row0[i] < 0) return cudaErrorInvalidValue;
+        seqs.row0[i] = row0[i];
+        seqs.len[i] = len[i];
+        seqs.chunk0[i] = seqs.chunks;
+        seqs.chunks += (len[i] + C - 1) / C;
+        longest = std::max(longest, len[i]);
+        rows = std::max<long>(rows, (long)row0[i] + len[i]);
+    }
+    const Layout layout(seqs.chunks * C, H);
+    if (workspace_bytes != 0 && layout.total > workspace_bytes) return cudaErrorInvalidValue;
     static bool prep_done[64] = {}, scan_done[64] = {};
     cudaError_t e = set_smem_once(gdn_prep_tc5, PREP_SMEM, prep_done);
     if (e != cudaSuccess) return e;
     e = set_smem_once(gdn_scan_tc5, SCAN_SMEM, scan_done);
     if (e != cudaSuccess) return e;
-    const int NC = (T + C - 1) / C;
-    const Work ws = split(workspace, T, H);
-    CUtensorMap map_v;  // [64 rows, 64 columns] boxes, 128-byte swizzle
-    if (!tensor_map_2d(v, (uint64_t)T, (uint64_t)H * D, (uint64_t)H * D, C, &map_v)) return CS1_ERR_TENSOR_MAP;
-    e = launch_dep_family(DEP_GDN, gdn_prep_tc5, dim3(NC, H), PREP_THREADS, PREP_SMEM, st, map_v,
-                          static_cast<const bf16*>(q), static_cast<const bf16*>(k), g, static_cast<const bf16*>(beta), ws, T,
-                          H, HK, NC, scale);
+    const Work ws = split(workspace, seqs.chunks * C, H);
+    CUtensorMap map_v;  // [64 rows, 64 columns] boxes over all the packed rows, 128-byte swizzle
+    if (!tensor_map_2d(v, (uint64_t)rows, (uint64_t)H * D, (uint64_t)H * D, C, &map_v)) return CS1_ERR_TENSOR_MAP;
+    e = launch_dep_family(DEP_GDN, gdn_prep_tc5, dim3((longest + C - 1) / C, H, nseq), PREP_THREADS, PREP_SMEM, st, map_v,
+                          static_cast<const bf16*>(q), static_cast<const bf16*>(k), g, static_cast<const bf16*>(beta), ws, seqs,
+                          H, HK, scale);
     if (e != cudaSuccess) return e;
-    e = launch_dep_family(DEP_GDN, gdn_scan_tc5, dim3(H, D / VS), SCAN_THREADS, SCAN_SMEM, st, ws, static_cast<bf16*>(o), T, H,
-                          NC, si, so);
+    e = launch_dep_family(DEP_GDN, gdn_scan_tc5, dim3(H, D / VS, nseq), SCAN_THREADS, SCAN_SMEM, st, ws, static_cast<bf16*>(o),
+                          seqs, H, si, so);
     return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+int gdn_run(const void* q, const void* k, const void* v, const float* g, const void* beta, void* o,
+            float* workspace, int T, int H, int HK, float scale, const void* s_in, void* s_out, void* stream) {
+    if (T < 0 || H <= 0 || HK <= 0 || H % HK != 0) return cudaErrorInvalidValue;
+    if (T == 0) {
+        // no tokens: the state passes through unchanged
+        if (s_out == nullptr) return cudaSuccess;
+        const size_t bytes = (size_t)H * D * D * sizeof(float);
+        return s_in != nullptr ? cudaMemcpyAsync(s_out, s_in, bytes, cudaMemcpyDeviceToDevice, as_stream(stream))
+                               : cudaMemsetAsync(s_out, 0, bytes, as_stream(stream));
+    }
+    const int zero = 0;
+    return gdn_run_batch(q, k, v, g, beta, o, workspace, 0, &zero, &T, 1, H, HK, scale, s_in, s_out, stream);
 }
 
 }  // namespace
@@ -863,6 +912,20 @@ extern "C" int cs1_gdn_prefill_x(const void* q, const void* k, const void* v, co
                                  void* o, float* workspace, int T, int H, int HK, float scale, const void* s_in,
                                  void* s_out, void* stream) {
     return gdn_run(q, k, v, g, beta, o, workspace, T, H, HK, scale, s_in, s_out, stream);
+}
+
+// Several sequences of one pack in one pair of launches: sequence i is rows [row0[i], row0[i] +
+// len[i]) of the packed q, k, v, g, beta and o (nseq <= 16, the pack limit); all start from the
+// same state s_in (nullable: zero) - the candidates of one captured prefix - and sequence i
+// leaves its state in s_out + i H 128 128 (nullable). Bit for bit what nseq calls of
+// cs1_gdn_prefill_x compute. The workspace must hold cs1_gdn_workspace_floats(64 * chunks, H)
+// floats, chunks = sum of ceil(len[i] / 64); workspace_floats is what the caller has.
+extern "C" int s1_gdn_prefill_batch(const void* q, const void* k, const void* v, const float* g, const void* beta,
+                                    void* o, float* workspace, size_t workspace_floats, const int* row0, const int* len,
+                                    int nseq, int H, int HK, float scale, const void* s_in, void* s_out, void* stream) {
+    if (workspace_floats == 0) return cudaErrorInvalidValue;
+    return gdn_run_batch(q, k, v, g, beta, o, workspace, workspace_floats * sizeof(float), row0, len, nseq, H, HK, scale, s_in,
+                         s_out, stream);
 }
 
 // ---------------------------------------------------------------------------------------

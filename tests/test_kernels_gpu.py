@@ -502,6 +502,55 @@ def test_gdn_prefill_two_phase_matches_one_shot_bit_for_bit(cs1, stream):
         assert np.abs(s_full - s64).max() <= 2e-2 * np.abs(s64).max()
 
 
+@pytest.mark.parametrize("h,hk", [(4, 2), (48, 16)])
+def test_gdn_prefill_batch_equals_one_call_per_sequence(cs1, stream, h, hk):
+    """s1_gdn_prefill_batch over a pack (sequences of 1 to 700 tokens with unused rows between some
+    of them, as the lead rows of continuations leave) against cs1_gdn_prefill_x per sequence:
+    outputs and final states bit for bit, from a shared initial state and from none; the rows
+    between sequences stay untouched; sizes and counts beyond the limits are refused."""
+    lens = [37, 700, 1, 64, 129, 300, 5, 65]
+    gaps = [0, 3, 3, 0, 7, 0, 1, 3]
+    row0, at = [], 0
+    for n, gap in zip(lens, gaps):
+        at += gap
+        row0.append(at)
+        at += n
+    total = at + 2
+    q, k, v, g, beta = gdn_inputs(total, h, hk, 0.4, 1.0)
+    qa, ka, va, ga, ba = (x.reshape(total, -1) for x in (q, k, v, g, beta))
+    state = (np.random.default_rng(5).standard_normal((h, 128, 128)) * 0.05).astype(np.float32)
+    qd, kd, vd, gd, bd = dev(q, stream), dev(k, stream), dev(v, stream), dev(g, stream), dev(beta, stream)
+    chunks = sum(-(-n // 64) for n in lens)
+    floats = cs1.cs1_gdn_workspace_floats(64 * chunks, h)
+    ws = L.DeviceBuffer(floats * 4)
+    r0, ln = np.array(row0, np.int32), np.array(lens, np.int32)
+    for s_in in (None, state):
+        si = None if s_in is None else dev(s_in, stream)
+        o = dev(np.full((total, h * 128), 0x7FC0, np.uint16), stream)
+        so = L.DeviceBuffer(len(lens) * h * 128 * 128 * 4)
+        L.check(cs1.s1_gdn_prefill_batch(qd.at(), kd.at(), vd.at(), gd.at(), bd.at(), o.at(), ws.at(), floats,
+                                         r0.ctypes.data_as(C.c_void_p), ln.ctypes.data_as(C.c_void_p), len(lens), h, hk,
+                                         128 ** -0.5, None if si is None else si.at(), so.at(), stream.handle), "batch")
+        got = host(o, (total, h, 128), stream)
+        states = host(so, (len(lens), h, 128, 128), stream, np.float32)
+        assert L.gdn_status() == 0
+        covered = np.zeros(total, bool)
+        for i, (a, n) in enumerate(zip(row0, lens)):
+            want, s_want = run_gdn(cs1, stream, qa[a:a + n], ka[a:a + n], va[a:a + n], ga[a:a + n], ba[a:a + n], n, h, hk,
+                                   s_in=s_in, want_state=True)
+            assert np.array_equal(got[a:a + n], want), (i, n)
+            assert np.array_equal(states[i], s_want), (i, n)
+            covered[a:a + n] = True
+        assert np.all(got[~covered] == 0x7FC0)
+    args = (qd.at(), kd.at(), vd.at(), gd.at(), bd.at(), o.at(), ws.at())
+    tail = (h, hk, 128 ** -0.5, None, None, stream.handle)
+    many = np.ones(17, np.int32)
+    assert cs1.s1_gdn_prefill_batch(*args, floats, many.ctypes.data_as(C.c_void_p), many.ctypes.data_as(C.c_void_p), 17, *tail) != 0
+    assert cs1.s1_gdn_prefill_batch(*args, floats // 2, r0.ctypes.data_as(C.c_void_p), ln.ctypes.data_as(C.c_void_p), len(lens), *tail) != 0
+    zero = np.array([5, 0], np.int32)
+    assert cs1.s1_gdn_prefill_batch(*args, floats, r0.ctypes.data_as(C.c_void_p), zero.ctypes.data_as(C.c_void_p), 2, *tail) != 0
+
+
 def test_gdn_empty_window_captures_state_copy_and_zero_initial_state(cs1, stream):
     # kernels.rs:692-742: T = 0 copies (or zeroes) the state as a captured graph node
     st = stream.handle
