@@ -60,6 +60,24 @@ int s1_gdn_conv_gates(const void* qkv, int ld, const void* w, void* q, void* k, 
                       int value_dim, const void* b, const void* a, const void* A_log, const void* dt_bias, void* beta,
                       float* g, int H, void* stream);
 
+/* cs1_attn_prep for the sequences of one pack in one launch (the reference calls it once per
+ * sequence, model.rs:1244-1254): every pointer is that of packed row 0 and T counts the packed
+ * rows in all; sequence i is rows [row0[i], row0[i] + rows[i]) and its first row takes the first
+ * row of the tables (cos and sin point at the position the sequences start from). Rows outside
+ * every sequence are left as they are. nseq <= 16. The same bits as one call per sequence. */
+int s1_attn_prep_batch(const void* qg, const void* kr, int ld, const void* qw, const void* kw, const void* cos,
+                       const void* sin, void* q, void* gate, void* k, int T, const int* row0, const int* rows, int nseq,
+                       int Hq, int Hk, int Dh, int half, float eps, void* stream);
+
+/* s1_attention_gated_shared_prefix for the sequences of one pack in one launch: sequence i owns
+ * rows [row0[i], row0[i] + rows[i]) of q, gate, out, k and v and sits at positions
+ * [prefix_len, prefix_len + rows[i]) behind the shared prefix (prefix_len 0: none - the plain
+ * packed pass, where the reference calls cs1_attention_gated once per sequence,
+ * model.rs:1255-1268). nseq <= 16, rows[i] > 0. The same bits as one call per sequence. */
+int s1_attention_gated_batch(const void* q, const void* k, const void* v, int ldv, const void* gate, void* out,
+                             const void* k_prefix, const void* v_prefix, int ldv_prefix, int prefix_len, const int* row0,
+                             const int* rows, int nseq, int Hq, int Hk, int Dh, float scale, void* stream);
+
 /* cs1_gdn_prefill_x for the sequences of one pack in one pair of launches (the reference calls it
  * once per sequence, model.rs:690-712). Sequence i is rows [row0[i], row0[i] + len[i]) of the
  * packed q, k, v, g, beta and o; nseq <= 16 (the pack limit of s1_batch_ranges), len[i] > 0. All

@@ -266,14 +266,34 @@ __device__ __forceinline__ void softmax_rows(unsigned char* smem, uint64_t* bars
     }
 }
 
+// The sequences of one launch (a pack holds at most 16): sequence i has positions [0, T[i]) and its
+// own rows - positions from own_base on - start at row row0[i] of q, k, v, gate and out.
+constexpr int ATTN_MAX_SEQS = 16;
+struct AttnSeqs {
+    int n;
+    int row0[ATTN_MAX_SEQS], T[ATTN_MAX_SEQS];
+};
+
 template <int DH, bool GATED, bool CAUSAL>
 __global__ void __launch_bounds__(ATHREADS, ACfg<DH>::BLOCKS_PER_SM)
-    attn_tc5_kernel(const __grid_constant__ AttnMaps maps, const bf16* __restrict__ gate, bf16* __restrict__ out, int T,
-                    int Hq, int Hk, float scale_log2, int q_base, int own_base, int vec_ok) {
+    attn_tc5_kernel(const __grid_constant__ AttnMaps maps, const bf16* __restrict__ gate, bf16* __restrict__ out,
+                    const __grid_constant__ AttnSeqs seqs, int Hq, int Hk, float scale_log2, int q_base, int own_base,
+                    int vec_ok) {
     using namespace tc5;
     using G = ACfg<DH>;
     constexpr int BN = G::BN;
     grid_dep_trigger();
+    // Block index -> (query block, sequence, head), the heads and sequences of one query block next
+    // to each other and the last query block first: under a causal mask a block's work grows with
+    // its position, so the blocks are handed out longest first over the whole launch and its ragged
+    // end is made of the shortest blocks (the heads of a query block also share their keys in L2).
+    // The grid is as deep as the longest sequence: a block past its sequence's end has nothing to do.
+    const int per_q = seqs.n * Hq;
+    const int rest = blockIdx.x % per_q, sq = rest / Hq;
+    const int h = rest % Hq, hk = h / (Hq / Hk);
+    const int T = seqs.T[sq], row0 = seqs.row0[sq] - own_base;  // row of position p: row0 + p
+    const int q0 = q_base + (gridDim.x / per_q - 1 - blockIdx.x / per_q) * ABM;
+    if (q0 >= T) return;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);
@@ -290,13 +310,6 @@ __global__ void __launch_bounds__(ATHREADS, ACfg<DH>::BLOCKS_PER_SM)
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    // Block index -> (query block, head), the heads of one query block next to each other and the
-    // last query block first: under a causal mask a block's work grows with its position, so the
-    // blocks are handed out longest first over the whole launch and the ragged end of the launch
-    // is made of its shortest blocks (the heads of a query block also share their keys in L2).
-    const int nq = gridDim.x / Hq;
-    const int h = blockIdx.x % Hq, hk = h / (Hq / Hk);
-    const int q0 = q_base + (nq - 1 - blockIdx.x / Hq) * ABM;
     const int kv_end = CAUSAL ? min(T, q0 + ABM) : T;
     const int ntiles = (kv_end + BN - 1) / BN;
 
@@ -338,7 +351,7 @@ __global__ void __launch_bounds__(ATHREADS, ACfg<DH>::BLOCKS_PER_SM)
             if (issuer) {
                 mbar_expect_tx(q_full, G::Q_BYTES);
                 for (int c = 0; c < DH / 64; c++)
-                    tma_load_2d(smem + c * (ABM * 128), &maps.q, h * DH + c * 64, q0 - own_base, q_full);
+                    tma_load_2d(smem + c * (ABM * 128), &maps.q, h * DH + c * 64, row0 + q0, q_full);
             }
             for (int j = 0; j < ntiles; j++) {
                 const int stage = j & 1;
@@ -356,7 +369,7 @@ __global__ void __launch_bounds__(ATHREADS, ACfg<DH>::BLOCKS_PER_SM)
                         if (r0 < own_base)
                             tma_load_2d(dst, &maps.kpre, hk * DH + c * 64, r0, &k_full[stage]);
                         else
-                            tma_load_2d(dst, &maps.k, hk * DH + c * 64, r0 - own_base, &k_full[stage]);
+                            tma_load_2d(dst, &maps.k, hk * DH + c * 64, row0 + r0, &k_full[stage]);
                     }
                 if (!mbar_wait(&v_empty[stage], parity, abort_flag)) {
                     fail(22);
@@ -370,7 +383,7 @@ __global__ void __launch_bounds__(ATHREADS, ACfg<DH>::BLOCKS_PER_SM)
                         if (r0 < own_base)
                             tma_load_2d(dst, &maps.vpre, hk * DH + c * 64, r0, &v_full[stage]);
                         else
-                            tma_load_2d(dst, &maps.v, hk * DH + c * 64, r0 - own_base, &v_full[stage]);
+                            tma_load_2d(dst, &maps.v, hk * DH + c * 64, row0 + r0, &v_full[stage]);
                     }
             }
         }
@@ -438,7 +451,7 @@ __global__ void __launch_bounds__(ATHREADS, ACfg<DH>::BLOCKS_PER_SM)
         }
         __syncwarp();
     } else {
-        softmax_rows<DH, GATED, CAUSAL>(smem, bars, tmem_base, abort_flag, gate, out, T, Hq, h, q0, own_base, ntiles, scale_log2,
+        softmax_rows<DH, GATED, CAUSAL>(smem, bars, tmem_base, abort_flag, gate, out, T, Hq, h, q0, -row0, ntiles, scale_log2,
                                 vec_ok, warp, lane);
     }
 
@@ -451,8 +464,8 @@ __global__ void __launch_bounds__(ATHREADS, ACfg<DH>::BLOCKS_PER_SM)
 }
 
 template <int DH, bool GATED, bool CAUSAL = true>
-int launch_attn(const AttnMaps& maps, const bf16* gate, bf16* out, int T, int Hq, int Hk, float scale, int q_base,
-                int own_base, cudaStream_t st) {
+int launch_attn(const AttnMaps& maps, const bf16* gate, bf16* out, const AttnSeqs& seqs, int Hq, int Hk, float scale,
+                int q_base, int own_base, cudaStream_t st) {
     using G = ACfg<DH>;
     static bool configured[64] = {};
     int dev = 0;
@@ -465,9 +478,11 @@ int launch_attn(const AttnMaps& maps, const bf16* gate, bf16* out, int T, int Hq
         configured[dev] = true;
     }
     constexpr float LOG2E = 1.4426950408889634f;
-    const dim3 grid(((T - q_base + ABM - 1) / ABM) * Hq);
+    int longest = 0;
+    for (int i = 0; i < seqs.n; i++) longest = max(longest, seqs.T[i]);
+    const dim3 grid(((longest - q_base + ABM - 1) / ABM) * seqs.n * Hq);
     const int vec_ok = aligned16(out) && (!GATED || aligned16(gate));
-    return launch_dep_family(DEP_ATTENTION, attn_tc5_kernel<DH, GATED, CAUSAL>, grid, ATHREADS, G::SMEM, st, maps, gate, out, T, Hq, Hk, scale * LOG2E,
+    return launch_dep_family(DEP_ATTENTION, attn_tc5_kernel<DH, GATED, CAUSAL>, grid, ATHREADS, G::SMEM, st, maps, gate, out, seqs, Hq, Hk, scale * LOG2E,
                       q_base, own_base, vec_ok);
 }
 
@@ -476,10 +491,19 @@ int launch_attn(const AttnMaps& maps, const bf16* gate, bf16* out, int T, int Hq
 
 using namespace s1;
 
-int s1_attn_tc5(const bf16* q, const bf16* k, const bf16* v, int ldv, const bf16* gate, bf16* out, int T, int Hq, int Hk,
-                int Dh, float scale, int q_base, const bf16* kpre, const bf16* vpre, int ldvpre, int own_base,
-                cudaStream_t st) {
-    const uint64_t own_rows = (uint64_t)(T - own_base);
+int s1_attn_tc5_batch(const bf16* q, const bf16* k, const bf16* v, int ldv, const bf16* gate, bf16* out, const int* row0,
+                      const int* T, int nseq, int Hq, int Hk, int Dh, float scale, int q_base, const bf16* kpre,
+                      const bf16* vpre, int ldvpre, int own_base, cudaStream_t st) {
+    if (nseq <= 0 || nseq > ATTN_MAX_SEQS) return cudaErrorInvalidValue;
+    AttnSeqs seqs{};
+    seqs.n = nseq;
+    uint64_t own_rows = 0;  // rows of q, k, v that the launch may address
+    for (int i = 0; i < nseq; i++) {
+        if (row0[i] < 0 || T[i] <= q_base) return cudaErrorInvalidValue;
+        seqs.row0[i] = row0[i];
+        seqs.T[i] = T[i];
+        own_rows = std::max<uint64_t>(own_rows, (uint64_t)row0[i] + (uint64_t)(T[i] - own_base));
+    }
     AttnMaps maps;
     if (!tensor_map_2d(q, own_rows, (uint64_t)Hq * Dh, (uint64_t)Hq * Dh, ABM, &maps.q) ||
         !tensor_map_2d(k, own_rows, (uint64_t)Hk * Dh, (uint64_t)Hk * Dh, 64, &maps.k) ||
@@ -494,10 +518,17 @@ int s1_attn_tc5(const bf16* q, const bf16* k, const bf16* v, int ldv, const bf16
         maps.vpre = maps.v;
     }
     if (Dh == 256)
-        return gate ? launch_attn<256, true>(maps, gate, out, T, Hq, Hk, scale, q_base, own_base, st)
-                    : launch_attn<256, false>(maps, gate, out, T, Hq, Hk, scale, q_base, own_base, st);
-    return gate ? launch_attn<128, true>(maps, gate, out, T, Hq, Hk, scale, q_base, own_base, st)
-                : launch_attn<128, false>(maps, gate, out, T, Hq, Hk, scale, q_base, own_base, st);
+        return gate ? launch_attn<256, true>(maps, gate, out, seqs, Hq, Hk, scale, q_base, own_base, st)
+                    : launch_attn<256, false>(maps, gate, out, seqs, Hq, Hk, scale, q_base, own_base, st);
+    return gate ? launch_attn<128, true>(maps, gate, out, seqs, Hq, Hk, scale, q_base, own_base, st)
+                : launch_attn<128, false>(maps, gate, out, seqs, Hq, Hk, scale, q_base, own_base, st);
+}
+
+int s1_attn_tc5(const bf16* q, const bf16* k, const bf16* v, int ldv, const bf16* gate, bf16* out, int T, int Hq, int Hk,
+                int Dh, float scale, int q_base, const bf16* kpre, const bf16* vpre, int ldvpre, int own_base,
+                cudaStream_t st) {
+    const int zero = 0;
+    return s1_attn_tc5_batch(q, k, v, ldv, gate, out, &zero, &T, 1, Hq, Hk, Dh, scale, q_base, kpre, vpre, ldvpre, own_base, st);
 }
 
 // Non-causal attention over all n positions, head dim 64, as many key-value heads as query heads
@@ -511,7 +542,10 @@ int s1_attn_tc5_full64(const bf16* q, const bf16* k, const bf16* v, int ldv, bf1
         return CS1_ERR_TENSOR_MAP;
     maps.kpre = maps.k;
     maps.vpre = maps.v;
-    return launch_attn<64, false, false>(maps, nullptr, out, n, heads, heads, scale, 0, 0, st);
+    AttnSeqs seqs{};
+    seqs.n = 1;
+    seqs.T[0] = n;
+    return launch_attn<64, false, false>(maps, nullptr, out, seqs, heads, heads, scale, 0, 0, st);
 }
 
 // The device error word of the attention kernel on the current device (0 = no bounded wait ever

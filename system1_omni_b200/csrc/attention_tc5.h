@@ -10,6 +10,13 @@
 int s1_attn_tc5(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v, int ldv,
                 const __nv_bfloat16* gate, __nv_bfloat16* out, int T, int Hq, int Hk, int Dh, float scale, int q_base,
                 const __nv_bfloat16* kpre, const __nv_bfloat16* vpre, int ldvpre, int own_base, cudaStream_t stream);
+// The same for nseq <= 16 sequences in one launch: sequence i has positions [0, T[i]), T[i] > q_base, and its own
+// rows (positions from own_base on) start at row row0[i] of q, k, v, gate and out; the prefix below own_base
+// (kpre, vpre) is shared by all of them. The same bits as one call per sequence.
+int s1_attn_tc5_batch(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v, int ldv,
+                      const __nv_bfloat16* gate, __nv_bfloat16* out, const int* row0, const int* T, int nseq, int Hq, int Hk,
+                      int Dh, float scale, int q_base, const __nv_bfloat16* kpre, const __nv_bfloat16* vpre, int ldvpre,
+                      int own_base, cudaStream_t stream);
 // Non-causal attention over all n positions with head dim 64 and heads == key-value heads (the
 // vision tower): q, k, out [n, heads, 64], v rows ldv elements apart. Same return codes.
 int s1_attn_tc5_full64(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v, int ldv,

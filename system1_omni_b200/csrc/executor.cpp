@@ -440,6 +440,44 @@ int delta_rule(Model* m, const int* lengths, int nseq, int lead, const void* s_i
     return 0;
 }
 
+// Norm, rotary and gate split, then gated causal attention, of every sequence of the pack in one
+// launch each (the reference calls both operators once per sequence, model.rs:1244-1268). Sequence
+// q owns lengths[q] of the t packed rows, the first `lead` of them skipped, and sits at positions
+// from qb on behind the shared prefix k_pre / v_pre (null: none). keep_k / keep_v (capture; one
+// sequence then): where the keys after norm and rotary and the values as projected are copied to.
+int attention_pack(Model* m, const Layer& ly, const int* lengths, int nseq, int t, int lead, int qb, const void* k_pre,
+                   const void* v_pre, void* keep_k, void* keep_v) {
+    const Scratch& s = m->s;
+    const S1Config& c = m->cfg;
+    void* st = m->stream;
+    const int hq = c.heads, hk = c.kv_heads, hd = c.head_dim, attn_in = m->attn_in_w(), attn_q = m->attn_q_w();
+    const size_t kv_row = (size_t)hk * hd * BF16;
+    const size_t k = s.attn_in + (size_t)attn_q * BF16, v = k + kv_row;
+    for (int first = 0, off = 0; first < nseq;) {
+        const int n = std::min(nseq - first, PACK_SEQS);
+        int row0[PACK_SEQS], rows[PACK_SEQS];
+        for (int i = 0; i < n; i++) {
+            row0[i] = off + lead;
+            rows[i] = lengths[first + i] - lead;
+            off += lengths[first + i];
+        }
+        // the tables from position qb on: every sequence restarts there (model.rs:1244-1251)
+        S1_OP(S1_FAMILY_ATTN_PREP, 1,
+              s1_attn_prep_batch(s.at(s.attn_in), s.at(k), attn_in, m->w(ly.q_norm), m->w(ly.k_norm),
+                                 s.at(s.cos + (size_t)qb * c.rotary_half * BF16), s.at(s.sin + (size_t)qb * c.rotary_half * BF16),
+                                 s.at(s.aq), s.at(s.agate), s.at(s.ak), t, row0, rows, n, hq, hk, hd, c.rotary_half, c.eps, st));
+        if (keep_k) {
+            S1_TRY(cs1_copy_dd(keep_k, s.at(s.ak + (size_t)row0[0] * kv_row), (size_t)rows[0] * kv_row, st));
+            S1_TRY(cs1_copy2d(keep_v, kv_row, s.at(v + (size_t)row0[0] * attn_in * BF16), (size_t)attn_in * BF16, kv_row, rows[0], st));
+        }
+        S1_OP(S1_FAMILY_ATTENTION, 1,
+              s1_attention_gated_batch(s.at(s.aq), s.at(s.ak), s.at(v), attn_in, s.at(s.agate), s.at(s.ao), k_pre, v_pre, hk * hd,
+                                       qb, row0, rows, n, hq, hk, hd, 1.0f / sqrtf((float)hd), st));
+        first += n;
+    }
+    return 0;
+}
+
 // The layer loop (model.rs:1119-1338). Pointwise operators and the input / gate-up GEMMs run
 // once over the packed rows; conv, delta rule, attention prep and attention run per sequence.
 // dump (nullable, host) receives the residual stream after each layer.
@@ -470,8 +508,8 @@ int run(Model* m, const int* lengths, int nseq, char* dump) {
     for (int i = 0; i < nseq; i++) t += lengths[i];
     const OverlapScope overlap(m, t);
     const int h = c.hidden, vd = m->value_dim(), hv = c.lin_v_heads;
-    const int hq = c.heads, hk = c.kv_heads, hd = c.head_dim;
-    const int gdn_in = m->gdn_in_w(), attn_in = m->attn_in_w(), attn_q = m->attn_q_w(), conv = m->conv_w();
+    const int hq = c.heads, hd = c.head_dim;
+    const int gdn_in = m->gdn_in_w(), attn_in = m->attn_in_w(), conv = m->conv_w();
     const float eps = c.eps;
     S1_OP(S1_FAMILY_NORM, 1, cs1_rms_norm(s.at(s.res), m->w(m->layers[0].input_norm), s.at(s.x), t, h, eps, st));
     for (size_t li = 0; li < m->layers.size(); li++) {
@@ -490,24 +528,7 @@ int run(Model* m, const int* lengths, int nseq, char* dump) {
             S1_TRY(gemm_rows(m, s.ln, ly.out, s.delta, lengths, nseq, h, vd));
         } else {
             S1_TRY(gemm(m, s.x, ly.qkv, s.attn_in, t, attn_in, h));
-            const size_t k = s.attn_in + (size_t)attn_q * BF16;
-            const size_t v = k + (size_t)hk * hd * BF16;
-            size_t off = 0;
-            for (int q = 0; q < nseq; q++) {
-                // the unshifted table base restarts positions at 0 for every sequence (model.rs:1244-1251)
-                S1_OP(S1_FAMILY_ATTN_PREP, 1,
-                      cs1_attn_prep(s.at(s.attn_in + off * attn_in * BF16), s.at(k + off * attn_in * BF16), attn_in,
-                                    m->w(ly.q_norm), m->w(ly.k_norm), s.at(s.cos), s.at(s.sin),
-                                    s.at(s.aq + off * hq * hd * BF16), s.at(s.agate + off * hq * hd * BF16),
-                                    s.at(s.ak + off * hk * hd * BF16), lengths[q], hq, hk, hd, c.rotary_half, eps,
-                                    st));
-                S1_OP(S1_FAMILY_ATTENTION, 1,
-                      cs1_attention_gated(s.at(s.aq + off * hq * hd * BF16), s.at(s.ak + off * hk * hd * BF16),
-                                          s.at(v + off * attn_in * BF16), attn_in,
-                                          s.at(s.agate + off * hq * hd * BF16), s.at(s.ao + off * hq * hd * BF16),
-                                          lengths[q], hq, hk, hd, 1.0f / sqrtf((float)hd), st));
-                off += lengths[q];
-            }
+            S1_TRY(attention_pack(m, ly, lengths, nseq, t, 0, 0, nullptr, nullptr, nullptr, nullptr));
             S1_TRY(gemm_rows(m, s.ao, ly.o, s.delta, lengths, nseq, h, hq * hd));
         }
         S1_TRY(mlp_block(m, li, lengths, nseq, t));
@@ -550,9 +571,9 @@ int run_window(Model* m, const int* lengths, int nseq, Prefix* capture, const Pr
     const OverlapScope overlap(m, t);
     const int lead = prefix ? TAIL_ROWS : 0, qb = prefix ? prefix->len : 0;
     const int h = c.hidden, vd = m->value_dim(), hv = c.lin_v_heads;
-    const int hq = c.heads, hk = c.kv_heads, hd = c.head_dim;
-    const int gdn_in = m->gdn_in_w(), attn_in = m->attn_in_w(), attn_q = m->attn_q_w(), conv = m->conv_w();
-    const size_t kv_row = (size_t)hk * hd * BF16, tail_bytes = (size_t)TAIL_ROWS * gdn_in * BF16;
+    const int hq = c.heads, hd = c.head_dim;
+    const int gdn_in = m->gdn_in_w(), attn_in = m->attn_in_w(), conv = m->conv_w();
+    const size_t tail_bytes = (size_t)TAIL_ROWS * gdn_in * BF16;
     const float eps = c.eps;
     if (prefix) {
         // the lead rows skip the per-sequence operators; give what those would have written a value
@@ -569,10 +590,21 @@ int run_window(Model* m, const int* lengths, int nseq, Prefix* capture, const Pr
             if (capture)
                 S1_TRY(cs1_copy_dd(capture->tail[la], s.at(s.gdn_in + (size_t)(t - TAIL_ROWS) * gdn_in * BF16), tail_bytes,
                                    st));
-            size_t off = 0;
-            for (int q = 0; prefix && q < nseq; q++) {
-                S1_TRY(cs1_copy_dd(s.at(s.gdn_in + off * gdn_in * BF16), prefix->tail[la], tail_bytes, st));
-                off += lengths[q];
+            for (int first = 0, off = 0; prefix && first < nseq;) {  // the prefix's conv tail in front of every continuation
+                const int n = std::min(nseq - first, PACK_SEQS);
+                int row0[PACK_SEQS];
+                for (int i = 0; i < n; i++) {
+                    row0[i] = off;
+                    off += lengths[first + i];
+                }
+                if (gdn_in % 8 == 0) {
+                    S1_TRY(s1::spread_block(s.at(s.gdn_in), (size_t)gdn_in * BF16 / 16, row0, n, prefix->tail[la], tail_bytes / 16,
+                                            static_cast<cudaStream_t>(st)));
+                } else {
+                    for (int i = 0; i < n; i++)
+                        S1_TRY(cs1_copy_dd(s.at(s.gdn_in + (size_t)row0[i] * gdn_in * BF16), prefix->tail[la], tail_bytes, st));
+                }
+                first += n;
             }
             // one convolution over the pack: a continuation's first token row sees its lead rows
             S1_TRY(conv_gates(m, ly, 0, t));
@@ -584,32 +616,9 @@ int run_window(Model* m, const int* lengths, int nseq, Prefix* capture, const Pr
             la++;
         } else {
             S1_TRY(gemm(m, s.x, ly.qkv, s.attn_in, t, attn_in, h));
-            const size_t k = s.attn_in + (size_t)attn_q * BF16;
-            const size_t v = k + kv_row;
-            size_t off = 0;
-            for (int q = 0; q < nseq; q++) {
-                const size_t r = off + lead;
-                const int rows = lengths[q] - lead;
-                // rotary tables from position qb on
-                S1_OP(S1_FAMILY_ATTN_PREP, 1,
-                      cs1_attn_prep(s.at(s.attn_in + r * attn_in * BF16), s.at(k + r * attn_in * BF16), attn_in,
-                                    m->w(ly.q_norm), m->w(ly.k_norm), s.at(s.cos + (size_t)qb * c.rotary_half * BF16),
-                                    s.at(s.sin + (size_t)qb * c.rotary_half * BF16), s.at(s.aq + r * hq * hd * BF16),
-                                    s.at(s.agate + r * hq * hd * BF16), s.at(s.ak + r * kv_row), rows, hq, hk, hd,
-                                    c.rotary_half, eps, st));
-                if (capture) {
-                    // keys after norm and rotary; values as projected
-                    S1_TRY(cs1_copy_dd(capture->k[fa], s.at(s.ak), (size_t)rows * kv_row, st));
-                    S1_TRY(cs1_copy2d(capture->v[fa], kv_row, s.at(v), (size_t)attn_in * BF16, kv_row, rows, st));
-                }
-                S1_OP(S1_FAMILY_ATTENTION, 1,
-                      s1_attention_gated_shared_prefix(
-                          s.at(s.aq + r * hq * hd * BF16), s.at(s.ak + r * kv_row), s.at(v + r * attn_in * BF16), attn_in,
-                          s.at(s.agate + r * hq * hd * BF16), s.at(s.ao + r * hq * hd * BF16),
-                          prefix ? prefix->k[fa] : nullptr, prefix ? prefix->v[fa] : nullptr, hk * hd, qb, rows, hq, hk,
-                          hd, 1.0f / sqrtf((float)hd), st));
-                off += lengths[q];
-            }
+            S1_TRY(attention_pack(m, ly, lengths, nseq, t, lead, qb, prefix ? prefix->k[fa] : nullptr,
+                                  prefix ? prefix->v[fa] : nullptr, capture ? capture->k[fa] : nullptr,
+                                  capture ? capture->v[fa] : nullptr));
             S1_TRY(gemm_rows(m, s.ao, ly.o, s.delta, lengths, nseq, h, hq * hd));
             fa++;
         }

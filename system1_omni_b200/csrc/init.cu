@@ -39,6 +39,17 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ x, const int* __res
     for (int i = threadIdx.x; i < packs; i += blockDim.x) out[dst + i] = x[src + i];
 }
 
+struct SpreadRows {
+    int row0[16];
+};
+__global__ void spread_block_kernel(uint4* __restrict__ dst, size_t row_packs, const __grid_constant__ SpreadRows rows,
+                                    const uint4* __restrict__ src, size_t packs) {
+    grid_dep_trigger();
+    grid_dep_sync();
+    uint4* out = dst + (size_t)rows.row0[blockIdx.y] * row_packs;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < packs; i += (size_t)gridDim.x * blockDim.x) out[i] = src[i];
+}
+
 __global__ void collect_status_kernel(const int* a, const int* b, const int* c, int* out) {
     out[0] = *a;
     out[1] = *b;
@@ -79,6 +90,15 @@ int gather_rows(const void* x, const int* ends_device, void* out, int nseq, int 
     if (nseq == 0) return 0;
     gather_rows_kernel<<<nseq, 128, 0, st>>>(static_cast<const uint4*>(x), ends_device, static_cast<uint4*>(out),
                                              D / 8);
+    return cudaGetLastError();
+}
+
+int spread_block(void* dst, size_t row_packs, const int* row0, int n, const void* src, size_t packs, cudaStream_t st) {
+    if (n <= 0 || n > 16 || packs == 0) return n == 0 || packs == 0 ? 0 : (int)cudaErrorInvalidValue;
+    SpreadRows rows{};
+    for (int i = 0; i < n; i++) rows.row0[i] = row0[i];
+    const unsigned bx = (unsigned)std::min<size_t>((packs + 255) / 256, 64);
+    spread_block_kernel<<<dim3(bx, n), 256, 0, st>>>(static_cast<uint4*>(dst), row_packs, rows, static_cast<const uint4*>(src), packs);
     return cudaGetLastError();
 }
 

@@ -424,6 +424,69 @@ def test_windowed_attention_matches_full_pass_bit_for_bit(cs1, stream, dh):
                                               0.0625, 32, stream.handle) != 0
 
 
+@pytest.mark.parametrize("dh", [256, 128])
+@pytest.mark.parametrize("prefix_len", [0, 192])
+def test_batched_attention_equals_one_call_per_sequence(cs1, stream, dh, prefix_len):
+    """s1_attn_prep_batch + s1_attention_gated_batch over a pack (1 to 300 rows per sequence, unused
+    rows between some) against cs1_attn_prep + s1_attention_gated_shared_prefix per sequence: the
+    same bits in q, gate, k and the output; rows outside every sequence stay untouched."""
+    hq, hk, half = 8, 2, 32
+    lens = [5, 300, 1, 128, 129, 64, 77]
+    gaps = [0, 3, 3, 0, 2, 0, 3]
+    row0, at = [], 0
+    for n, gap in zip(lens, gaps):
+        at += gap
+        row0.append(at)
+        at += n
+    total = at + 1
+    attn_q = hq * dh * 2
+    ld = attn_q + 2 * hk * dh
+    x = O.random_bf16(total * ld, 61, 1.5)
+    qw, kw = O.random_bf16(dh, 62, 0.3), O.random_bf16(dh, 63, 0.3)
+    cos, sin = O.rotary_tables(np.arange(prefix_len + max(lens)), half, 1e7)
+    kpre = O.random_bf16(max(prefix_len, 1) * hk * dh, 64, 1.0)
+    vpre = O.random_bf16(max(prefix_len, 1) * hk * dh, 65, 1.0)
+    xd, qwd, kwd, cd, sd, kpd, vpd = (dev(a, stream) for a in (x, qw, kw, cos, sin, kpre, vpre))
+    tab = prefix_len * half * 2     # byte offset of the first position's table row
+    scale = dh ** -0.5
+    r0, ln = np.array(row0, np.int32), np.array(lens, np.int32)
+
+    def buffers():
+        fill = np.full(total * hq * dh, 0x7FC0, np.uint16)
+        return dev(fill, stream), dev(fill, stream), dev(fill[: total * hk * dh], stream), dev(fill, stream)
+
+    q1, g1, k1, o1 = buffers()
+    L.check(cs1.s1_attn_prep_batch(xd.at(), xd.at(attn_q * 2), ld, qwd.at(), kwd.at(), cd.at(tab), sd.at(tab), q1.at(), g1.at(),
+                                   k1.at(), total, r0.ctypes.data_as(C.c_void_p), ln.ctypes.data_as(C.c_void_p), len(lens), hq, hk,
+                                   dh, half, EPS, stream.handle), "prep batch")
+    L.check(cs1.s1_attention_gated_batch(q1.at(), k1.at(), xd.at((attn_q + hk * dh) * 2), ld, g1.at(), o1.at(),
+                                         kpd.at() if prefix_len else None, vpd.at() if prefix_len else None, hk * dh, prefix_len,
+                                         r0.ctypes.data_as(C.c_void_p), ln.ctypes.data_as(C.c_void_p), len(lens), hq, hk, dh,
+                                         scale, stream.handle), "attention batch")
+    q2, g2, k2, o2 = buffers()
+    for a, n in zip(row0, lens):
+        L.check(cs1.cs1_attn_prep(xd.at(a * ld * 2), xd.at((a * ld + attn_q) * 2), ld, qwd.at(), kwd.at(), cd.at(tab), sd.at(tab),
+                                  q2.at(a * hq * dh * 2), g2.at(a * hq * dh * 2), k2.at(a * hk * dh * 2), n, hq, hk, dh, half, EPS,
+                                  stream.handle), "prep")
+        L.check(cs1.s1_attention_gated_shared_prefix(q2.at(a * hq * dh * 2), k2.at(a * hk * dh * 2),
+                                                     xd.at((a * ld + attn_q + hk * dh) * 2), ld, g2.at(a * hq * dh * 2),
+                                                     o2.at(a * hq * dh * 2), kpd.at() if prefix_len else None,
+                                                     vpd.at() if prefix_len else None, hk * dh, prefix_len, n, hq, hk, dh, scale,
+                                                     stream.handle), "attention")
+    assert L.attn_status() == 0
+    for got, want, width in ((q1, q2, hq * dh), (g1, g2, hq * dh), (k1, k2, hk * dh), (o1, o2, hq * dh)):
+        assert np.array_equal(host(got, (total, width), stream), host(want, (total, width), stream))
+    covered = np.zeros(total, bool)
+    for a, n in zip(row0, lens):
+        covered[a:a + n] = True
+    assert np.all(host(o1, (total, hq * dh), stream)[~covered] == 0x7FC0)
+    assert np.all(host(q1, (total, hq * dh), stream)[~covered] == 0x7FC0)
+    many = np.ones(17, np.int32)
+    assert cs1.s1_attention_gated_batch(q1.at(), k1.at(), xd.at(), ld, g1.at(), o1.at(), None, None, hk * dh, 0,
+                                        many.ctypes.data_as(C.c_void_p), many.ctypes.data_as(C.c_void_p), 17, hq, hk, dh, scale,
+                                        stream.handle) != 0
+
+
 # ---------------------------------------------------------------- gated delta rule
 
 def run_gdn(cs1, stream, q, k, v, g, beta, t, h, hk, s_in=None, want_state=False, t_ws=None):
