@@ -89,6 +89,14 @@ int s1_gdn_prefill_batch(const void* q, const void* k, const void* v, const floa
                          float* workspace, size_t workspace_floats, const int* row0, const int* len, int nseq, int H,
                          int HK, float scale, const void* s_in, void* s_out, void* stream);
 
+/* s1_gdn_conv_gates for the sequences of one pack in one launch: every pointer is that of packed
+ * row 0 (b and a: the two gate columns of row 0); sequence i is rows [row0[i], row0[i] + len[i]) and
+ * its convolution sees zeros before its first row. nseq <= 16, len[i] > 0. The same bits as one
+ * call per sequence, CS1_ERR_UNSUPPORTED under the same conditions. */
+int s1_gdn_conv_gates_batch(const void* qkv, int ld, const void* w, void* q, void* k, void* v, const int* row0,
+                            const int* len, int nseq, int key_dim, int value_dim, const void* b, const void* a,
+                            const void* A_log, const void* dt_bias, void* beta, float* g, int H, void* stream);
+
 /* The attention kernel's counterpart of s1_gemm_tc5_status: its device error word (0 = no bounded
  * wait ever gave up), read after waiting for all queued work, then cleared. */
 int s1_attn_tc5_status(int* code);

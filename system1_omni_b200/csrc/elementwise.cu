@@ -179,6 +179,34 @@ __global__ void __launch_bounds__(CONV_THREADS)
     for (int i = first + (int)threadIdx.x; i < end; i += CONV_THREADS) gate_element(b, a, ld, A_log, dt_bias, beta, g, i, H);
 }
 
+// The same for the sequences of a pack (blockIdx.z): sequence i is rows [row0[i], row0[i] + len[i])
+// of every operand; the convolution of a sequence's first rows sees zeros before it, not the
+// sequence packed in front of it.
+struct ConvSeqs {
+    int row0[16], len[16];
+};
+template <int TT>
+__global__ void __launch_bounds__(CONV_THREADS)
+    gdn_conv_gates_batch_kernel(const bf16* __restrict__ qkv, int ld, const bf16* __restrict__ w, bf16* __restrict__ q,
+                                bf16* __restrict__ k, bf16* __restrict__ v, const __grid_constant__ ConvSeqs seqs, int key_dim,
+                                int value_dim, int conv_blocks, const bf16* __restrict__ b, const bf16* __restrict__ a,
+                                const bf16* __restrict__ A_log, const bf16* __restrict__ dt_bias, bf16* __restrict__ beta,
+                                float* __restrict__ g, int H) {
+    grid_dep_trigger();
+    const int T = seqs.len[blockIdx.z];
+    if ((int)blockIdx.x * TT >= T) return;
+    const size_t r = (size_t)seqs.row0[blockIdx.z];
+    grid_dep_sync();
+    if ((int)blockIdx.y < conv_blocks) {
+        conv_block<TT>(qkv + r * ld, ld, w, q + r * key_dim, k + r * key_dim, v + r * value_dim, T, key_dim, value_dim);
+        return;
+    }
+    const int first = blockIdx.x * TT * H;
+    const int end = min((int)(blockIdx.x + 1) * TT, T) * H;
+    for (int i = first + (int)threadIdx.x; i < end; i += CONV_THREADS)
+        gate_element(b + r * ld, a + r * ld, ld, A_log, dt_bias, beta + r * H, g + r * H, i, H);
+}
+
 // ---- x * sigmoid(gate) ----
 __global__ void sigmoid_gate_kernel(bf16* __restrict__ x, const bf16* __restrict__ gate, size_t n) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -304,6 +332,38 @@ extern "C" int s1_gdn_conv_gates(const void* qkv, int ld, const void* w, void* q
                static_cast<const bf16*>(w), static_cast<bf16*>(q), static_cast<bf16*>(k), static_cast<bf16*>(v), T, key_dim,
                value_dim, conv_blocks, static_cast<const bf16*>(b), static_cast<const bf16*>(a),
                static_cast<const bf16*>(A_log), static_cast<const bf16*>(dt_bias), static_cast<bf16*>(beta), g, H);
+    return cudaGetLastError();
+}
+
+// s1_gdn_conv_gates for the sequences of one pack in one launch: every pointer is that of packed
+// row 0 (b and a: the two gate columns of row 0); sequence i is rows [row0[i], row0[i] + len[i]).
+// nseq <= 16, len[i] > 0. The same bits as one call per sequence; CS1_ERR_UNSUPPORTED likewise.
+extern "C" int s1_gdn_conv_gates_batch(const void* qkv, int ld, const void* w, void* q, void* k, void* v, const int* row0,
+                                       const int* len, int nseq, int key_dim, int value_dim, const void* b, const void* a,
+                                       const void* A_log, const void* dt_bias, void* beta, float* g, int H, void* stream) {
+    if (nseq <= 0 || nseq > 16 || !row0 || !len || key_dim < 0 || value_dim < 0 || H < 0 || ld < 2 * key_dim + value_dim || ld < H)
+        return cudaErrorInvalidValue;
+    const int channels = 2 * key_dim + value_dim;
+    const bool packed = key_dim % 8 == 0 && value_dim % 8 == 0 && ld % 8 == 0 && aligned16(qkv) && aligned16(w) &&
+                        aligned16(q) && aligned16(k) && aligned16(v);
+    ConvSeqs seqs{};
+    int longest = 0;
+    for (int i = 0; i < nseq; i++) {
+        if (row0[i] < 0 || len[i] <= 0) return cudaErrorInvalidValue;
+        if ((long long)len[i] * H > 0x7fffffffLL) return CS1_ERR_UNSUPPORTED;
+        seqs.row0[i] = row0[i];
+        seqs.len[i] = len[i];
+        longest = longest > len[i] ? longest : len[i];
+    }
+    if (!packed || channels == 0 || H == 0) return CS1_ERR_UNSUPPORTED;
+    const int conv_blocks = (channels / 8 + CONV_THREADS - 1) / CONV_THREADS;
+    const int tt = longest <= CONV_SHORT_TOKENS ? CONV_TT_SHORT : CONV_TT;
+    const dim3 grid((longest + tt - 1) / tt, conv_blocks + 1, nseq);
+    launch_dep(tt == CONV_TT ? gdn_conv_gates_batch_kernel<CONV_TT> : gdn_conv_gates_batch_kernel<CONV_TT_SHORT>, grid,
+               CONV_THREADS, 0, as_stream(stream), static_cast<const bf16*>(qkv), ld, static_cast<const bf16*>(w),
+               static_cast<bf16*>(q), static_cast<bf16*>(k), static_cast<bf16*>(v), seqs, key_dim, value_dim, conv_blocks,
+               static_cast<const bf16*>(b), static_cast<const bf16*>(a), static_cast<const bf16*>(A_log),
+               static_cast<const bf16*>(dt_bias), static_cast<bf16*>(beta), g, H);
     return cudaGetLastError();
 }
 

@@ -415,6 +415,38 @@ int conv_gates(Model* m, const Layer& ly, size_t off, int len) {
     return 0;
 }
 
+// conv_gates of every sequence of the pack: one launch where the fused kernel takes the shapes,
+// else sequence by sequence.
+int conv_gates_pack(Model* m, const Layer& ly, const int* lengths, int nseq) {
+    const Scratch& s = m->s;
+    const int kd = m->key_dim(), vd = m->value_dim(), hv = m->cfg.lin_v_heads, gdn_in = m->gdn_in_w(), conv = m->conv_w();
+    const size_t b = s.gdn_in + (size_t)(conv + vd) * BF16, a = b + (size_t)hv * BF16;
+    for (int first = 0, off = 0; first < nseq;) {
+        const int n = std::min(nseq - first, PACK_SEQS);
+        int row0[PACK_SEQS];
+        for (int i = 0, at = off; i < n; i++) {
+            row0[i] = at;
+            at += lengths[first + i];
+        }
+        int fused = CS1_ERR_UNSUPPORTED;
+        if (m->fuse_swiglu && n > 1) {
+            S1_TRY(op(m, S1_FAMILY_CONV, 0, [&] {
+                fused = s1_gdn_conv_gates_batch(s.at(s.gdn_in), gdn_in, m->w(ly.conv), s.at(s.lq), s.at(s.lk), s.at(s.lv), row0,
+                                                lengths + first, n, kd, vd, s.at(b), s.at(a), m->w(ly.a_log), m->w(ly.dt_bias),
+                                                s.at(s.beta), reinterpret_cast<float*>(s.at(s.g)), hv, m->stream);
+                return fused == CS1_ERR_UNSUPPORTED ? 0 : fused;
+            }));
+            if (fused == 0) m->launches[S1_FAMILY_CONV] += 1;
+        }
+        for (int i = 0; i < n; i++) {
+            if (fused == CS1_ERR_UNSUPPORTED) S1_TRY(conv_gates(m, ly, (size_t)row0[i], lengths[first + i]));
+            off += lengths[first + i];
+        }
+        first += n;
+    }
+    return 0;
+}
+
 // The delta rule of every sequence of the pack in one pair of launches (the reference calls its
 // operator once per sequence, model.rs:690-712): sequence q owns lengths[q] packed rows of which
 // the first `lead` are skipped. s_in: the state all of them start from (null = zero); s_out: where
@@ -517,11 +549,7 @@ int run(Model* m, const int* lengths, int nseq, char* dump) {
         if (!ly.full) {
             S1_TRY(gemm(m, s.x, ly.in_proj, s.gdn_in, t, gdn_in, h));
             const size_t z = s.gdn_in + (size_t)conv * BF16;
-            size_t off = 0;
-            for (int q = 0; q < nseq; q++) {
-                S1_TRY(conv_gates(m, ly, off, lengths[q]));
-                off += lengths[q];
-            }
+            S1_TRY(conv_gates_pack(m, ly, lengths, nseq));
             S1_TRY(delta_rule(m, lengths, nseq, 0, nullptr, nullptr));
             S1_OP(S1_FAMILY_GATED_NORM, 1,
                   cs1_gated_rms_norm(s.at(s.lo), s.at(z), gdn_in, m->w(ly.norm), s.at(s.ln), t, hv, 128, eps, st));

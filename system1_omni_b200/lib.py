@@ -135,6 +135,7 @@ SIGNATURES = {
     "s1_decide": (i32, [vp, i32, f64, vp]),
     "s1_batch_ranges": (i32, [vp, i32, vp]),
     "s1_assign_requests": (i32, [vp, i32, i32, f64, f64, vp]),
+    "s1_gdn_conv_gates_batch": (i32, [vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, i32, vp]),
     "s1_attn_prep_batch": (i32, [vp, vp, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, f32, vp]),
     "s1_attention_gated_batch": (i32, [vp, vp, vp, i32, vp, vp, vp, vp, i32, i32, vp, vp, i32, i32, i32, i32, f32, vp]),
     "s1_gdn_prefill_batch": (i32, [vp, vp, vp, vp, vp, vp, vp, C.c_size_t, vp, vp, i32, i32, i32, f32, vp, vp, vp]),

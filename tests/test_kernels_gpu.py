@@ -215,6 +215,44 @@ def test_gdn_conv_and_gates_in_one_launch(cs1, stream, T, kd, vd, H):
                                  dd.at(), None, None, H, stream.handle) == 2000
 
 
+@pytest.mark.parametrize("lens", [[1, 7, 300, 9, 16, 67], [2100, 33, 2049]])
+def test_gdn_conv_and_gates_of_a_pack_in_one_launch(cs1, stream, lens):
+    """s1_gdn_conv_gates_batch against s1_gdn_conv_gates per sequence: the same bits; a sequence's
+    first rows see zeros before them, not the rows of the sequence packed in front."""
+    kd, vd, H = 256, 512, 4
+    ch = 2 * kd + vd
+    ld = (ch + vd + 2 * H + 7) // 8 * 8
+    T = sum(lens)
+    row0 = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int32)
+    ln = np.array(lens, np.int32)
+    x = O.random_bf16(T * ld, 163, 3.0)
+    w = O.random_bf16(ch * 4, 164, 0.7)
+    A_log = bf(np.random.default_rng(0).uniform(0, np.log(16), H).astype(np.float32))
+    dt = bf(np.random.default_rng(1).normal(0, 0.1, H).astype(np.float32))
+    xd, wd, Ad, dd = dev(x, stream), dev(w, stream), dev(A_log, stream), dev(dt, stream)
+    b_at, a_at = (ch + vd) * 2, (ch + vd + H) * 2
+    outs = []
+    for batch in (False, True):
+        q, k, v = (dev(np.full(T * n, 0x7FC0, np.uint16), stream) for n in (kd, kd, vd))
+        beta, g = dev(np.full(T * H, 0x7FC0, np.uint16), stream), dev(np.full(T * H, np.nan, np.float32), stream)
+        if batch:
+            L.check(cs1.s1_gdn_conv_gates_batch(xd.at(), ld, wd.at(), q.at(), k.at(), v.at(), row0.ctypes.data_as(C.c_void_p),
+                                                ln.ctypes.data_as(C.c_void_p), len(lens), kd, vd, xd.at(b_at), xd.at(a_at),
+                                                Ad.at(), dd.at(), beta.at(), g.at(), H, stream.handle), "batch")
+        else:
+            for a0, n in zip(row0.tolist(), lens):
+                L.check(cs1.s1_gdn_conv_gates(xd.at(a0 * ld * 2), ld, wd.at(), q.at(a0 * kd * 2), k.at(a0 * kd * 2),
+                                              v.at(a0 * vd * 2), n, kd, vd, xd.at(a0 * ld * 2 + b_at), xd.at(a0 * ld * 2 + a_at),
+                                              Ad.at(), dd.at(), beta.at(a0 * H * 2), g.at(a0 * H * 4), H, stream.handle), "one")
+        outs.append([host(q, (T, kd), stream), host(k, (T, kd), stream), host(v, (T, vd), stream),
+                     host(beta, (T, H), stream), host(g, (T, H), stream, np.float32)])
+    for one, many in zip(*outs):
+        assert np.array_equal(one, many)
+    assert cs1.s1_gdn_conv_gates_batch(xd.at(), ld, wd.at(), None, None, None, row0.ctypes.data_as(C.c_void_p),
+                                       ln.ctypes.data_as(C.c_void_p), len(lens), kd - 4, vd, xd.at(b_at), xd.at(a_at), Ad.at(),
+                                       dd.at(), None, None, H, stream.handle) == 2000
+
+
 def test_device_copy_helpers_roundtrip(cs1, stream):
     # kernels.rs:744-769
     a = dev(O.random_bf16(4099, 1, 2.0), stream)
