@@ -1,24 +1,28 @@
-// Causal GQA flash attention for sm_100a on tcgen05: one block per (128 query rows, query head).
+// Causal GQA flash attention for sm_100a on tcgen05: one block per (128 query rows, query head,
+// sequence); a launch covers the sequences of a pack (a table of up to 16 is a kernel parameter).
 //
 //   warp 0    TMA producer: the Q tile once, then K and V tiles of BN keys through two stages
 //             each ([64 rows, 64 columns] boxes, 128-byte swizzle)
-//   warp 1    one thread issues the MMAs: S = Q K^T (128 x BN, K-major operands) into one of two
-//             score buffers in tensor memory, and O += P V (128 x Dh; V is read MN-major, as it
-//             lies in memory) into the output accumulator, also in tensor memory
+//   warp 1    one thread issues the MMAs: S = Q K^T (128 x BN, K-major operands from shared
+//             memory) into one of two score buffers in tensor memory, and O += P V (128 x Dh) with
+//             P read from tensor memory (where the softmax threads left it, over the scores) and V
+//             MN-major from shared memory, as it lies in global memory; O stays in tensor memory
 //   warps 2-9 two threads per query row (warps w and w + 4 share the rows of one quarter of
 //             tensor memory, each takes half of the columns): tcgen05.ld the scores, scale,
 //             causal mask, online softmax in base 2 (the two halves exchange only their row
-//             maximum, through shared memory), rescale O in tensor memory when a row maximum
-//             moved, write P (bf16) into shared memory in the operand layout, and at the end
-//             normalise, gate and store. Two warps per scheduler hide the dependent latencies
-//             of the exponentials that one warp per scheduler leaves exposed.
+//             maximum, through shared memory; the exponent offset of a row moves only when its
+//             maximum has grown by 2^8, so O is rescaled on few tiles; every fourth exponential
+//             is a cubic on the FMA pipe), tcgen05.st P (bf16) back into tensor memory, and at the
+//             end normalise, gate and store.
 //
-// The score MMA of tile j + 1 is issued before the P V MMA of tile j, so it runs under tile
-// j's softmax. Same arithmetic contract as the mma.sync kernel in attention.cu (attention.cu:110-233
-// of the reference): P rounded to bf16 before P V, the row sum taken from the unrounded p, output
-// divided by the sum, then the gate. A row's result does not depend on where its 128-row block
-// starts, only on the key tiling (tiles of BN from position 0), so windows that start at a
-// multiple of 64 repeat the one-shot arithmetic. Every barrier wait is bounded.
+// Head dim 128 runs key tiles of 64 and two blocks per SM, so that one block's MMAs and copies
+// run under the other's softmax; head dim 256 key tiles of 128 and one block per SM. The score
+// MMA of tile j + 1 is issued before the P V MMA of tile j, so it runs under tile j's softmax.
+// Arithmetic contract as in the reference's kernel (attention.cu:110-233 there): P rounded to
+// bf16 before P V, the row sum taken from the unrounded p, output divided by the sum, then the
+// gate. A row's result does not depend on where its 128-row block starts, only on the key tiling
+// (tiles of BN from position 0), so windows that start at a multiple of 64 repeat the one-shot
+// arithmetic. Every barrier wait is bounded.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>

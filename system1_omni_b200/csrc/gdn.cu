@@ -1,12 +1,13 @@
 // Chunked (C = 64) WY-form gated delta rule, prefill only, head dim 128.
 //
-// Two kernels per call, both on tcgen05 tensor cores with accumulators in tensor memory:
-//   gdn_prep_tc5  one block per (two chunks = 128 rows, value head), fully parallel: cumulative
+// Two kernels per call, both on tcgen05 tensor cores with accumulators in tensor memory, each
+// over all the sequences of a pack (a table of up to 16 sequences is a kernel parameter):
+//   gdn_prep_tc5  one block per (chunk = 64 rows, value head, sequence), fully parallel: cumulative
 //             log-decays, L2 norms of q and k, the pair products k.k and q.k (TF32), the
 //             triangular inverse T = (I + A)^-1 in float32, [u | w] = T beta [v | k exp(cum)]
 //             (bf16). Leaves u, w, qd = q exp(cum), kd = k exp(cum_last - cum), P = (q.k)
 //             decay-masked and exp(cum_last) in the workspace.
-//   gdn_scan_tc5  one block per (value head, 64 value columns), sequential over chunks: the
+//   gdn_scan_tc5  one block per (value head, 64 value columns, sequence), sequential over chunks: the
 //             state S [128 x 64] stays on the chip for the whole sequence - the float32 master
 //             in tensor memory, its bf16 copy in shared memory as the operand of the next
 //             chunk's products. Per chunk v_new = u - w S, o = qd S + P v_new (written straight
