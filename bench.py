@@ -403,9 +403,11 @@ def main():
         a, b = disp_cost(cost)
         t = lengths[disp.local].astype(np.float64)
         seen = disp.allgather([float((a * t + b * t * t).sum()), e0.elapsed_ms(e1) / 2])
-        rate = seen[:, 0] / seen[:, 1]
-        speeds = rate / rate.mean()
-        if speeds.max() / speeds.min() > 1.005:
+        with np.errstate(divide="ignore", invalid="ignore"):
+            rate = seen[:, 0] / seen[:, 1]
+        speeds = rate / rate.mean() if np.all(np.isfinite(rate)) and np.all(rate > 0) else np.ones(world)
+        # a rank more than 25 % off the mean is a measurement gone wrong, not a GPU: keep the plain assignment
+        if speeds.max() / speeds.min() > 1.005 and speeds.min() > 0.75 and speeds.max() < 1.25:
             disp.set_speed(speeds)
             disp.plan(model, lengths, N_CLASSES)
             disp.stage(ids_all)
