@@ -415,6 +415,55 @@ def requests(b, out):
     model.close()
 
 
+def single_requests(b, out):
+    """Single-candidate requests one at a time on the 27B-shaped decoder: 74 prompt lengths
+    log-uniform on [80, 3399] (numpy default_rng(74)), the shape statistics the reference publishes
+    for its end-to-end set (74 requests of 80-3399 tokens, concurrency 1). Per request: token ids
+    in host memory -> the public forward call -> last hidden row back on the host -> float64 head ->
+    decision; host wall clock, second pass over the set (the first records nothing but warms
+    kernels up; no length repeats, so no CUDA graph is replayed)."""
+    import time
+    from . import model as M
+    types = [("full_attention" if (i + 1) % 4 == 0 else "linear_attention") for i in range(64)]
+    cfg = M.Config(hidden=5120, intermediate=17408, layer_types=types, heads=24, kv_heads=4, head_dim=128,
+                   rotary_half=32, lin_k_heads=16, lin_v_heads=48, vocab=151936, eps=1e-6, rope_theta=1e7,
+                   max_positions=262144)
+    rng = np.random.default_rng(74)
+    lengths = np.exp(rng.uniform(np.log(80), np.log(3399), 74)).astype(np.int64)
+    prompts = [rng.integers(0, cfg.vocab, int(n)).astype(np.int32) for n in lengths]
+    head = np.random.default_rng(7).normal(0, 1.0, (16, cfg.hidden)).astype(np.float32)
+    model = M.Model(cfg, device=0)
+    model.init_random(seed=0, std=0.02)
+    def two_passes():
+        ms = []
+        for rep in range(2):
+            ms = []
+            for ids in prompts:
+                t0 = time.perf_counter()
+                last = model.forward_batch([ids])[0]
+                M.answer(M.head_logits(head, last))
+                ms.append((time.perf_counter() - t0) * 1e3)
+        return np.array(ms)
+
+    # as shipped (whole-tile GEMMs, so a prompt's bits do not depend on its pack; a length vector is
+    # recorded as a graph on its second sight, which is what the second pass pays for), eager only,
+    # and eager with the few-row GEMM schedules that split K (faster below some 700 rows; bits then
+    # depend on the row count)
+    rows = {}
+    for key, graphs, exact in (("default", True, True), ("eager", False, True), ("eager_split_k", False, False)):
+        model.enable_graphs(graphs)
+        model.set_exact_packing(exact)
+        ms = two_passes()
+        rows[key] = {"ms_mean": float(ms.mean()), "ms_p50": float(np.percentile(ms, 50)), "ms_p95": float(np.percentile(ms, 95)),
+                     "ms_min": float(ms.min()), "ms_max": float(ms.max()), "tokens_per_s": float(lengths.sum() / ms.sum() * 1e3)}
+    out({"op": "single_requests", "model": "27B-shaped", "requests": 74, "distinct_lengths": int(len(set(lengths.tolist()))),
+         "tokens_min": int(lengths.min()), "tokens_max": int(lengths.max()), "tokens_mean": float(lengths.mean()),
+         **{f"{k}_{name}": v for name, r in rows.items() for k, v in r.items()},
+         "weights_once_through_hbm_ms": model.weight_bytes / (peaks()[0] * 1e9) * 1e3,
+         "timing": "host wall clock per request around the public call, head and decision included, second pass"})
+    model.close()
+
+
 def latency(b, out):
     """Prefill time of one request on the 4B-shaped decoder (32 layers, 7.9 GB of bf16 weights) against
     its length, CUDA-graph replay, ids resident on the device: the short-prompt end is bound by one pass
@@ -479,7 +528,7 @@ def attention(b, out):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", default="all", choices=["elementwise", "gemm", "gdn", "layer", "attention", "prefix", "candidates", "requests", "latency", "all"])
+    ap.add_argument("--what", default="all", choices=["elementwise", "gemm", "gdn", "layer", "attention", "prefix", "candidates", "requests", "single", "latency", "all"])
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--out", default=None)
@@ -515,6 +564,8 @@ def main():
         prefix(b, out)
     if args.what == "latency":
         latency(b, out)
+    if args.what == "single":  # builds a 27B-shaped model (47 GB of weights): only on request
+        single_requests(b, out)
     if args.what == "requests":  # builds a 27B-shaped model (47 GB of weights): only on request
         requests(b, out)
     if sink:
