@@ -73,6 +73,17 @@ def test_packed_equals_independent_execution(setup):
     assert np.array_equal(again, packed[perm])
 
 
+def test_more_sequences_than_a_pack_in_one_call(setup):
+    """The per-sequence operators take 16 sequences a launch (the pack limit); a call with more is
+    issued in groups and every prompt still equals its run alone."""
+    cfg, weights, model = setup
+    rng = np.random.default_rng(21)
+    prompts = [rng.integers(0, cfg.vocab, int(n)).tolist() for n in rng.integers(1, 90, 37)]
+    packed = model.forward_batch(prompts)
+    for i in (0, 15, 16, 17, 31, 32, 36):
+        assert np.array_equal(packed[i], model.forward(prompts[i])), i
+
+
 def test_fused_mlp_kernel_equals_the_two_operators(setup):
     """The executor's one-kernel gate/up + SiLU-multiply against the reference's two-operator
     sequence (model.rs:1301-1316): identical hidden states, eager and replayed."""

@@ -85,6 +85,22 @@ def test_continuation_equals_the_one_shot_pass(setup, plen):
     assert np.array_equal(single[0], packed[2])
 
 
+def test_more_candidates_than_a_pack_in_one_continuation(setup):
+    """19 candidates behind one prefix: the per-sequence operators run them in groups of 16, and
+    each still equals its whole prompt run in one piece."""
+    cfg, model = setup
+    rng = np.random.default_rng(33)
+    prefix_ids = rng.integers(0, cfg.vocab, 128).tolist()
+    candidates = [rng.integers(0, cfg.vocab, int(n)).tolist() for n in rng.integers(1, 70, 19)]
+    prefix = model.capture_prefix(prefix_ids)
+    try:
+        packed = model.forward_continue(prefix, candidates)
+    finally:
+        prefix.close()
+    for i in (0, 15, 16, 18):
+        assert np.array_equal(packed[i], model.forward(prefix_ids + candidates[i])), i
+
+
 def test_continuation_without_exact_packing_is_within_rounding(setup):
     cfg, model = setup
     rng = np.random.default_rng(9)
