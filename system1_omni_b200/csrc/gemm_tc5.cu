@@ -25,6 +25,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <math.h>
+
 #include <mutex>
 #include <unordered_map>
 
@@ -998,7 +1000,34 @@ PlanOverride g_override;
 constexpr double SMALL_KB_US[3] = {0.38, 0.31, 0.30};  // widths 256, 128, 64
 constexpr double SMALL_W_BYTES_PER_US = 4.5e6;
 
+// Whole tiles only (no K split: the executor's default, where a row's bits must not depend on the
+// row count): the width alone is chosen, by what the blocks have to pull in. Every block reads its
+// rows of w once from HBM and all of x from L2, and what a launch of n busy SMs takes in per
+// microsecond was measured to saturate as 9.8 (1 - exp(-n / 62)) MB (27B-shaped projections at 81
+// rows, widths 64 to 256: 2.5 MB/us on 20 SMs, 4.6-5.0 on 40, 6.9-7.2 on 80, 8.9 on 112-129), with
+// w itself bounded by 6.3 MB/us of HBM; a launch costs 4 us beside that. Narrow tiles put more SMs
+// to work but fetch x more often; the estimate below weighs the two.
+SmallPlan small_plan_whole(int M, int N, int K, DeviceInfo* info) {
+    const int rows = M < BM ? M : BM;
+    const double w_mb = (double)N * K * 2.0 / 1e6, x_mb = (double)rows * K * 2.0 / 1e6;
+    const int widths[3] = {256, 128, 64};
+    SmallPlan best{64, 1, 1e30};
+    for (int i = 0; i < 3; i++) {
+        const int bn = widths[i];
+        if (g_override.bn && bn != g_override.bn) continue;
+        const long tiles = (long)((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+        const double busy = (double)(tiles < info->sms ? tiles : info->sms);
+        const double intake = 9.8 * (1.0 - exp(-busy / 62.0));
+        const long waves = (tiles + info->sms - 1) / info->sms;
+        const double pull = (w_mb + (double)tiles * x_mb) / intake, hbm = w_mb / 6.3;
+        const double cost = 4.0 + (double)(waves - 1) + (pull > hbm ? pull : hbm);
+        if (cost < best.us - 1e-9) best = SmallPlan{bn, 1, cost};
+    }
+    return best;
+}
+
 SmallPlan small_plan(int M, int N, int K, DeviceInfo* info, bool may_split) {
+    if (!may_split && !g_override.splits && M <= BM) return small_plan_whole(M, N, K, info);  // measured at one row block only
     const int kblocks = (K + BK - 1) / BK;
     const int rows = M < BM ? M : BM;
     const int force_bn = g_override.bn, force_s = g_override.splits;
