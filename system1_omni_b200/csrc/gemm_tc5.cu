@@ -1012,15 +1012,23 @@ SmallPlan small_plan_whole(int M, int N, int K, DeviceInfo* info) {
     const double w_mb = (double)N * K * 2.0 / 1e6, x_mb = (double)rows * K * 2.0 / 1e6;
     const int widths[3] = {256, 128, 64};
     SmallPlan best{64, 1, 1e30};
+    auto intake = [](double busy) { return 9.8 * (1.0 - exp(-busy / 62.0)); };
     for (int i = 0; i < 3; i++) {
         const int bn = widths[i];
         if (g_override.bn && bn != g_override.bn) continue;
         const long tiles = (long)((M + BM - 1) / BM) * ((N + bn - 1) / bn);
-        const double busy = (double)(tiles < info->sms ? tiles : info->sms);
-        const double intake = 9.8 * (1.0 - exp(-busy / 62.0));
-        const long waves = (tiles + info->sms - 1) / info->sms;
-        const double pull = (w_mb + (double)tiles * x_mb) / intake, hbm = w_mb / 6.3;
-        const double cost = 4.0 + (double)(waves - 1) + (pull > hbm ? pull : hbm);
+        // a block has one tile: tiles beyond the SM count run as a further wave, which lasts as long
+        // as its blocks need for their bytes (an SM takes in 0.125 MB/us at most)
+        const double block_mb = (double)bn * K * 2.0 / 1e6 + x_mb;
+        const long full = tiles / info->sms, rest = tiles % info->sms;
+        auto wave = [&](double blocks) {
+            const double all = blocks * block_mb / intake(blocks), one = block_mb / 0.125;
+            return all > one ? all : one;
+        };
+        double pull = (double)full * wave((double)info->sms);
+        if (rest) pull += wave((double)rest);
+        const double hbm = w_mb / 6.3;
+        const double cost = 4.0 + (pull > hbm ? pull : hbm);
         if (cost < best.us - 1e-9) best = SmallPlan{bn, 1, cost};
     }
     return best;
@@ -1057,6 +1065,13 @@ SmallPlan small_plan(int M, int N, int K, DeviceInfo* info, bool may_split) {
                 best = SmallPlan{bn, c, cost};
             }
         }
+    }
+    // One row block: whole tiles as the intake model sees them, where that is clearly ahead of what
+    // this estimate found (the wide projections, which it takes for bound by one streaming rate
+    // whatever the width; on small problems the intake model runs low and does not get the say).
+    if (M <= BM && !force_s) {
+        const SmallPlan whole = small_plan_whole(M, N, K, info);
+        if (whole.us < 0.85 * best_cost) return whole;
     }
     return best;
 }

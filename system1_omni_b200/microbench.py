@@ -178,13 +178,17 @@ def gemm(b, out):
         x = b.bf16(M * K)
         y = L.DeviceBuffer(M * N * 2)
         row = {"model": model, "proj": proj, "M": M, "N": N, "K": K, "flops": 2.0 * M * N * K, "weight_copies": n}
-        arms = [("tcgen05", lambda i: lib.s1_gemm_tcgen05(handle, x.at(), ws[i].at(), y.at(), M, N, K, N, st))]
+        # tcgen05: the planner free to share a tile's K range between blocks (cs1_gemm); whole_tiles: no K
+        # split, a row's bits independent of the row count (what the executor runs by default)
+        arms = [("tcgen05", lambda i: lib.s1_gemm_tcgen05(handle, x.at(), ws[i].at(), y.at(), M, N, K, N, st)),
+                ("whole_tiles", lambda i: lib.s1_gemm_unsplit(handle, x.at(), ws[i].at(), y.at(), M, N, K, N, st))]
         if compare is not None:
             arms.append(("cublaslt", lambda i: compare.s1_compare_library_gemm(x.at(), ws[i].at(), y.at(), M, N, K, st)))
         for engine, call in arms:
             us = b.time(call, n)
             row[engine + "_us"] = us
             row[engine + "_TFLOP/s"] = row["flops"] / us / 1e6
+        row["w_once_from_hbm_us"] = wbytes / (peaks()[0] * 1e3)
         row["tcgen05_frac_of_peak"] = row["tcgen05_TFLOP/s"] / tf
         if compare is not None:
             row["tcgen05_vs_cublaslt"] = row["cublaslt_us"] / row["tcgen05_us"]
