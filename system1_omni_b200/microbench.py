@@ -538,6 +538,7 @@ def main():
     ap.add_argument("--out", default=None)
     ap.add_argument("--gemm-shape", type=int, nargs=3, metavar=("M", "N", "K"), default=None,
                     help="time this one GEMM problem only (for a profiler capture)")
+    ap.add_argument("--gemm-bn", type=int, default=0, help="pin the GEMM planners' tile width (s1_gemm_plan_override), 0 = their choice")
     ap.add_argument("--attn-shape", type=int, nargs=4, metavar=("Dh", "Hq", "Hk", "T"), default=None,
                     help="time this one attention problem only (for a profiler capture)")
     ap.add_argument("--gdn-shape", type=int, nargs=3, metavar=("H", "HK", "T"), default=None,
@@ -550,6 +551,8 @@ def main():
         return 0
     b = Bench(args.warmup, args.iters)
     b.gemm_shape = args.gemm_shape
+    if args.gemm_bn:
+        b.lib.s1_gemm_plan_override(args.gemm_bn, 0, 2, 0)
     b.gdn_shape = args.gdn_shape
     b.attn_shape = args.attn_shape
     sink = open(args.out, "w") if args.out else None
